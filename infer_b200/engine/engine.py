@@ -1,0 +1,218 @@
+"""The step function: one batch of (request, its next tokens) through the model, from the cache.
+
+``Engine.step(entries)`` runs exactly the tokens it is given, as one batch: portions of prompts
+beside single decoded tokens, cut anywhere.  Keys and values of earlier steps come from the
+request's pages; the new tokens' keys and values are written before attention runs, so the tokens
+of one portion see each other causally (the reference's row model, kernels/batch_gpu.cu:238-275 and
+:294-297, generalised from "one prompt" or "one row per slot" to any mix).  It returns float32
+logits at the wanted places, in the order of the entries and of their ``want`` lists.
+
+All per-step integers (token ids, positions, which request each token belongs to, block tables,
+wanted rows) travel to the device in ONE packed int32 buffer and one copy.
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass, field
+from typing import Dict, Hashable, List, Mapping, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache.manager import CacheManager
+from ..config.registry import load_config
+from ..config.specs import ModelSpec
+from ..runtime import Runtime, parse_dtype
+from ..weights.binder import load_weights
+from .model import Model
+from .. import parts as _builtin_parts   # noqa: F401  (registers the built-in parts)
+from .. import models as _builtin_models  # noqa: F401  (registers the built-in architectures)
+
+
+class OutOfPages(RuntimeError):
+    """The step needs more pages than are free. Nothing was changed."""
+
+
+@dataclass
+class StepEntry:
+    rid: Hashable
+    tokens: Sequence[int]
+    want: Sequence[int] = ()        # indices into ``tokens`` whose logits are wanted
+
+
+@dataclass
+class StepContext:
+    """The device-side description of one step's batch. Every tensor is int32 on the device."""
+    n_tokens: int
+    n_segments: int
+    n_want: int
+    token_ids: torch.Tensor          # [T]
+    positions: torch.Tensor          # [T] absolute position of each token in its request
+    token_seg: torch.Tensor          # [T] which segment (entry of the step) the token belongs to
+    seg_start: torch.Tensor          # [S+1] first row of each segment
+    seg_pos0: torch.Tensor           # [S] position of each segment's first token = cached length before the step
+    seg_slot: torch.Tensor           # [S] state slot of each segment's request
+    want_rows: torch.Tensor          # [n_want]
+    block_tables: List[torch.Tensor]  # per cache group: [S, max_blocks]
+    status: torch.Tensor             # [1] kernels raise it on a page index or token id out of range
+    # host copies, for planning kernel launches without a device round trip
+    seg_lens: List[int] = field(default_factory=list)
+    seg_pos0_host: List[int] = field(default_factory=list)
+    max_q_len: int = 0
+    max_ctx_len: int = 0
+    decode_only: bool = False
+    extras: Dict[str, object] = field(default_factory=dict)   # per-step scratch that fast kernels share
+
+
+def _round_up(x: int, m: int) -> int:
+    return (x + m - 1) // m * m
+
+
+class Engine:
+    """A model, its cache and the step function."""
+
+    def __init__(self, spec: ModelSpec, weights: Mapping[str, torch.Tensor], dtype=torch.bfloat16,
+                 device="cuda:0", max_tokens: int = 4096, max_requests: int = 8, page_size: int = 16,
+                 max_seq_len: Optional[int] = None, kernels: Optional[Dict[str, str]] = None):
+        """max_tokens: positions the page pool of every cache group holds (rounded up to whole pages).
+        max_requests: live requests (state slots). max_seq_len: longest request (default: the
+        smaller of the model's position limit and max_tokens)."""
+        if not torch.cuda.is_available():
+            raise RuntimeError("infer_b200 needs a CUDA device; there is no CPU path")
+        dtype = parse_dtype(dtype)
+        self.spec = spec
+        n_pages = max(1, -(-int(max_tokens) // page_size))
+        self.max_seq_len = int(min(spec.max_positions, max_seq_len or n_pages * page_size))
+        self.rt = Runtime(dtype=dtype, device=torch.device(device), kernels=dict(kernels or {}),
+                          max_seq_len=self.max_seq_len)
+        torch.cuda.set_device(self.rt.device)
+        self.model = Model(spec, weights, self.rt)
+        self.cache = CacheManager(self.model.cache_needs(), n_pages, page_size, max_requests)
+        self.cache.make_storage(dtype, self.rt.device)
+        self.cache_views = {cid: self.cache.view(cid) for cid in range(spec.num_caches)}
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.rt.device)
+        self.steps_run = 0
+
+    # ------------------------------------------------------------------ construction helpers
+
+    @classmethod
+    def from_folder(cls, model_dir: str, **kw) -> "Engine":
+        """A folder with config.json and model.safetensors; the model class follows config.json."""
+        arch, typed = load_config(model_dir)
+        spec = arch.to_spec(typed)
+        return cls(spec, load_weights(model_dir, spec), **kw)
+
+    # ------------------------------------------------------------------ requests
+
+    def add_request(self, rid) -> None:
+        self.cache.admit(rid)
+
+    def end_request(self, rid) -> None:
+        self.cache.release(rid)
+
+    def has_request(self, rid) -> bool:
+        return rid in self.cache.requests
+
+    # ------------------------------------------------------------------ the step
+
+    def _build_context(self, entries: Sequence[StepEntry]) -> StepContext:
+        V, cache = self.spec.vocab_size, self.cache
+        S = len(entries)
+        T = sum(len(e.tokens) for e in entries)
+        n_want = sum(len(e.want) for e in entries)
+        n_groups = len(cache.groups)
+        seg_lens = [len(e.tokens) for e in entries]
+        pos0 = [cache.length(e.rid) for e in entries]
+        widths = []
+        for gi in range(n_groups):
+            w = max(-(-(p + n) // cache.page_size) for p, n in zip(pos0, seg_lens))
+            widths.append(_round_up(max(w, 1), 8))
+        # layout of the packed buffer
+        sizes = [T, T, T, S + 1, S, S, max(n_want, 1)] + [S * w for w in widths]
+        offs = np.concatenate([[0], np.cumsum([_round_up(s, 4) for s in sizes])])
+        buf = np.zeros(int(offs[-1]), dtype=np.int32)
+        ids, pos, seg = (buf[offs[i]:offs[i] + T] for i in range(3))
+        seg_start = buf[offs[3]:offs[3] + S + 1]
+        seg_pos0 = buf[offs[4]:offs[4] + S]
+        seg_slot = buf[offs[5]:offs[5] + S]
+        want = buf[offs[6]:offs[6] + n_want]
+        r = w_i = 0
+        for s, e in enumerate(entries):
+            n = seg_lens[s]
+            toks = np.asarray(e.tokens, dtype=np.int64)
+            if toks.ndim != 1 or n == 0:
+                raise ValueError(f"request {e.rid!r}: a step entry needs at least one token")
+            if toks.min() < 0 or toks.max() >= V:
+                bad = int(toks[(toks < 0) | (toks >= V)][0])
+                raise ValueError(f"request {e.rid!r}: token id {bad} is outside the vocabulary [0, {V})")
+            if pos0[s] + n > self.max_seq_len:
+                raise ValueError(f"request {e.rid!r}: {pos0[s] + n} positions exceed the limit of {self.max_seq_len}")
+            ids[r:r + n] = toks
+            pos[r:r + n] = np.arange(pos0[s], pos0[s] + n)
+            seg[r:r + n] = s
+            seg_start[s] = r
+            seg_pos0[s] = pos0[s]
+            seg_slot[s] = cache.slot(e.rid)
+            for wi in e.want:
+                if not 0 <= int(wi) < n:
+                    raise ValueError(f"request {e.rid!r}: wanted place {wi} is outside its {n} tokens")
+                want[w_i] = r + int(wi)
+                w_i += 1
+            r += n
+        seg_start[S] = T
+        for gi in range(n_groups):
+            tab = buf[offs[7 + gi]:offs[7 + gi] + S * widths[gi]].reshape(S, widths[gi])
+            tab[:] = -1
+            for s, e in enumerate(entries):
+                t = cache.block_table(e.rid, gi)
+                tab[s, :len(t)] = t
+        dev = torch.from_numpy(buf).pin_memory().to(self.rt.device, non_blocking=True)
+
+        def cut(i, n):
+            return dev[int(offs[i]):int(offs[i]) + n]
+        return StepContext(
+            n_tokens=T, n_segments=S, n_want=n_want,
+            token_ids=cut(0, T), positions=cut(1, T), token_seg=cut(2, T), seg_start=cut(3, S + 1),
+            seg_pos0=cut(4, S), seg_slot=cut(5, S), want_rows=cut(6, n_want),
+            block_tables=[cut(7 + gi, S * widths[gi]).view(S, widths[gi]) for gi in range(n_groups)],
+            status=self.status, seg_lens=seg_lens, seg_pos0_host=pos0, max_q_len=max(seg_lens),
+            max_ctx_len=max(p + n for p, n in zip(pos0, seg_lens)), decode_only=all(n == 1 for n in seg_lens))
+
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Runs one batch; returns float32 logits [wanted places, vocab] on the device."""
+        entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
+        if not entries:
+            return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.rt.device)
+        rids = [e.rid for e in entries]
+        if len(set(rids)) != len(rids):
+            raise ValueError("a request may appear once in a step")
+        for e in entries:
+            if e.rid not in self.cache.requests:
+                raise KeyError(f"request {e.rid!r} is not admitted (add_request first)")
+        wanted = [(e.rid, len(e.tokens)) for e in entries]
+        if not self.cache.can_reserve(wanted):
+            raise OutOfPages(f"step needs more pages than are free (free per group: {self.cache.pages_free()})")
+        for rid, n in wanted:
+            if not self.cache.reserve(rid, n):
+                raise AssertionError("reserve failed after can_reserve succeeded")
+        try:
+            ctx = self._build_context(entries)
+        except Exception:
+            for rid in rids:
+                self.cache.unreserve(rid)
+            raise
+        with torch.cuda.device(self.rt.device):
+            logits = self.model.forward(ctx, self.cache_views)
+        for rid, n in wanted:
+            self.cache.advance(rid, n)
+        self.steps_run += 1
+        return logits
+
+    def check_status(self) -> None:
+        """Synchronises and raises if a kernel met a page index or token id out of range."""
+        code = int(self.status.item())
+        if code:
+            self.status.zero_()
+            what = {1: "a token id outside the table", 2: "a cache write through an invalid page",
+                    3: "a cache read through an invalid page"}.get(code, f"code {code}")
+            raise RuntimeError(f"device status word was raised: {what}")

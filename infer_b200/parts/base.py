@@ -1,0 +1,147 @@
+"""Interfaces of the parts a layer is made of, and the registries that map a spec's ``kind`` to a class.
+
+A part is built from its own ``PartSpec`` alone: it knows its sizes and constants, the local
+names and shapes of its parameters, and what it needs from the cache manager.  It does not know
+which architecture, which layer index or which model it is in.
+
+To add a part: subclass the matching interface below, decorate it with
+``@register_mixer("name")`` (or the feed-forward / norm / position / block variant), and let an
+architecture's ``to_spec`` name that kind.  No framework file changes.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any, Callable, Dict, Mapping, Optional, Tuple
+
+import torch
+
+from ..config.specs import PartSpec
+
+
+# ----------------------------------------------------------------------------- cache needs
+
+@dataclass(frozen=True)
+class PagedKVNeed:
+    """Keys and values of every position (or of the last ``window`` positions) in pages."""
+    num_kv_heads: int
+    head_dim: int
+    window: Optional[int] = None     # None: all positions stay; n: only the last n are ever read
+
+
+@dataclass(frozen=True)
+class StateNeed:
+    """A fixed-size state per request, zeroed when the request is admitted.
+
+    shapes maps a state tensor's name to (shape without the slot dimension, torch dtype)."""
+    shapes: Mapping[str, Tuple[Tuple[int, ...], torch.dtype]]
+
+
+# ----------------------------------------------------------------------------- interfaces
+
+class Part:
+    """Common surface of every part."""
+
+    def __init__(self, spec: PartSpec, runtime: "Runtime"):
+        self.spec = spec
+        self.rt = runtime
+
+    @classmethod
+    def param_shapes(cls, spec: PartSpec) -> Dict[str, Tuple[int, ...]]:
+        """Local parameter name -> shape, as the checkpoint stores them under ``spec.prefix``."""
+        return {}
+
+    @classmethod
+    def init_params(cls, spec: PartSpec, name: str, shape: Tuple[int, ...], gen: torch.Generator) -> torch.Tensor:
+        """Random value for one parameter (float32, on the generator's device): matrices and
+        biases N(0, 0.02).  Parts whose parameters want another distribution override this."""
+        return torch.randn(shape, generator=gen, dtype=torch.float32, device=gen.device) * 0.02
+
+    def load(self, params: Mapping[str, torch.Tensor]) -> None:
+        """Receives the part's parameters (CPU tensors in their stored dtype) and moves what it
+        needs to the device, in the layout its kernels want."""
+
+
+class Norm(Part):
+    def forward(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        """x [rows, size] float32 (the residual stream) -> normalised rows in the compute dtype."""
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    def apply(self, q: torch.Tensor, k: torch.Tensor, positions: torch.Tensor) -> None:
+        """Encodes positions into q [T, heads, head_dim] and k [T, kv_heads, head_dim] in place.
+        positions: int32 [T], absolute."""
+        raise NotImplementedError
+
+    def rotary_tables(self):
+        """(cos, sin) float32 [max_positions, head_dim/2] if this encoding is a half-split rotation
+        that a mixer's fused kernel may apply itself; None otherwise."""
+        return None
+
+
+class Mixer(Part):
+    def cache_need(self):
+        """PagedKVNeed, StateNeed or None."""
+        return None
+
+    def forward(self, x: torch.Tensor, step: "StepContext", cache: Any, residual: torch.Tensor,
+                write_cache: bool = True) -> torch.Tensor:
+        """x: normalised rows [T, hidden] in the compute dtype; residual: float32 [T, hidden].
+        Returns residual + mixer(x) as float32 [T, hidden] (it may overwrite ``residual``).
+        ``cache`` is what the cache manager made for this part's need: a ``PagedKVView``,
+        a dict of state tensors [slots, ...], or None."""
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, x: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
+        """Returns residual + feed_forward(x), float32 [T, hidden] (may overwrite ``residual``)."""
+        raise NotImplementedError
+
+
+class Block:
+    """An arrangement of a mixer, a feed-forward and their norms."""
+
+    def __init__(self, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm, feed_forward_norm: Norm):
+        self.mixer, self.feed_forward = mixer, feed_forward
+        self.mixer_norm, self.feed_forward_norm = mixer_norm, feed_forward_norm
+
+    def forward(self, h: torch.Tensor, step: "StepContext", cache: Any, write_cache: bool) -> torch.Tensor:
+        raise NotImplementedError
+
+
+# ----------------------------------------------------------------------------- registries
+
+_REGISTRIES: Dict[str, Dict[str, type]] = {"mixer": {}, "feed_forward": {}, "norm": {}, "position": {}, "block": {}}
+
+
+def _register(family: str, name: str) -> Callable[[type], type]:
+    def deco(cls: type) -> type:
+        if name in _REGISTRIES[family] and _REGISTRIES[family][name] is not cls:
+            raise ValueError(f"{family} kind {name!r} is already registered")
+        _REGISTRIES[family][name] = cls
+        return cls
+    return deco
+
+
+def register_mixer(name: str): return _register("mixer", name)
+def register_feed_forward(name: str): return _register("feed_forward", name)
+def register_norm(name: str): return _register("norm", name)
+def register_position(name: str): return _register("position", name)
+def register_block(name: str): return _register("block", name)
+
+
+def unregister(family: str, name: str) -> None:
+    _REGISTRIES[family].pop(name, None)
+
+
+def part_class(family: str, kind: str) -> type:
+    try:
+        return _REGISTRIES[family][kind]
+    except KeyError:
+        known = ", ".join(sorted(_REGISTRIES[family])) or "(none)"
+        raise KeyError(f"no {family} part of kind {kind!r} is registered; known: {known}") from None
+
+
+def build_part(family: str, spec: PartSpec, runtime: "Runtime") -> Part:
+    return part_class(family, spec.kind)(spec, runtime)
