@@ -308,6 +308,95 @@ __global__ void sample_kernel(const float* __restrict__ logits, int64_t vocab, c
     if (threadIdx.x == 0) out[b] = si[0] == 0x7fffffff ? 0 : si[0];
 }
 
+// Sampling with top-k / top-p filters (src/sampler.cpp:8-63): x = logit / T; keep the k largest x; among
+// those keep the smallest set of largest probabilities whose mass reaches top_p; sample among the kept
+// by argmax of x + Gumbel noise. Both thresholds are found by bisection over an order-preserving integer
+// image of x, each probe a fixed-order block reduction, so the result is the same on every run.
+__device__ __forceinline__ uint32_t ordered_key(float x) {
+    const uint32_t u = __float_as_uint(x);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+__global__ void __launch_bounds__(1024)
+sample_filtered_kernel(const float* __restrict__ logits, int64_t vocab, const float* __restrict__ temperature,
+                       const int64_t* __restrict__ seed, const int64_t* __restrict__ step,
+                       const int64_t* __restrict__ top_k, const float* __restrict__ top_p, int* __restrict__ out) {
+    __shared__ float red[32];
+    __shared__ float sv[1024];
+    __shared__ int si[1024];
+    const int b = blockIdx.x;
+    const float* row = logits + int64_t(b) * vocab;
+    const float T = temperature[b];
+    const float invT = T > 0.0f ? 1.0f / T : 1.0f;
+    uint32_t thr = 0u;                                   // keep keys >= thr
+    float mx = -INFINITY;
+    for (int64_t v = threadIdx.x; v < vocab; v += blockDim.x) mx = fmaxf(mx, row[v] * invT);
+    mx = ib::block_max(mx, red);
+    if (T > 0.0f) {
+        const int64_t k = top_k[b];
+        if (k > 0 && k < vocab) {
+            uint32_t lo = 0u, hi = 0xFFFFFFFFu;
+            while (lo < hi) {
+                const uint32_t mid = lo + (hi - lo) / 2u + ((hi - lo) & 1u);
+                float cnt = 0.0f;
+                for (int64_t v = threadIdx.x; v < vocab; v += blockDim.x) cnt += ordered_key(row[v] * invT) >= mid ? 1.0f : 0.0f;
+                cnt = ib::block_sum(cnt, red);
+                if (cnt >= float(k)) lo = mid; else hi = mid - 1u;
+            }
+            thr = lo;
+        }
+        const float p = top_p[b];
+        if (p < 1.0f) {
+            float Z = 0.0f;
+            for (int64_t v = threadIdx.x; v < vocab; v += blockDim.x) {
+                const float x = row[v] * invT;
+                if (ordered_key(x) >= thr) Z += expf(x - mx);
+            }
+            Z = ib::block_sum(Z, red);
+            const float want = p * Z;
+            uint32_t lo = thr, hi = 0xFFFFFFFFu;
+            while (lo < hi) {
+                const uint32_t mid = lo + (hi - lo) / 2u + ((hi - lo) & 1u);
+                float mass = 0.0f;
+                for (int64_t v = threadIdx.x; v < vocab; v += blockDim.x) {
+                    const float x = row[v] * invT;
+                    if (ordered_key(x) >= mid) mass += expf(x - mx);
+                }
+                mass = ib::block_sum(mass, red);
+                if (mass >= want) lo = mid; else hi = mid - 1u;
+            }
+            thr = lo;
+        }
+    }
+    float best = -INFINITY;
+    int besti = 0x7fffffff;
+    for (int64_t v = threadIdx.x; v < vocab; v += blockDim.x) {
+        float x = row[v] * invT;
+        if (T > 0.0f) {
+            if (ordered_key(x) < thr) continue;
+            x = row[v] / T - logf(-logf(hash_uniform(uint64_t(seed[b]), uint64_t(step[b]), uint64_t(v))));
+        } else {
+            x = row[v];
+        }
+        if (x > best || (x == best && v < besti)) { best = x; besti = int(v); }
+    }
+    sv[threadIdx.x] = best;
+    si[threadIdx.x] = besti;
+    __syncthreads();
+    for (int s = blockDim.x / 2; s > 0; s >>= 1) {
+        if (threadIdx.x < s) {
+            const float ov = sv[threadIdx.x + s];
+            const int oi = si[threadIdx.x + s];
+            if (ov > sv[threadIdx.x] || (ov == sv[threadIdx.x] && oi < si[threadIdx.x])) {
+                sv[threadIdx.x] = ov;
+                si[threadIdx.x] = oi;
+            }
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) out[b] = si[0] == 0x7fffffff ? 0 : si[0];
+}
+
 inline unsigned blocks_for(int64_t n, int threads) { return unsigned((n + threads - 1) / threads); }
 
 }  // namespace
@@ -421,4 +510,13 @@ IB_EXPORT int ib_sample(const float* logits, int64_t n_rows, int64_t vocab, cons
     if (vocab <= 0 || vocab >= 0x7fffffff) return ib::fail(IB_ERR_ARG, "ib_sample: vocabulary %lld out of range", (long long)vocab);
     sample_kernel<<<unsigned(n_rows), 256, 0, stream>>>(logits, vocab, temperature, seed, step, out);
     return ib::check_launch("ib_sample");
+}
+
+IB_EXPORT int ib_sample_filtered(const float* logits, int64_t n_rows, int64_t vocab, const float* temperature,
+                                 const int64_t* seed, const int64_t* step, const int64_t* top_k, const float* top_p,
+                                 int* out, cudaStream_t stream) {
+    if (n_rows <= 0) return IB_OK;
+    if (vocab <= 0 || vocab >= 0x7fffffff) return ib::fail(IB_ERR_ARG, "ib_sample_filtered: vocabulary %lld out of range", (long long)vocab);
+    sample_filtered_kernel<<<unsigned(n_rows), 1024, 0, stream>>>(logits, vocab, temperature, seed, step, top_k, top_p, out);
+    return ib::check_launch("ib_sample_filtered");
 }

@@ -73,10 +73,12 @@ class Engine:
 
     def __init__(self, spec: ModelSpec, weights: Mapping[str, torch.Tensor], dtype=torch.bfloat16,
                  device="cuda:0", max_tokens: int = 4096, max_requests: int = 8, page_size: int = 16,
-                 max_seq_len: Optional[int] = None, kernels: Optional[Dict[str, str]] = None):
+                 max_seq_len: Optional[int] = None, kernels: Optional[Dict[str, str]] = None,
+                 cache_budget_bytes: int = 0):
         """max_tokens: positions the page pool of every cache group holds (rounded up to whole pages).
         max_requests: live requests (state slots). max_seq_len: longest request (default: the
-        smaller of the model's position limit and max_tokens)."""
+        smaller of the model's position limit and max_tokens). cache_budget_bytes, if given, replaces max_tokens:
+        the page pools together take at most this many bytes."""
         if not torch.cuda.is_available():
             raise RuntimeError("infer_b200 needs a CUDA device; there is no CPU path")
         dtype = parse_dtype(dtype)
@@ -87,7 +89,11 @@ class Engine:
                           max_seq_len=self.max_seq_len)
         torch.cuda.set_device(self.rt.device)
         self.model = Model(spec, weights, self.rt)
-        self.cache = CacheManager(self.model.cache_needs(), n_pages, page_size, max_requests)
+        needs = self.model.cache_needs()
+        if cache_budget_bytes:
+            probe = CacheManager(needs, 1, page_size, 1)
+            n_pages = max(1, int(cache_budget_bytes) // max(1, probe.storage_bytes(dtype)))
+        self.cache = CacheManager(needs, n_pages, page_size, max_requests)
         self.cache.make_storage(dtype, self.rt.device)
         self.cache_views = {cid: self.cache.view(cid) for cid in range(spec.num_caches)}
         self.status = torch.zeros(1, dtype=torch.int32, device=self.rt.device)

@@ -204,3 +204,21 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, seed: torch.Tensor, 
     f = _fn("plain", "ib_sample", [c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
     _call(f, logits.data_ptr(), B, V, temperature.data_ptr(), seed.data_ptr(), step.data_ptr(), out.data_ptr(), _stream())
     return out
+
+
+def sample_filtered(logits: torch.Tensor, temperature: torch.Tensor, seed: torch.Tensor, step: torch.Tensor,
+                    top_k: torch.Tensor, top_p: torch.Tensor) -> torch.Tensor:
+    """As ``sample``, after keeping the top_k (int64 [B], 0 = all) largest logits and then the smallest set of
+    largest probabilities whose mass reaches top_p (float32 [B], 1 = all)."""
+    _check(logits, "logits", torch.float32)
+    B, V = logits.shape
+    _check(temperature, "temperature", torch.float32, (B,))
+    _check(seed, "seed", torch.int64, (B,))
+    _check(step, "step", torch.int64, (B,))
+    _check(top_k, "top_k", torch.int64, (B,))
+    _check(top_p, "top_p", torch.float32, (B,))
+    out = torch.empty((B,), dtype=torch.int32, device=logits.device)
+    f = _fn("plain", "ib_sample_filtered", [c_void_p, c_int64, c_int64] + [c_void_p] * 7)
+    _call(f, logits.data_ptr(), B, V, temperature.data_ptr(), seed.data_ptr(), step.data_ptr(), top_k.data_ptr(),
+          top_p.data_ptr(), out.data_ptr(), _stream())
+    return out

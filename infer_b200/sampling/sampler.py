@@ -1,0 +1,48 @@
+"""Sampling on the device.
+
+Greedy (temperature 0): first index of the maximum.  Temperature: argmax of logit/T + Gumbel noise,
+the noise a hash of (seed, position of the token fed, vocabulary index); this is an exact sample of
+softmax(logits/T), needs no state, and gives the same stream however the request is batched or cut
+(kernels/ops/batch.cu:450-478; kernels/batch_gpu.cu:245).  top-k / top-p (src/sampler.cpp:8-63):
+keep the k highest logits, then the smallest set of highest probabilities whose mass reaches p,
+and sample among those the same way.
+"""
+from __future__ import annotations
+
+from typing import List, Sequence
+
+import numpy as np
+import torch
+
+from .. import ops
+
+
+class Sampler:
+    def __init__(self, device):
+        self.device = torch.device(device)
+
+    def sample(self, logits: torch.Tensor, params: Sequence, positions: Sequence[int]) -> torch.Tensor:
+        """logits float32 [B, vocab] on the device; params: objects with temperature, seed, top_k, top_p;
+        positions: the sampler's step key per row. Returns int32 [B] on the device."""
+        B = logits.shape[0]
+        if B != len(params) or B != len(positions):
+            raise ValueError("one SampleParams and one position per row of logits")
+        host = np.zeros((B, 4), dtype=np.int64)
+        temp = np.zeros(B, dtype=np.float32)
+        top_p = np.ones(B, dtype=np.float32)
+        filtered = False
+        for i, (p, pos) in enumerate(zip(params, positions)):
+            temp[i] = max(0.0, float(p.temperature))
+            host[i, 0] = int(p.seed) & 0x7FFFFFFFFFFFFFFF
+            host[i, 1] = int(pos)
+            host[i, 2] = int(getattr(p, "top_k", 0) or 0)
+            top_p[i] = float(getattr(p, "top_p", 1.0))
+            if temp[i] > 0 and (host[i, 2] > 0 or top_p[i] < 1.0):
+                filtered = True
+        ints = torch.from_numpy(host).pin_memory().to(self.device, non_blocking=True)
+        t = torch.from_numpy(temp).pin_memory().to(self.device, non_blocking=True)
+        seed, step = ints[:, 0].contiguous(), ints[:, 1].contiguous()
+        if not filtered:
+            return ops.sample(logits, t, seed, step)
+        tp = torch.from_numpy(top_p).pin_memory().to(self.device, non_blocking=True)
+        return ops.sample_filtered(logits, t, seed, step, ints[:, 2].contiguous(), tp)
