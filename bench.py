@@ -1,0 +1,301 @@
+"""Headline benchmark: decode tokens/s (and prefill tokens/s at 2,048 tokens) at Qwen2.5-1.5B layer sizes with
+random weights on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--context 2048] [--layers L] [--impl reference]
+
+Prints ONE JSON line. "value" is decoded tokens per second of the step function, timed on the device with CUDA
+events around K decode steps of a batch of 8 requests whose 2,048-token contexts already lie in the paged cache
+(the cache is filled with random keys and values: throughput does not depend on their values). "e2e" is the same
+through the Python entry point's scheduler: host token ids in, sampled host token ids out, every step.
+Every step reads all weights (3.1 GB) and the live requests' cache (0.47 GB at batch 8): far more than the 126 MB
+L2, so no flush is needed between steps.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# BASELINE.json configs[2]: Qwen2.5-1.5B layer sizes
+CONFIG = dict(architectures=["Qwen2ForCausalLM"], hidden_size=1536, num_hidden_layers=28, num_attention_heads=12,
+              num_key_value_heads=2, intermediate_size=8960, vocab_size=151936, rope_theta=1000000.0, rms_norm_eps=1e-6,
+              max_position_embeddings=32768, tie_word_embeddings=True, use_sliding_window=False)
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    src = "fallback"
+    p = dict(FALLBACK_PEAKS)
+    if os.path.isfile(path):
+        try:
+            raw = json.load(open(path))
+            flat = {}
+
+            def walk(d):
+                for k, v in d.items():
+                    if isinstance(v, dict):
+                        walk(v)
+                    elif isinstance(v, (int, float)):
+                        flat.setdefault(k, float(v))
+            walk(raw)
+            for k in p:
+                if k in flat:
+                    p[k] = flat[k]
+            src = "measured"
+        except Exception:
+            pass
+    p["source"] = src
+    return p
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs (reads only)."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.rows, self.proc = [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0])), mx.append(float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for n, v in zip(names, r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def build_engine(n_layers, batch, context, steps_total, dtype="bfloat16"):
+    import torch
+    from infer_b200.config import parse_config
+    from infer_b200.engine import Engine
+    from infer_b200.weights import random_weights
+    import infer_b200.models  # noqa: F401
+    cfg = dict(CONFIG, num_hidden_layers=n_layers)
+    arch, typed = parse_config(cfg)
+    spec = arch.to_spec(typed)
+    W = random_weights(spec, 0, torch.bfloat16, device="cuda")
+    max_seq = context + steps_total + 16
+    eng = Engine(spec, W, dtype=dtype, max_tokens=batch * (max_seq + 16), max_requests=batch, max_seq_len=max_seq)
+    del W
+    torch.cuda.empty_cache()
+    return eng
+
+
+def fill_contexts(eng, batch, context):
+    """Admits `batch` requests and gives each a context of `context` positions of random keys and values."""
+    import torch
+    for g in eng.cache.groups:
+        g.k.normal_(0, 0.5)
+        g.v.normal_(0, 0.5)
+    for r in range(batch):
+        eng.add_request(r)
+        assert eng.cache.reserve(r, context)
+        eng.cache.advance(r, context)
+    torch.cuda.synchronize()
+
+
+def release_all(eng):
+    for r in list(eng.cache.requests):
+        eng.end_request(r)
+
+
+def decode_bytes(eng, batch, context_mid):
+    """Bytes one decode step has to read: every weight once (the token table only as the output matrix when tied,
+    plus `batch` rows), and the cache of the live requests."""
+    spec = eng.spec
+    w = eng.model.weight_bytes()
+    item = 2 if str(eng.rt.dtype).endswith("bfloat16") else 4
+    if spec.head_name is not None:
+        w -= spec.vocab_size * spec.hidden_size * item - batch * spec.hidden_size * item
+    kv = sum(2 * len(g.cache_ids) * g.need.num_kv_heads * g.need.head_dim * item for g in eng.cache.groups)
+    return w + batch * context_mid * kv, w, kv
+
+
+def time_decode(eng, batch, context, steps, warmup, kernel_counter):
+    """Device-timed decode steps of the step function: greedy ids are fed back on the device side of the engine's
+    inputs only through the host packing of token ids (the ids fed are fixed: throughput does not depend on them)."""
+    import torch
+    from infer_b200.engine import StepEntry
+    fill_contexts(eng, batch, context)
+    ids = [(7 * r + 1) % eng.spec.vocab_size for r in range(batch)]
+
+    def one():
+        return eng.step([StepEntry(r, [ids[r]], [0]) for r in range(batch)])
+    for _ in range(warmup):
+        one()
+    torch.cuda.synchronize()
+    n0 = kernel_counter()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        one()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    eng.check_status()
+    launches = kernel_counter() - n0
+    release_all(eng)
+    return ms / steps, launches
+
+
+def time_prefill(eng, tokens, reps, warmup):
+    import torch
+    from infer_b200.engine import StepEntry
+    import numpy as np
+    ids = np.random.default_rng(0).integers(0, eng.spec.vocab_size, tokens).tolist()
+    times = []
+    for i in range(warmup + reps):
+        eng.add_request("p")
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        eng.step([StepEntry("p", ids, [tokens - 1])])
+        e1.record()
+        torch.cuda.synchronize()
+        eng.end_request("p")
+        if i >= warmup:
+            times.append(e0.elapsed_time(e1))
+    times.sort()
+    return times[len(times) // 2]
+
+
+def prefill_flops(cfg, n_layers, T):
+    H, nh, nkv, hd, I, V = (cfg["hidden_size"], cfg["num_attention_heads"], cfg["num_key_value_heads"],
+                            cfg["hidden_size"] // cfg["num_attention_heads"], cfg["intermediate_size"], cfg["vocab_size"])
+    lin = 2 * T * (H * (nh + 2 * nkv) * hd + nh * hd * H + 3 * H * I)
+    attn = 2 * 2 * nh * hd * T * (T + 1) / 2
+    return n_layers * (lin + attn) + 2 * H * V          # logits at the last place only
+
+
+def time_e2e(eng, batch, context, steps, warmup):
+    """Decode through the scheduler of the Python entry point: every step packs host token ids into pinned memory,
+    copies them to the device, runs the step, samples on the device and reads the sampled ids back to the host."""
+    import torch
+    from infer_b200.engine.generation import GenerationEngine
+    from infer_b200.engine.scheduler import BatchItem, SampleParams
+    fill_contexts(eng, batch, context)
+    ge = GenerationEngine(eng)
+    toks = {r: (7 * r + 1) % eng.spec.vocab_size for r in range(batch)}
+    sp = SampleParams()
+    pos = context
+
+    def one(pos):
+        out = ge.run([BatchItem(r, [toks[r]], sp, pos) for r in range(batch)])
+        for r, t in out.items():
+            toks[r] = t
+    for _ in range(warmup):
+        one(pos)
+        pos += 1
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        one(pos)
+        pos += 1
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    # per step: the packed int32 buffer and the sampler's parameters in, `batch` int32 token ids out
+    h2d = eng.last_h2d_bytes + ge.sampler.last_h2d_bytes
+    release_all(eng)
+    return batch * steps / dt, h2d, 4 * batch
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=2048)
+    ap.add_argument("--layers", type=int, default=CONFIG["num_hidden_layers"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable": "RyanXiaoo/infer is a C++/CUDA CMake project built for sm_120 "
+                          "only, with no setup.py or pyproject.toml: pip reports 'not installable'"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    args.warmup = max(3, args.warmup)
+    import torch
+    from infer_b200 import ops
+    pk = peaks()
+    n_layers = args.layers
+    total_steps = args.steps + args.warmup
+    eng = build_engine(n_layers, 64, args.context, 2 * total_steps + 64)
+    cfg = CONFIG
+
+    clocks = ClockSampler()
+    clocks.start()
+    ms_step, launches = time_decode(eng, args.batch, args.context, args.steps, args.warmup, ops.kernel_launches)
+    clk = clocks.stop()
+    value = args.batch * 1e3 / ms_step
+    ctx_mid = args.context + args.warmup + args.steps // 2
+    nbytes, wbytes, kv_per_tok = decode_bytes(eng, args.batch, ctx_mid)
+    achieved = nbytes / (ms_step * 1e-3) / 1e9
+    e2e_value, h2d, d2h = time_e2e(eng, args.batch, args.context, args.steps, args.warmup)
+
+    out = {"metric": "decode tok/s at batch 8, 2048-token contexts (Qwen2.5-1.5B sizes)", "value": round(value, 1),
+           "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_step, 4),
+           "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+           "data": "synthetic: random weights N(0,0.02), random cache contents, fixed token ids",
+           "config": {"model": "Qwen2.5-1.5B sizes", "layers": n_layers, "layers_of_model": CONFIG["num_hidden_layers"],
+                      "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+                      "head_dim": 128, "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
+                      "global_batch": args.batch, "seq_len": args.context, "page_size": 16, "tied_head": True,
+                      "parallelism": "single GPU", "l2": "inputs larger than L2 (3.1 GB weights per step)",
+                      "peaks": pk["source"]},
+           "clocks": clk, "gpu_launches": launches,
+           "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+           "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                        "frac": round(achieved / pk["hbm_gbs"], 4)}}
+    if not args.no_points:
+        points = {}
+        for b in (1, 64):
+            ms_b, _ = time_decode(eng, b, args.context, max(16, args.steps // 2), args.warmup, ops.kernel_launches)
+            points[f"decode_b{b}"] = round(b * 1e3 / ms_b, 1)
+        out["points"] = points
+        T = 2048
+        ms_p = time_prefill(eng, T, 5, 3)
+        fl = prefill_flops(cfg, n_layers, T)
+        out["prefill"] = {"value": round(T * 1e3 / ms_p, 1), "tokens": T, "ms": round(ms_p, 3),
+                          "frac": round(fl / (ms_p * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -173,6 +173,7 @@ class Engine:
                 t = cache.block_table(e.rid, gi)
                 tab[s, :len(t)] = t
         dev = torch.from_numpy(buf).pin_memory().to(self.rt.device, non_blocking=True)
+        self.last_h2d_bytes = buf.nbytes
 
         def cut(i, n):
             return dev[int(offs[i]):int(offs[i]) + n]

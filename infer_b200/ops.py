@@ -64,7 +64,16 @@ def _fn(module: str, name: str, argtypes):
     return f
 
 
+_LAUNCHES = [0]
+
+
+def kernel_launches() -> int:
+    """How many launcher calls of this package's own kernels have been made in this process."""
+    return _LAUNCHES[0]
+
+
 def _call(f, *args) -> None:
+    _LAUNCHES[0] += 1
     rc = f(*args)
     if rc != 0:
         msg = f._lib.ib_last_error()

@@ -41,6 +41,7 @@ class Sampler:
                 filtered = True
         ints = torch.from_numpy(host).pin_memory().to(self.device, non_blocking=True)
         t = torch.from_numpy(temp).pin_memory().to(self.device, non_blocking=True)
+        self.last_h2d_bytes = host.nbytes + temp.nbytes
         seed, step = ints[:, 0].contiguous(), ints[:, 1].contiguous()
         if not filtered:
             return ops.sample(logits, t, seed, step)
