@@ -1,0 +1,525 @@
+// bfloat16 matrix product on the 5th-generation tensor cores of sm_100a:
+//   out[M, N] = x[M, K] . w[N, K]^T (+ bias[N]) (+ residual[M, N])
+// both operands row-major with K contiguous ("K-major"), float accumulation in tensor memory (TMEM).
+//
+// Structure of one CTA (192 threads, one 128 x BN output tile, BN in {16, 32, 64, 128}):
+//   warp 0      one lane issues TMA loads (cp.async.bulk.tensor.2d, 128-byte swizzle) of 128 x 64 and BN x 64
+//               operand tiles into a ring of shared-memory stages, each guarded by a full/empty mbarrier pair;
+//   warp 1      allocates BN TMEM columns; one lane issues tcgen05.mma (M=128, N=BN, K=16, kind::f16) four times
+//               per stage, then tcgen05.commit to hand the stage back, and at the end to signal the epilogue;
+//   warps 2-5   read the accumulator with tcgen05.ld (each warp its 32 TMEM lanes = 32 tile rows), apply the
+//               epilogue (bias, residual, conversion) and store to global memory.
+//
+// Two ways to map the product onto a tile:
+//   plain   A = x (tokens on the 128-row side), B = w;  for many tokens (prefill)
+//   swap    A = w (output features on the 128-row side), B = x, tokens on the BN side padded to 16/32/64;
+//           for few tokens (decode), where the weights are streamed once and the tensor core's M is not wasted.
+// With few tiles the K range is cut into `splits` slices (grid.z); each CTA writes a float partial tile to the
+// workspace, and the CTA that arrives last at the tile's counter adds the slices in ascending order (so the sum
+// does not depend on arrival order) and runs the epilogue.
+//
+// Sizes: any M, N >= 1; K a multiple of 8 (TMA needs 16-byte row pitch); rows beyond M, N and columns beyond K are
+// zero-filled by TMA and masked at the store. Everything else is refused with an error.
+//
+// Every wait on an mbarrier is bounded; a wait that runs out raises the status word, and the CTA drains its
+// copies, frees its TMEM and returns.
+#include "common.cuh"
+
+#include <cuda.h>
+#include <mutex>
+#include <unordered_map>
+
+IB_DEFINE_LAST_ERROR()
+
+namespace {
+
+using bf16 = __nv_bfloat16;
+
+constexpr int BM = 128;            // tile rows on the A side = TMEM lanes
+constexpr int BK = 64;             // bf16 elements per stage row = one 128-byte swizzle line
+constexpr int UMMA_K = 16;
+constexpr int NUM_THREADS = 192;
+constexpr uint32_t SPIN_LIMIT = 1u << 22;
+
+constexpr int STATUS_TIMEOUT_PRODUCER = 101, STATUS_TIMEOUT_MMA = 102, STATUS_TIMEOUT_EPILOGUE = 103;
+
+// ------------------------------------------------------------------------------------------------ PTX wrappers
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait (non-blocking probes, short sleeps after the first thousand): false if the phase did not complete
+// within the limit, which is of the order of a second.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < SPIN_LIMIT; i++) {
+        if (mbar_test(bar, parity)) return true;
+        if (i > 1024) __nanosleep(64);
+    }
+    return false;
+}
+__device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t slot_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_smem), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// Arrives on the mbarrier once every MMA issued so far by this thread has finished (reading smem, writing TMEM).
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile of 128-byte rows in 128-byte swizzle: groups of 8 rows are
+// 1024 bytes apart (stride byte offset), the leading offset is unused by swizzled K-major layouts, descriptor
+// version 1 (Blackwell), layout type 2 (SWIZZLE_128B). Stepping 16 elements along K adds 32 bytes to the start.
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= uint64_t((smem_addr & 0x3FFFF) >> 4);
+    d |= uint64_t(1) << 16;
+    d |= uint64_t(1024 >> 4) << 32;
+    d |= uint64_t(1) << 46;
+    d |= uint64_t(2) << 61;
+    return d;
+}
+
+// Instruction descriptor for kind::f16: D float (bit 4), A and B bfloat16 (bits 7, 10), both K-major (bits 15, 16
+// clear), N/8 at bit 17, M/16 at bit 24.
+__host__ __device__ constexpr uint32_t make_idesc(int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(n >> 3) << 17) | (uint32_t(BM >> 4) << 24);
+}
+
+struct GemmParams {
+    int64_t rows_a, rows_b, K;           // extents on the 128-row side, the BN side, and the reduction
+    int kb_total, kb_per_split, splits;
+    int swap;                            // 0: A = x (tokens), B = w (features); 1: A = w, B = x
+    int64_t M, N;                        // logical output [M tokens, N features], leading dimension N
+    const float* bias;                   // [N] or null
+    const float* residual;               // [M, N] or null (may alias out)
+    void* out;
+    float* workspace;                    // [splits, tiles, 128, BN] partials (splits > 1)
+    unsigned int* counters;              // [tiles], zero between calls
+    int* status;
+};
+
+template <int BN> struct Cfg {
+    static constexpr int A_BYTES = BM * BK * 2;
+    static constexpr int B_BYTES = BN * BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int STAGES = BN >= 128 ? 3 : (BN >= 64 ? 4 : 5);       // <= ~100 KB: two CTAs per SM
+    static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
+
+template <typename TOut> __device__ __forceinline__ void store_elem(TOut* p, float v);
+template <> __device__ __forceinline__ void store_elem<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void store_elem<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+// Applies bias/residual and stores 16 accumulator values of tile row `r`, tile columns [c0, c0 + 16).
+template <typename TOut>
+__device__ __forceinline__ void epilogue_store(const GemmParams& p, const float* v, int64_t a_row, int64_t b_row0) {
+    TOut* out = reinterpret_cast<TOut*>(p.out);
+    if (p.swap) {
+        // a_row = output feature n; b rows = tokens m. A warp's 32 lanes hold 32 consecutive features of one token.
+        const int64_t n = a_row;
+        if (n >= p.N) return;
+        const float b = p.bias ? p.bias[n] : 0.0f;
+#pragma unroll
+        for (int j = 0; j < 16; j++) {
+            const int64_t m = b_row0 + j;
+            if (m < p.M) {
+                float x = v[j] + b;
+                if (p.residual) x += p.residual[m * p.N + n];
+                store_elem<TOut>(out + m * p.N + n, x);
+            }
+        }
+    } else {
+        const int64_t m = a_row;
+        if (m >= p.M) return;
+        const int64_t n0 = b_row0;
+        if (n0 + 16 <= p.N && (p.N & 7) == 0) {
+            float x[16];
+#pragma unroll
+            for (int j = 0; j < 16; j++) x[j] = v[j] + (p.bias ? p.bias[n0 + j] : 0.0f);
+            if (p.residual) {
+                const float4* r4 = reinterpret_cast<const float4*>(p.residual + m * p.N + n0);
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const float4 r = r4[j];
+                    x[4 * j] += r.x; x[4 * j + 1] += r.y; x[4 * j + 2] += r.z; x[4 * j + 3] += r.w;
+                }
+            }
+            if constexpr (sizeof(TOut) == 4) {
+                float4* o4 = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + m * p.N + n0);
+#pragma unroll
+                for (int j = 0; j < 4; j++) o4[j] = make_float4(x[4 * j], x[4 * j + 1], x[4 * j + 2], x[4 * j + 3]);
+            } else {
+                uint4* o4 = reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(p.out) + m * p.N + n0);
+#pragma unroll
+                for (int j = 0; j < 2; j++) {
+                    __nv_bfloat162 h0 = __floats2bfloat162_rn(x[8 * j], x[8 * j + 1]);
+                    __nv_bfloat162 h1 = __floats2bfloat162_rn(x[8 * j + 2], x[8 * j + 3]);
+                    __nv_bfloat162 h2 = __floats2bfloat162_rn(x[8 * j + 4], x[8 * j + 5]);
+                    __nv_bfloat162 h3 = __floats2bfloat162_rn(x[8 * j + 6], x[8 * j + 7]);
+                    uint4 u;
+                    u.x = *reinterpret_cast<uint32_t*>(&h0); u.y = *reinterpret_cast<uint32_t*>(&h1);
+                    u.z = *reinterpret_cast<uint32_t*>(&h2); u.w = *reinterpret_cast<uint32_t*>(&h3);
+                    o4[j] = u;
+                }
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 16; j++) {
+                const int64_t n = n0 + j;
+                if (n < p.N) {
+                    float x = v[j] + (p.bias ? p.bias[n] : 0.0f);
+                    if (p.residual) x += p.residual[m * p.N + n];
+                    store_elem<TOut>(out + m * p.N + n, x);
+                }
+            }
+        }
+    }
+}
+
+template <int BN, typename TOut>
+__global__ void __launch_bounds__(NUM_THREADS)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const GemmParams p) {
+    using C = Cfg<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    // Operand stages need 1024-byte alignment for the 128-byte swizzle pattern.
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t bars = base + C::STAGES * C::STAGE_BYTES;                  // full[S], empty[S], tmem_full
+    volatile uint32_t* slots = reinterpret_cast<volatile uint32_t*>(base_ptr + C::STAGES * C::STAGE_BYTES + (2 * C::STAGES + 1) * 8);
+    // slots[0] = TMEM base address, slots[1] = abort flag, slots[2] = "this CTA reduces the split-K slices"
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile_a = blockIdx.x, tile_b = blockIdx.y, split = blockIdx.z;
+    const int kb0 = split * p.kb_per_split;
+    const int kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+    const int n_kb = kb1 - kb0;
+
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (C::STAGES + s); };
+    const uint32_t tmem_full_bar = bars + 8u * (2 * C::STAGES);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; s++) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        mbar_init(tmem_full_bar, 1);
+        slots[1] = 0; slots[2] = 0;
+        fence_barrier_init();
+        prefetch_tensormap(&tm_a);
+        prefetch_tensormap(&tm_b);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(const_cast<uint32_t*>(&slots[0])), C::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = slots[0];
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- TMA producer
+        if (lane == 0) {
+            int issued = 0;
+            for (int i = 0; i < n_kb; i++) {
+                const int s = i % C::STAGES;
+                const uint32_t round = i / C::STAGES;
+                if (i >= C::STAGES && !mbar_wait(empty_bar(s), (round - 1) & 1)) {
+                    atomicExch(p.status, STATUS_TIMEOUT_PRODUCER); slots[1] = 1; break;
+                }
+                if (slots[1]) break;
+                const uint32_t a_dst = base + s * C::STAGE_BYTES, b_dst = a_dst + C::A_BYTES;
+                mbar_expect_tx(full_bar(s), C::STAGE_BYTES);
+                tma_load_2d(a_dst, &tm_a, full_bar(s), (kb0 + i) * BK, tile_a * BM);
+                tma_load_2d(b_dst, &tm_b, full_bar(s), (kb0 + i) * BK, tile_b * BN);
+                issued = i + 1;
+            }
+            if (slots[1]) {
+                // Drain: wait (bounded) until every copy this thread started has landed, so that none writes into
+                // shared memory after the CTA is gone.
+                for (int i = max(0, issued - C::STAGES); i < issued; i++) mbar_wait(full_bar(i % C::STAGES), (i / C::STAGES) & 1);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc(BN);
+            for (int i = 0; i < n_kb; i++) {
+                const int s = i % C::STAGES;
+                if (!mbar_wait(full_bar(s), (i / C::STAGES) & 1)) {
+                    atomicExch(p.status, STATUS_TIMEOUT_MMA); slots[1] = 1; break;
+                }
+                tc_fence_after();
+                const uint32_t a_addr = base + s * C::STAGE_BYTES, b_addr = a_addr + C::A_BYTES;
+                const uint64_t a_desc = make_desc(a_addr), b_desc = make_desc(b_addr);
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; k++) {
+                    // 16 elements along K = 32 bytes = 2 units of the descriptor's 16-byte address field
+                    umma_f16(tmem_base, a_desc + uint64_t(2 * k), b_desc + uint64_t(2 * k), idesc, (i > 0 || k > 0) ? 1u : 0u);
+                }
+                umma_commit(empty_bar(s));
+            }
+            umma_commit(tmem_full_bar);
+        }
+    } else {
+        // ---------------------------------------------------------------- epilogue (warps 2..5)
+        const int quad = warp & 3;                                  // this warp may touch TMEM lanes [32 quad, 32 quad + 32)
+        const int r = quad * 32 + lane;                             // tile row
+        const int64_t a_row = int64_t(tile_a) * BM + r;
+        bool ok = mbar_wait(tmem_full_bar, 0);
+        if (!ok) { atomicExch(p.status, STATUS_TIMEOUT_EPILOGUE); slots[1] = 1; }
+        ok = __all_sync(0xffffffffu, ok);
+        tc_fence_after();
+        if (ok) {
+            const int n_tiles = gridDim.x * gridDim.y;
+            const int tile = tile_b * gridDim.x + tile_a;
+            if (p.splits == 1) {
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 16) {
+                    uint32_t raw[16];
+                    tmem_ld16(tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(c), raw);
+                    tmem_ld_wait();
+                    float v[16];
+#pragma unroll
+                    for (int j = 0; j < 16; j++) v[j] = __uint_as_float(raw[j]);
+                    epilogue_store<TOut>(p, v, a_row, int64_t(tile_b) * BN + c);
+                }
+            } else {
+                float* mine = p.workspace + ((int64_t(split) * n_tiles + tile) * BM + r) * BN;
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 16) {
+                    uint32_t raw[16];
+                    tmem_ld16(tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(c), raw);
+                    tmem_ld_wait();
+                    float4* dst = reinterpret_cast<float4*>(mine + c);
+#pragma unroll
+                    for (int j = 0; j < 4; j++)
+                        dst[j] = make_float4(__uint_as_float(raw[4 * j]), __uint_as_float(raw[4 * j + 1]),
+                                             __uint_as_float(raw[4 * j + 2]), __uint_as_float(raw[4 * j + 3]));
+                }
+                __threadfence();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (warp == 2 && lane == 0) {
+                    const unsigned int prev = atomicAdd(p.counters + tile, 1u);
+                    slots[2] = (prev == unsigned(p.splits - 1)) ? 1u : 0u;
+                    if (prev == unsigned(p.splits - 1)) p.counters[tile] = 0;        // ready for the next call
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (slots[2]) {
+                    __threadfence();
+#pragma unroll 1
+                    for (int c = 0; c < BN; c += 16) {
+                        float v[16];
+#pragma unroll
+                        for (int j = 0; j < 16; j++) v[j] = 0.0f;
+                        for (int z = 0; z < p.splits; z++) {
+                            const float4* src = reinterpret_cast<const float4*>(
+                                p.workspace + ((int64_t(z) * n_tiles + tile) * BM + r) * BN + c);
+#pragma unroll
+                            for (int j = 0; j < 4; j++) {
+                                const float4 t = __ldcg(src + j);
+                                v[4 * j] += t.x; v[4 * j + 1] += t.y; v[4 * j + 2] += t.z; v[4 * j + 3] += t.w;
+                            }
+                        }
+                        epilogue_store<TOut>(p, v, a_row, int64_t(tile_b) * BN + c);
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, C::TMEM_COLS);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ host side
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn() {
+    static EncodeFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeFn>(ptr);
+    });
+    return fn;
+}
+
+struct MapKey {
+    const void* ptr; int64_t rows, cols; int box_rows;
+    bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && cols == o.cols && box_rows == o.box_rows; }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        size_t h = std::hash<const void*>()(k.ptr);
+        h ^= std::hash<int64_t>()(k.rows * 1315423911LL + k.cols * 2654435761LL + k.box_rows) + 0x9e3779b97f4a7c15ULL + (h << 6) + (h >> 2);
+        return h;
+    }
+};
+
+// Tensor map of a row-major bf16 matrix [rows, cols] with boxes of box_rows x 64 elements, 128-byte swizzle,
+// zero fill outside. Encoding is pure host arithmetic on (pointer, shape); results are cached.
+int get_map(const void* ptr, int64_t rows, int64_t cols, int box_rows, CUtensorMap* out) {
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    static std::mutex mu;
+    const MapKey key{ptr, rows, cols, box_rows};
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) { *out = it->second; return IB_OK; }
+    EncodeFn fn = encode_fn();
+    if (!fn) return ib::fail(IB_ERR_CUDA, "gemm_tc: cuTensorMapEncodeTiled is not available from this driver");
+    const cuuint64_t dims[2] = {cuuint64_t(cols), cuuint64_t(rows)};
+    const cuuint64_t strides[1] = {cuuint64_t(cols) * 2};
+    const cuuint32_t box[2] = {cuuint32_t(BK), cuuint32_t(box_rows)};
+    const cuuint32_t estr[2] = {1, 1};
+    CUtensorMap m;
+    const CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return ib::fail(IB_ERR_CUDA, "gemm_tc: cuTensorMapEncodeTiled failed with code %d", int(r));
+    if (cache.size() > 8192) cache.clear();
+    cache.emplace(key, m);
+    *out = m;
+    return IB_OK;
+}
+
+template <int BN, typename TOut>
+int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, dim3 grid, cudaStream_t stream) {
+    using C = Cfg<BN>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, TOut>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+        if (e != cudaSuccess) return ib::fail(IB_ERR_CUDA, "gemm_tc: cannot set shared memory size: %s", cudaGetErrorString(e));
+        configured = true;
+    }
+    gemm_tc_kernel<BN, TOut><<<grid, NUM_THREADS, C::SMEM_BYTES, stream>>>(ma, mb, p);
+    return ib::check_launch("gemm_tc");
+}
+
+}  // namespace
+
+// Plans a product: how tokens and features map onto the tile, the BN to use, the number of K slices, and the
+// float workspace and counters it needs. Returns 0, or IB_ERR_ARG if the kernel does not take the sizes.
+IB_EXPORT int ib_gemm_tc_plan(int64_t M, int64_t N, int64_t K, int sm_count, int* swap, int* bn, int* splits,
+                              int64_t* workspace_floats, int64_t* n_counters) {
+    if (M <= 0 || N <= 0 || K <= 0) return ib::fail(IB_ERR_ARG, "gemm_tc: sizes must be positive");
+    if (K % 8) return ib::fail(IB_ERR_ARG, "gemm_tc: K = %lld is not a multiple of 8 (TMA needs a 16-byte row pitch)", (long long)K);
+    if (M >= (1LL << 31) || N >= (1LL << 31) || K >= (1LL << 31)) return ib::fail(IB_ERR_ARG, "gemm_tc: a size exceeds 2^31");
+    const int kb_total = int((K + BK - 1) / BK);
+    *swap = M <= 64 ? 1 : 0;
+    if (*swap) *bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64); else *bn = 128;
+    const int64_t rows_a = *swap ? N : M, rows_b = *swap ? M : N;
+    const int64_t tiles = ((rows_a + BM - 1) / BM) * ((rows_b + *bn - 1) / *bn);
+    if ((rows_b + *bn - 1) / *bn > 65535) return ib::fail(IB_ERR_ARG, "gemm_tc: too many tiles on the grid's second axis");
+    int s = 1;
+    if (sm_count > 0 && tiles < 2 * sm_count) {
+        s = int((2 * sm_count + tiles - 1) / tiles);
+        if (s > 16) s = 16;
+        if (s > kb_total / 2) s = kb_total / 2 > 0 ? kb_total / 2 : 1;    // at least two k-blocks per slice
+    }
+    const int per = (kb_total + s - 1) / s;
+    s = (kb_total + per - 1) / per;
+    *splits = s;
+    *workspace_floats = s > 1 ? int64_t(s) * tiles * BM * (*bn) : 0;
+    *n_counters = s > 1 ? tiles : 0;
+    return IB_OK;
+}
+
+// out[M, N] = x[M, K] . w[N, K]^T (+ bias) (+ residual). x, w bfloat16 with 16-byte aligned bases; out float or
+// bfloat16; bias, residual float. swap/bn/splits come from ib_gemm_tc_plan (or a caller's override within the same
+// rules); workspace holds splits * tiles * 128 * bn floats and counters `tiles` zeroed words when splits > 1.
+// The workspace and counters are shared by every call that passes them: calls on different streams must not overlap.
+IB_EXPORT int ib_gemm_tc(const void* x, const void* w, const float* bias, const float* residual, void* out, int64_t M,
+                         int64_t N, int64_t K, int out_dtype, int swap, int bn, int splits, float* workspace,
+                         unsigned int* counters, int* status, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return IB_OK;
+    if (K <= 0 || K % 8) return ib::fail(IB_ERR_ARG, "gemm_tc: K = %lld must be a positive multiple of 8", (long long)K);
+    if ((uintptr_t(x) & 15) || (uintptr_t(w) & 15)) return ib::fail(IB_ERR_ARG, "gemm_tc: operand bases must be 16-byte aligned");
+    if (bn != 16 && bn != 32 && bn != 64 && bn != 128) return ib::fail(IB_ERR_ARG, "gemm_tc: bn must be 16, 32, 64 or 128");
+    if (!status) return ib::fail(IB_ERR_ARG, "gemm_tc: a status word is required");
+    GemmParams p;
+    p.swap = swap ? 1 : 0;
+    p.M = M; p.N = N; p.K = K;
+    p.rows_a = swap ? N : M;
+    p.rows_b = swap ? M : N;
+    p.kb_total = int((K + BK - 1) / BK);
+    if (splits < 1) splits = 1;
+    if (splits > p.kb_total) splits = p.kb_total;
+    p.kb_per_split = (p.kb_total + splits - 1) / splits;
+    p.splits = (p.kb_total + p.kb_per_split - 1) / p.kb_per_split;
+    if (p.splits > 1 && (!workspace || !counters)) return ib::fail(IB_ERR_ARG, "gemm_tc: split-K needs a workspace and counters");
+    p.bias = bias; p.residual = residual; p.out = out;
+    p.workspace = workspace; p.counters = counters; p.status = status;
+    const dim3 grid{unsigned((p.rows_a + BM - 1) / BM), unsigned((p.rows_b + bn - 1) / bn), unsigned(p.splits)};
+    if (grid.y > 65535) return ib::fail(IB_ERR_ARG, "gemm_tc: too many tiles on the grid's second axis");
+    CUtensorMap ma, mb;
+    int rc = get_map(swap ? w : x, p.rows_a, K, BM, &ma);
+    if (rc) return rc;
+    rc = get_map(swap ? x : w, p.rows_b, K, bn, &mb);
+    if (rc) return rc;
+    const bool f32 = out_dtype == IB_F32;
+    if (!f32 && out_dtype != IB_BF16) return ib::fail(IB_ERR_ARG, "gemm_tc: unknown output dtype %d", out_dtype);
+    switch (bn) {
+        case 16: return f32 ? launch<16, float>(ma, mb, p, grid, stream) : launch<16, bf16>(ma, mb, p, grid, stream);
+        case 32: return f32 ? launch<32, float>(ma, mb, p, grid, stream) : launch<32, bf16>(ma, mb, p, grid, stream);
+        case 64: return f32 ? launch<64, float>(ma, mb, p, grid, stream) : launch<64, bf16>(ma, mb, p, grid, stream);
+        default: return f32 ? launch<128, float>(ma, mb, p, grid, stream) : launch<128, bf16>(ma, mb, p, grid, stream);
+    }
+}

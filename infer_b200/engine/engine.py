@@ -96,7 +96,8 @@ class Engine:
         self.cache = CacheManager(needs, n_pages, page_size, max_requests)
         self.cache.make_storage(dtype, self.rt.device)
         self.cache_views = {cid: self.cache.view(cid) for cid in range(spec.num_caches)}
-        self.status = torch.zeros(1, dtype=torch.int32, device=self.rt.device)
+        from ..fast_ops import device_state
+        self.status = device_state(self.rt.device).status     # shared with the fast kernels of this device
         self.steps_run = 0
 
     # ------------------------------------------------------------------ construction helpers
@@ -221,5 +222,7 @@ class Engine:
         if code:
             self.status.zero_()
             what = {1: "a token id outside the table", 2: "a cache write through an invalid page",
-                    3: "a cache read through an invalid page"}.get(code, f"code {code}")
+                    3: "a cache read through an invalid page", 101: "a tensor-core GEMM's copy wait ran out",
+                    102: "a tensor-core GEMM's operand wait ran out", 103: "a tensor-core GEMM's accumulator wait ran out",
+                    }.get(code, f"code {code}")
             raise RuntimeError(f"device status word was raised: {what}")

@@ -1,0 +1,90 @@
+"""The tcgen05 matrix product alone against the plain kernel (same bfloat16 inputs, float accumulation), at sizes
+that the engine's tests do not use: both tile mappings, K tails, ragged M and N, bias, residual, split-K."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+SIZES = [
+    # (M, N, K)            mapping / what is special
+    (1, 128, 64),          # swap, one k-block
+    (1, 1536, 1536),       # swap, decode of one token
+    (8, 2048, 1536),       # swap, bn 16, split-K
+    (17, 300, 520),        # swap, bn 32, ragged N, K tail (520 = 8*64 + 8)
+    (64, 1536, 8960),      # swap, bn 64, long K, split-K
+    (5, 301, 80),          # swap, odd N (scalar stores), K < 128
+    (65, 96, 224),         # plain, one ragged tile each way, K tail
+    (128, 128, 128),       # plain, exact tiles
+    (300, 1000, 1536),     # plain, ragged M and N
+    (2048, 2048, 1536),    # plain, prefill-sized
+    (130, 301, 96),        # plain, odd N
+    (2, 320, 96),          # swap, K = 1.5 k-blocks
+]
+
+
+def _ref(x, w, bias, residual):
+    from infer_b200 import ops
+    return ops.linear_plain(x, w, bias, residual.clone() if residual is not None else None, torch.float32)
+
+
+@pytest.mark.parametrize("M,N,K", SIZES)
+def test_gemm_tc_matches_plain(M, N, K):
+    from infer_b200 import fast_ops
+    g = torch.Generator(device=DEV).manual_seed(M * 7 + N * 3 + K)
+    x = torch.randn(M, K, device=DEV, generator=g).bfloat16()
+    w = (torch.randn(N, K, device=DEV, generator=g) * 0.05).bfloat16()
+    bias = torch.randn(N, device=DEV, generator=g)
+    res = torch.randn(M, N, device=DEV, generator=g)
+    cond = x.float().abs() @ w.float().abs().T + 1.0
+    st = fast_ops.device_state(DEV)
+    st.status.zero_()
+    for b, r in ((None, None), (bias, None), (bias, res)):
+        ref = _ref(x, w, b, r)
+        got = fast_ops.gemm_tc(x, w, b, r.clone() if r is not None else None, torch.float32)
+        assert got is not None, "the kernel refused sizes it documents as supported"
+        assert st.status.item() == 0
+        err = ((got - ref).abs() / cond).max().item()
+        assert err < 2e-6, f"float output differs: {err:.3e} of the conditioning"
+    low = fast_ops.gemm_tc(x, w, bias, None, torch.bfloat16)
+    assert low.dtype == torch.bfloat16
+    ref16 = _ref(x, w, bias, None)
+    assert ((low.float() - ref16).abs() <= ref16.abs() * 2 ** -8 + 1e-6 * cond).all()
+    # in place over the residual, as the engine calls it
+    r2 = res.clone()
+    same = fast_ops.gemm_tc(x, w, None, r2, torch.float32, out=r2)
+    assert same.data_ptr() == r2.data_ptr()
+    assert ((r2 - _ref(x, w, None, res)).abs() / cond).max().item() < 2e-6
+    assert st.status.item() == 0
+
+
+def test_gemm_tc_repeated_calls_share_the_workspace():
+    """Split-K counters must be back at zero after every call."""
+    from infer_b200 import fast_ops
+    x = torch.randn(8, 1536, device=DEV).bfloat16()
+    w = (torch.randn(1536, 1536, device=DEV) * 0.05).bfloat16()
+    plan = fast_ops.gemm_plan(8, 1536, 1536, fast_ops.device_state(DEV).sm_count)
+    assert plan[0] == 1 and plan[2] > 1
+    first = fast_ops.gemm_tc(x, w, out_dtype=torch.float32)
+    for _ in range(5):
+        assert torch.equal(fast_ops.gemm_tc(x, w, out_dtype=torch.float32), first)     # the same bits every time
+    assert int(fast_ops.device_state(DEV)._counters.abs().sum()) == 0
+
+
+def test_gemm_tc_split_choices_agree():
+    from infer_b200 import fast_ops
+    x = torch.randn(16, 2048, device=DEV).bfloat16()
+    w = (torch.randn(512, 2048, device=DEV) * 0.05).bfloat16()
+    ref = _ref(x, w, None, None)
+    cond = x.float().abs() @ w.float().abs().T + 1.0
+    for splits in (1, 2, 5, 16):
+        plan = (1, 16, splits, splits * 4 * 128 * 16, 4)
+        got = fast_ops.gemm_tc(x, w, out_dtype=torch.float32, plan=plan)
+        assert ((got - ref).abs() / cond).max().item() < 2e-6, splits
+
+
+def test_gemm_tc_refuses_what_it_cannot_do():
+    from infer_b200 import fast_ops
+    x = torch.randn(4, 100, device=DEV).bfloat16()            # K = 100 is not a multiple of 8
+    w = torch.randn(32, 100, device=DEV).bfloat16()
+    assert fast_ops.gemm_tc(x, w) is None
