@@ -1,0 +1,475 @@
+// Attention over the paged bfloat16 cache on tensor cores (mma.sync m16n8k16, float accumulation, online softmax
+// in float), compiled for one head size: -DIB_HEAD_DIM=<multiple of 16, at most 128>. Pages hold 16 positions.
+//
+// Two kernels share one launch call; each segment (a request's tokens in this step) goes to one of them:
+//
+//  decode  (segments of ONE token)   grid (segments, kv heads, splits). The query heads that share a kv head are
+//          the rows of one 16-row tile, so a key or value is read once for the whole group. The key range is cut
+//          into `splits` slices (flash-decoding); inside a CTA each of the 4 warps walks its own pages (a page is a
+//          contiguous 16 x head_dim block per kv head) through a 3-stage cp.async ring, with its own running
+//          maximum, sum and output, merged in shared memory at the end. With more than one slice the CTA stores
+//          (max, sum, unnormalised output) to the workspace, and the CTA that arrives last at the (segment, kv head)
+//          counter adds the slices in ascending order and writes the result.
+//
+//  prefill (segments of 2 or more tokens)   grid (query tiles, heads, segments). 64 queries of one head per CTA,
+//          16 per warp; keys in tiles of 64 (4 pages) aligned to absolute multiples of 64, double-buffered with
+//          cp.async, causal and window masks applied in registers.
+//
+// A key j is visible to the query at position p iff max(0, p - window + 1) <= j <= p (window 0: every j <= p).
+// Rows of keys or values that are not visible and not yet written are zero-filled in shared memory, so stale
+// cache contents can never reach a sum. Page ids outside the pool raise the status word and read as zeros.
+#include "common.cuh"
+
+IB_DEFINE_LAST_ERROR()
+
+#ifndef IB_HEAD_DIM
+#define IB_HEAD_DIM 128
+#endif
+
+namespace {
+
+using bf16 = __nv_bfloat16;
+
+constexpr int HD = IB_HEAD_DIM;
+static_assert(HD % 16 == 0 && HD >= 16 && HD <= 128, "head_dim must be a multiple of 16 in [16, 128]");
+constexpr int PAGE = 16;
+constexpr int ROW_BYTES = HD * 2 + 16;          // padded row: 8 consecutive rows start in 8 different 16-byte bank groups
+constexpr int CHUNKS = HD / 8;                  // 16-byte chunks per row
+constexpr int KS = HD / 16;                     // k-steps over the head dimension
+constexpr float LOG2E = 1.4426950408889634f;
+
+constexpr int DEC_WARPS = 4, DEC_STAGES = 3;
+constexpr int DEC_STAGE_BYTES = 2 * PAGE * ROW_BYTES;                       // K page + V page
+constexpr int DEC_SMEM = DEC_WARPS * DEC_STAGES * DEC_STAGE_BYTES;
+constexpr int DEC_MERGE_BYTES = DEC_WARPS * (16 * HD + 32) * 4;
+static_assert(DEC_MERGE_BYTES <= DEC_SMEM, "merge area must fit the stage area");
+
+constexpr int PF_BM = 64, PF_BN = 64, PF_WARPS = 4;
+constexpr int PF_TILE_BYTES = PF_BN * ROW_BYTES;
+constexpr int PF_SMEM = PF_BM * ROW_BYTES + 2 * 2 * PF_TILE_BYTES;          // Q + 2 stages of (K, V)
+
+struct AttnParams {
+    const bf16* q; const bf16* k_cache; const bf16* v_cache; bf16* out;
+    const int* block_table; int max_blocks;
+    const int* seg_start; const int* seg_pos0;
+    int n_heads, n_kv, group, window;
+    float scale_log2;                      // softmax scale * log2(e)
+    int64_t n_pages;
+    int n_splits;
+    float* workspace; unsigned int* counters; int* status;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
+
+// 16-byte asynchronous copy; src_bytes = 0 writes zeros.
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// Online-softmax update of one 16-row tile held across a warp (rows g and g+8 per thread) with NT score tiles of 8
+// keys each; s holds raw dot products and is replaced by probabilities. `vis(row_half, key_offset)` tells visibility.
+template <int NT, int OT, typename Vis>
+__device__ __forceinline__ void softmax_update(float (*s)[4], float* m, float* l, float (*o)[4], float scale_log2, Vis vis) {
+    const int t4 = (threadIdx.x & 3) * 2;
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int n = 0; n < NT; n++)
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            const int half = e >> 1, key = n * 8 + t4 + (e & 1);
+            s[n][e] = vis(half, key) ? s[n][e] * scale_log2 : -INFINITY;
+            mx[half] = fmaxf(mx[half], s[n][e]);
+        }
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+    }
+    float corr[2], msafe[2];
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        const float m_new = fmaxf(m[h], mx[h]);
+        msafe[h] = m_new == -INFINITY ? 0.0f : m_new;
+        corr[h] = exp2f(m[h] - msafe[h]);                  // m = -inf gives 0
+        m[h] = m_new;
+    }
+    float sum[2] = {0.0f, 0.0f};
+#pragma unroll
+    for (int n = 0; n < NT; n++)
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            const float p = exp2f(s[n][e] - msafe[e >> 1]);
+            s[n][e] = p;
+            sum[e >> 1] += p;
+        }
+#pragma unroll
+    for (int h = 0; h < 2; h++) l[h] = l[h] * corr[h] + sum[h];
+#pragma unroll
+    for (int n = 0; n < OT; n++) {
+        o[n][0] *= corr[0]; o[n][1] *= corr[0];
+        o[n][2] *= corr[1]; o[n][3] *= corr[1];
+    }
+}
+
+// S[16 x 8 NT] += Q[16 x HD] . K^T, K rows (keys) at k_smem with ROW_BYTES pitch; qf = A fragments per k-step.
+template <int NT>
+__device__ __forceinline__ void qk_tile(float (*s)[4], const uint32_t (*qf)[4], uint32_t k_smem) {
+    const int lane = threadIdx.x & 31;
+    const int n_off = (lane & 7) + ((lane >> 4) << 3), k_off = ((lane >> 3) & 1) << 3;
+#pragma unroll
+    for (int ks = 0; ks < KS; ks++)
+#pragma unroll
+        for (int np = 0; np < NT / 2; np++) {
+            uint32_t b0, b1, b2, b3;
+            ldsm_x4(k_smem + (np * 16 + n_off) * ROW_BYTES + (ks * 16 + k_off) * 2, b0, b1, b2, b3);
+            mma_bf16(s[2 * np], qf[ks], b0, b1);
+            mma_bf16(s[2 * np + 1], qf[ks], b2, b3);
+        }
+}
+
+// O[16 x HD] += P[16 x 8 NT] . V, V rows (keys) at v_smem; probabilities in s (C layout) become A fragments.
+template <int NT>
+__device__ __forceinline__ void pv_tile(float (*o)[4], const float (*s)[4], uint32_t v_smem) {
+    const int lane = threadIdx.x & 31;
+    const int key_off = (lane & 7) + (((lane >> 3) & 1) << 3), d_off = (lane >> 4) << 3;
+#pragma unroll
+    for (int kk = 0; kk < NT / 2; kk++) {
+        uint32_t a[4];
+        a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+        a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+        a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+        a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+        for (int j = 0; j < KS; j++) {
+            uint32_t b0, b1, b2, b3;
+            ldsm_x4_trans(v_smem + (kk * 16 + key_off) * ROW_BYTES + (j * 16 + d_off) * 2, b0, b1, b2, b3);
+            mma_bf16(o[2 * j], a, b0, b1);
+            mma_bf16(o[2 * j + 1], a, b2, b3);
+        }
+    }
+}
+
+// ================================================================================================ decode
+
+__global__ void __launch_bounds__(DEC_WARPS * 32)
+attn_decode_kernel(const AttnParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ unsigned int is_last;
+    const int seg = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    const int t = p.seg_start[seg];
+    if (p.seg_start[seg + 1] - t != 1) return;
+    const int pos = p.seg_pos0[seg];
+    const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+    const int first_page = lo / PAGE, last_page = pos / PAGE;
+    const int n_pg = last_page - first_page + 1;
+    const int pps = (n_pg + p.n_splits - 1) / p.n_splits;
+    const int n_eff = (n_pg + pps - 1) / pps;
+    if (split >= n_eff) return;
+    const int pg_begin = first_page + split * pps, pg_end = min(last_page + 1, pg_begin + pps);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t4 = lane & 3;
+    const int* table = p.block_table + int64_t(seg) * p.max_blocks;
+    const int G = p.group;
+
+    // Query fragments straight from global memory: tile row = head within the group, zero beyond it.
+    uint32_t qf[KS][4];
+    {
+        const bf16* qb = p.q + (int64_t(t) * p.n_heads + int64_t(kvh) * G) * HD;
+#pragma unroll
+        for (int ks = 0; ks < KS; ks++) {
+            const int d = ks * 16 + t4 * 2;
+            qf[ks][0] = g < G ? *reinterpret_cast<const uint32_t*>(qb + g * HD + d) : 0u;
+            qf[ks][1] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(qb + (g + 8) * HD + d) : 0u;
+            qf[ks][2] = g < G ? *reinterpret_cast<const uint32_t*>(qb + g * HD + d + 8) : 0u;
+            qf[ks][3] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(qb + (g + 8) * HD + d + 8) : 0u;
+        }
+    }
+    const uint32_t my_smem = smem_u32(smem) + warp * DEC_STAGES * DEC_STAGE_BYTES;
+    const int my_pages = pg_end > pg_begin + warp ? (pg_end - pg_begin - warp + DEC_WARPS - 1) / DEC_WARPS : 0;
+
+    auto issue = [&](int i) {
+        if (i < my_pages) {
+            const int pg = pg_begin + warp + i * DEC_WARPS;
+            int page = table[pg];
+            if (page < 0 || page >= p.n_pages) { atomicExch(p.status, 3); page = -1; }
+            const uint32_t dst = my_smem + (i % DEC_STAGES) * DEC_STAGE_BYTES;
+            const int64_t base = page < 0 ? 0 : ((int64_t(page) * p.n_kv + kvh) * PAGE) * HD;
+#pragma unroll
+            for (int c = lane; c < PAGE * CHUNKS; c += 32) {
+                const int row = c / CHUNKS, col = c % CHUNKS;
+                const int key = pg * PAGE + row;
+                const int bytes = (page >= 0 && key <= pos) ? 16 : 0;          // rows not written yet read as zeros
+                cp_async16(dst + row * ROW_BYTES + col * 16, p.k_cache + base + row * HD + col * 8, bytes);
+                cp_async16(dst + PAGE * ROW_BYTES + row * ROW_BYTES + col * 16, p.v_cache + base + row * HD + col * 8, bytes);
+            }
+        }
+        cp_commit();
+    };
+
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
+    float o[HD / 8][4];
+#pragma unroll
+    for (int n = 0; n < HD / 8; n++) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f;
+
+#pragma unroll
+    for (int i = 0; i < DEC_STAGES - 1; i++) issue(i);
+    for (int i = 0; i < my_pages; i++) {
+        cp_wait<DEC_STAGES - 2>();
+        __syncwarp();
+        const uint32_t k_smem = my_smem + (i % DEC_STAGES) * DEC_STAGE_BYTES, v_smem = k_smem + PAGE * ROW_BYTES;
+        const int key0 = (pg_begin + warp + i * DEC_WARPS) * PAGE;
+        float s[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
+        qk_tile<2>(s, qf, k_smem);
+        softmax_update<2, HD / 8>(s, m, l, o, p.scale_log2, [&](int, int key) { return key0 + key >= lo && key0 + key <= pos; });
+        pv_tile<2>(o, s, v_smem);
+        __syncwarp();
+        issue(i + DEC_STAGES - 1);
+    }
+    cp_wait<0>();
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
+    }
+    __syncthreads();                                     // every warp is done with its stages: reuse them for the merge
+    float* mo = reinterpret_cast<float*>(smem);          // [warp][16][HD]
+    float* mml = mo + DEC_WARPS * 16 * HD;               // [warp][16][2]
+#pragma unroll
+    for (int n = 0; n < HD / 8; n++) {
+        float* b = mo + (warp * 16) * HD + n * 8 + t4 * 2;
+        b[g * HD] = o[n][0]; b[g * HD + 1] = o[n][1];
+        b[(g + 8) * HD] = o[n][2]; b[(g + 8) * HD + 1] = o[n][3];
+    }
+    if (t4 == 0) {
+        mml[(warp * 16 + g) * 2] = m[0]; mml[(warp * 16 + g) * 2 + 1] = l[0];
+        mml[(warp * 16 + g + 8) * 2] = m[1]; mml[(warp * 16 + g + 8) * 2 + 1] = l[1];
+    }
+    __syncthreads();
+    const int64_t unit = int64_t(seg) * p.n_kv + kvh;
+    float* ws_o = p.workspace + (unit * p.n_splits + split) * (16 * HD + 32);
+    float* ws_ml = ws_o + 16 * HD;
+    for (int idx = threadIdx.x; idx < G * HD; idx += DEC_WARPS * 32) {
+        const int row = idx / HD, d = idx - row * HD;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < DEC_WARPS; w++) M = fmaxf(M, mml[(w * 16 + row) * 2]);
+        const float Ms = M == -INFINITY ? 0.0f : M;
+        float L = 0.0f, acc = 0.0f;
+#pragma unroll
+        for (int w = 0; w < DEC_WARPS; w++) {
+            const float f = exp2f(mml[(w * 16 + row) * 2] - Ms);
+            L += mml[(w * 16 + row) * 2 + 1] * f;
+            acc += mo[(w * 16 + row) * HD + d] * f;
+        }
+        if (n_eff == 1) {
+            p.out[(int64_t(t) * p.n_heads + int64_t(kvh) * G + row) * HD + d] = __float2bfloat16_rn(L > 0.0f ? acc / L : 0.0f);
+        } else {
+            ws_o[row * HD + d] = acc;
+            if (d == 0) { ws_ml[row * 2] = M; ws_ml[row * 2 + 1] = L; }
+        }
+    }
+    if (n_eff == 1) return;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned int prev = atomicAdd(p.counters + unit, 1u);
+        is_last = prev == unsigned(n_eff - 1) ? 1u : 0u;
+        if (is_last) p.counters[unit] = 0;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    const float* base = p.workspace + unit * p.n_splits * (16 * HD + 32);
+    for (int idx = threadIdx.x; idx < G * HD; idx += DEC_WARPS * 32) {
+        const int row = idx / HD, d = idx - row * HD;
+        float M = -INFINITY;
+        for (int z = 0; z < n_eff; z++) M = fmaxf(M, __ldcg(base + z * (16 * HD + 32) + 16 * HD + row * 2));
+        const float Ms = M == -INFINITY ? 0.0f : M;
+        float L = 0.0f, acc = 0.0f;
+        for (int z = 0; z < n_eff; z++) {
+            const float* b = base + z * (16 * HD + 32);
+            const float f = exp2f(__ldcg(b + 16 * HD + row * 2) - Ms);
+            L += __ldcg(b + 16 * HD + row * 2 + 1) * f;
+            acc += __ldcg(b + row * HD + d) * f;
+        }
+        p.out[(int64_t(t) * p.n_heads + int64_t(kvh) * G + row) * HD + d] = __float2bfloat16_rn(L > 0.0f ? acc / L : 0.0f);
+    }
+}
+
+// ================================================================================================ prefill
+
+__global__ void __launch_bounds__(PF_WARPS * 32)
+attn_prefill_kernel(const AttnParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int qt = blockIdx.x, h = blockIdx.y, seg = blockIdx.z;
+    const int t0 = p.seg_start[seg];
+    const int q_len = p.seg_start[seg + 1] - t0;
+    if (q_len == 1 || qt * PF_BM >= q_len) return;
+    const int pos0 = p.seg_pos0[seg];
+    const int kvh = h / p.group;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t4 = lane & 3;
+    const int* table = p.block_table + int64_t(seg) * p.max_blocks;
+    const int q_first = pos0 + qt * PF_BM;                                   // position of tile row 0
+    const int q_last = min(pos0 + q_len - 1, q_first + PF_BM - 1);
+    const int lo_key = p.window > 0 ? max(0, q_first - p.window + 1) : 0;
+    const int kt0 = lo_key / PF_BN, kt1 = q_last / PF_BN;
+
+    const uint32_t q_smem = smem_u32(smem);
+    const uint32_t kv_smem = q_smem + PF_BM * ROW_BYTES;
+
+    // Q tile: rows beyond the segment are zero.
+    for (int c = threadIdx.x; c < PF_BM * CHUNKS; c += PF_WARPS * 32) {
+        const int row = c / CHUNKS, col = c % CHUNKS;
+        const int qi = qt * PF_BM + row;
+        const bf16* src = p.q + (int64_t(t0 + min(qi, q_len - 1)) * p.n_heads + h) * HD + col * 8;
+        cp_async16(q_smem + row * ROW_BYTES + col * 16, src, qi < q_len ? 16 : 0);
+    }
+    auto issue = [&](int kt, int stage) {
+        if (kt <= kt1) {
+            const uint32_t k_dst = kv_smem + stage * 2 * PF_TILE_BYTES, v_dst = k_dst + PF_TILE_BYTES;
+            for (int c = threadIdx.x; c < PF_BN * CHUNKS; c += PF_WARPS * 32) {
+                const int row = c / CHUNKS, col = c % CHUNKS;
+                const int key = kt * PF_BN + row;
+                int page = -1;
+                if (key >= (lo_key / PAGE) * PAGE && key <= q_last) {
+                    page = table[key / PAGE];
+                    if (page < 0 || page >= p.n_pages) { atomicExch(p.status, 3); page = -1; }
+                }
+                const int64_t off = page < 0 ? 0 : ((int64_t(page) * p.n_kv + kvh) * PAGE + key % PAGE) * HD + col * 8;
+                const int bytes = page >= 0 ? 16 : 0;
+                cp_async16(k_dst + row * ROW_BYTES + col * 16, p.k_cache + off, bytes);
+                cp_async16(v_dst + row * ROW_BYTES + col * 16, p.v_cache + off, bytes);
+            }
+        }
+        cp_commit();
+    };
+    issue(kt0, 0);                                                            // group 0: Q and the first key tile
+
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
+    float o[HD / 8][4];
+#pragma unroll
+    for (int n = 0; n < HD / 8; n++) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f;
+    const int row_pos[2] = {q_first + warp * 16 + g, q_first + warp * 16 + g + 8};
+    int row_lo[2];
+#pragma unroll
+    for (int hh = 0; hh < 2; hh++) row_lo[hh] = p.window > 0 ? max(0, row_pos[hh] - p.window + 1) : 0;
+    const uint32_t q_warp = q_smem + (warp * 16) * ROW_BYTES;
+    const int a_row = (lane & 7) + (((lane >> 3) & 1) << 3), a_k = (lane >> 4) << 3;
+
+    for (int kt = kt0; kt <= kt1; kt++) {
+        const int stage = (kt - kt0) & 1;
+        issue(kt + 1, stage ^ 1);
+        cp_wait<1>();
+        __syncthreads();
+        const uint32_t k_smem = kv_smem + stage * 2 * PF_TILE_BYTES, v_smem = k_smem + PF_TILE_BYTES;
+        // Skip tiles that lie entirely above this warp's rows (causal) or entirely before their windows.
+        const int warp_last = q_first + warp * 16 + 15, warp_first_lo = p.window > 0 ? max(0, q_first + warp * 16 - p.window + 1) : 0;
+        if (kt * PF_BN <= warp_last && kt * PF_BN + PF_BN - 1 >= warp_first_lo) {
+            float s[PF_BN / 8][4];
+#pragma unroll
+            for (int n = 0; n < PF_BN / 8; n++) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.0f;
+            uint32_t qf[KS][4];
+#pragma unroll
+            for (int ks = 0; ks < KS; ks++)
+                ldsm_x4(q_warp + a_row * ROW_BYTES + (ks * 16 + a_k) * 2, qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3]);
+            qk_tile<PF_BN / 8>(s, qf, k_smem);
+            const int key0 = kt * PF_BN;
+            softmax_update<PF_BN / 8, HD / 8>(s, m, l, o, p.scale_log2, [&](int half, int key) {
+                return key0 + key <= row_pos[half] && key0 + key >= row_lo[half];
+            });
+            pv_tile<PF_BN / 8>(o, s, v_smem);
+        }
+        __syncthreads();
+    }
+    cp_wait<0>();
+#pragma unroll
+    for (int hh = 0; hh < 2; hh++) {
+        l[hh] += __shfl_xor_sync(0xffffffffu, l[hh], 1);
+        l[hh] += __shfl_xor_sync(0xffffffffu, l[hh], 2);
+    }
+#pragma unroll
+    for (int hh = 0; hh < 2; hh++) {
+        const int qi = qt * PF_BM + warp * 16 + g + hh * 8;
+        if (qi >= q_len) continue;
+        const float inv = l[hh] > 0.0f ? 1.0f / l[hh] : 0.0f;
+        bf16* dst = p.out + (int64_t(t0 + qi) * p.n_heads + h) * HD + t4 * 2;
+#pragma unroll
+        for (int n = 0; n < HD / 8; n++)
+            *reinterpret_cast<uint32_t*>(dst + n * 8) = pack_bf16(o[n][hh * 2] * inv, o[n][hh * 2 + 1] * inv);
+    }
+}
+
+}  // namespace
+
+IB_EXPORT int ib_attention_head_dim() { return HD; }
+
+// Floats of workspace and counters a call needs for `n_segments` segments and `n_splits` slices.
+IB_EXPORT int64_t ib_attention_workspace_floats(int64_t n_segments, int n_kv, int n_splits) {
+    return n_segments * n_kv * int64_t(n_splits) * (16 * HD + 32);
+}
+
+// Attention for every segment of a step. q/out [tokens, heads*HD] bfloat16; caches [pages, kv_heads, 16, HD] bfloat16;
+// seg_start [S+1], seg_pos0 [S], block_table [S, max_blocks] int32. has_decode / max_q_len tell which kernels to
+// launch (a kernel skips segments of the other kind). counters: S * kv_heads zeroed words (left zeroed).
+IB_EXPORT int ib_attention_fast(const void* q, const void* k_cache, const void* v_cache, void* out, const int* block_table,
+                                int max_blocks, const int* seg_start, const int* seg_pos0, int n_segments, int n_heads,
+                                int n_kv, int head_dim, int page_size, int window, float scale, int64_t n_pages,
+                                int has_decode, int max_q_len, int n_splits, float* workspace, unsigned int* counters,
+                                int* status, cudaStream_t stream) {
+    if (n_segments <= 0) return IB_OK;
+    if (head_dim != HD) return ib::fail(IB_ERR_ARG, "attention_fast: built for head_dim %d, called with %d", HD, head_dim);
+    if (page_size != PAGE) return ib::fail(IB_ERR_ARG, "attention_fast: pages must hold %d positions, got %d", PAGE, page_size);
+    if (n_kv <= 0 || n_heads % n_kv) return ib::fail(IB_ERR_ARG, "attention_fast: heads %d not a multiple of kv heads %d", n_heads, n_kv);
+    if (n_heads / n_kv > 16) return ib::fail(IB_ERR_ARG, "attention_fast: more than 16 query heads per kv head");
+    if (n_heads > 65535 || n_segments > 65535) return ib::fail(IB_ERR_ARG, "attention_fast: too many heads or segments");
+    if (n_splits < 1) n_splits = 1;
+    if (n_splits > 65535) return ib::fail(IB_ERR_ARG, "attention_fast: too many splits");
+    if (!status) return ib::fail(IB_ERR_ARG, "attention_fast: a status word is required");
+    AttnParams p;
+    p.q = (const bf16*)q; p.k_cache = (const bf16*)k_cache; p.v_cache = (const bf16*)v_cache; p.out = (bf16*)out;
+    p.block_table = block_table; p.max_blocks = max_blocks; p.seg_start = seg_start; p.seg_pos0 = seg_pos0;
+    p.n_heads = n_heads; p.n_kv = n_kv; p.group = n_heads / n_kv; p.window = window;
+    p.scale_log2 = scale * LOG2E; p.n_pages = n_pages; p.n_splits = n_splits;
+    p.workspace = workspace; p.counters = counters; p.status = status;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM);
+        if (e != cudaSuccess) return ib::fail(IB_ERR_CUDA, "attention_fast: cannot set shared memory size: %s", cudaGetErrorString(e));
+        configured = true;
+    }
+    if (has_decode) {
+        if (n_splits > 1 && (!workspace || !counters)) return ib::fail(IB_ERR_ARG, "attention_fast: splits need a workspace and counters");
+        const dim3 grid{unsigned(n_segments), unsigned(n_kv), unsigned(n_splits)};
+        attn_decode_kernel<<<grid, DEC_WARPS * 32, DEC_SMEM, stream>>>(p);
+        int rc = ib::check_launch("attention_fast (decode)");
+        if (rc) return rc;
+    }
+    if (max_q_len > 1) {
+        const dim3 grid{unsigned((max_q_len + PF_BM - 1) / PF_BM), unsigned(n_heads), unsigned(n_segments)};
+        attn_prefill_kernel<<<grid, PF_WARPS * 32, PF_SMEM, stream>>>(p);
+        return ib::check_launch("attention_fast (prefill)");
+    }
+    return IB_OK;
+}

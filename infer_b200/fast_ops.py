@@ -113,8 +113,57 @@ def rope_kv_write(qkv, cos, sin, step, table, cache, n_heads, n_kv, head_dim, wr
     return None
 
 
+def attention_supported(n_heads: int, n_kv: int, head_dim: int, page_size: int) -> bool:
+    return head_dim % 16 == 0 and 16 <= head_dim <= 128 and page_size == 16 and n_heads // n_kv <= 16
+
+
+def attention_fast(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
+                   seg_start: torch.Tensor, seg_pos0: torch.Tensor, n_heads: int, n_kv: int, head_dim: int,
+                   window: Optional[int], scale: float, has_decode: bool, max_q_len: int, max_ctx_len: int,
+                   n_decode: Optional[int] = None, n_splits: Optional[int] = None) -> Optional[torch.Tensor]:
+    """Tensor-core attention of a step's segments over the paged bfloat16 cache; None if the shape is refused.
+    The library is compiled for this head size at first use."""
+    n_pages, ckv, page_size, chd = k_cache.shape
+    if q.dtype != torch.bfloat16 or not attention_supported(n_heads, n_kv, head_dim, page_size):
+        return None
+    _check(q, "q", torch.bfloat16)
+    T = q.shape[0]
+    _check(q, "q", None, (T, n_heads * head_dim))
+    _check(k_cache, "k_cache", torch.bfloat16)
+    _check(v_cache, "v_cache", torch.bfloat16, k_cache.shape)
+    if ckv != n_kv or chd != head_dim:
+        raise KernelError(f"cache shape {tuple(k_cache.shape)} does not match kv_heads={n_kv}, head_dim={head_dim}")
+    S = seg_pos0.numel()
+    _check(seg_start, "seg_start", torch.int32, (S + 1,))
+    _check(seg_pos0, "seg_pos0", torch.int32, (S,))
+    _check(block_table, "block_table", torch.int32)
+    st = device_state(q.device)
+    if n_splits is None:
+        n_splits = 1
+        if has_decode:
+            units = max(1, (n_decode if n_decode is not None else S) * n_kv)
+            visible = min(max_ctx_len, window) if window else max_ctx_len
+            pages = max(1, -(-visible // 16))
+            n_splits = max(1, min(-(-2 * st.sm_count // units), pages // 8, 64))
+    defines = {"IB_HEAD_DIM": head_dim}
+    ws = cnt = None
+    if has_decode and n_splits > 1:
+        ws = st.workspace(S * n_kv * n_splits * (16 * head_dim + 32))
+        cnt = st.counters(S * n_kv)
+    out = torch.empty_like(q)
+    f = _fn("attn", "ib_attention_fast", [c_void_p] * 5 + [c_int] + [c_void_p] * 2 + [c_int] * 6 + [c_float, c_int64] +
+            [c_int] * 3 + [c_void_p] * 4, defines)
+    _call(f, q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), block_table.data_ptr(),
+          block_table.shape[1], seg_start.data_ptr(), seg_pos0.data_ptr(), S, n_heads, n_kv, head_dim, page_size,
+          int(window or 0), float(scale), n_pages, int(has_decode), int(max_q_len), int(n_splits), _ptr(ws), _ptr(cnt),
+          st.status.data_ptr(), _stream())
+    return out
+
+
 def attention(q, cache, table, step, n_heads, n_kv, head_dim, window, scale):
-    return None
+    n_decode = sum(1 for n in step.seg_lens if n == 1)
+    return attention_fast(q, cache.k, cache.v, table, step.seg_start, step.seg_pos0, n_heads, n_kv, head_dim, window,
+                          scale, n_decode > 0, step.max_q_len, step.max_ctx_len, n_decode)
 
 
 def gate_up_swiglu(x, gate_up):

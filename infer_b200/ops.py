@@ -51,14 +51,14 @@ def _check(t: torch.Tensor, name: str, dtype=None, shape=None) -> None:
 _SIGS = {}
 
 
-def _fn(module: str, name: str, argtypes):
-    key = (module, name)
+def _fn(module: str, name: str, argtypes, defines=None, restype=c_int):
+    key = (module, name, tuple(sorted(defines.items())) if defines else None)
     f = _SIGS.get(key)
     if f is None:
-        lib = load_module(module)
+        lib = load_module(module, defines)
         f = getattr(lib, name)
         f.argtypes = argtypes
-        f.restype = c_int
+        f.restype = restype
         f._lib = lib
         _SIGS[key] = f
     return f

@@ -1,0 +1,108 @@
+"""The tensor-core attention kernels alone (flash-decoding with slices, causal prefill tiles) against the plain
+attention formula in float64, on shuffled pages with NaN in every cache row that is not in use."""
+import math
+
+import pytest
+import torch
+
+import plain_model as pm
+from test_kernels_gpu import _paged_setup
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _run(heads, kv, hd, window, segs, n_splits=None, seed=0):
+    """segs: list of (context length before the step, tokens in the step)."""
+    from infer_b200 import fast_ops
+    lens = [c + n for c, n in segs]
+    table, kc, vc, ks, vs = _paged_setup(torch.bfloat16, heads, kv, hd, 16, lens, n_pages=sum(-(-n // 16) for n in lens) + 5, seed=seed)
+    g = torch.Generator().manual_seed(seed + 1)
+    T = sum(n for _, n in segs)
+    q = torch.randn(T, heads, hd, generator=g).bfloat16()
+    seg_start = [0]
+    for _, n in segs:
+        seg_start.append(seg_start[-1] + n)
+    scale = 1 / math.sqrt(hd)
+    ref = torch.zeros(T, heads, hd, dtype=torch.float64)
+    r = 0
+    for s, (c, n) in enumerate(segs):
+        for i in range(n):
+            p = c + i
+            qq = torch.zeros(p + 1, heads, hd, dtype=torch.float64)
+            qq[p] = q[r].double()
+            ref[r] = pm.attention(qq, ks[s][:p + 1].double(), vs[s][:p + 1].double(), window, scale)[p]
+            r += 1
+    st = fast_ops.device_state(DEV)
+    st.status.zero_()
+    out = fast_ops.attention_fast(
+        q.reshape(T, -1).contiguous().to(DEV), kc.to(DEV), vc.to(DEV), table.to(DEV),
+        torch.tensor(seg_start, dtype=torch.int32, device=DEV), torch.tensor([c for c, _ in segs], dtype=torch.int32, device=DEV),
+        heads, kv, hd, window, scale, any(n == 1 for _, n in segs), max(n for _, n in segs), max(lens), n_splits=n_splits)
+    assert out is not None
+    assert st.status.item() == 0
+    got = out.cpu().double().view_as(ref)
+    assert not torch.isnan(got).any(), "a cache row that is not in use reached a sum"
+    err = (got - ref).abs().max().item()
+    assert err < 2e-2, f"max |diff| {err:.4f}"
+    return got
+
+
+LAYOUTS = [(12, 2, 128), (14, 2, 64), (4, 4, 16), (8, 1, 32), (5, 5, 48), (3, 1, 96)]
+
+
+@pytest.mark.parametrize("heads,kv,hd", LAYOUTS)
+@pytest.mark.parametrize("splits", [1, 3, None])
+def test_decode(heads, kv, hd, splits):
+    _run(heads, kv, hd, None, [(0, 1), (1, 1), (15, 1), (16, 1), (255, 1), (1000, 1), (33, 1)], splits)
+
+
+@pytest.mark.parametrize("heads,kv,hd", LAYOUTS)
+def test_decode_with_window(heads, kv, hd):
+    _run(heads, kv, hd, 40, [(0, 1), (38, 1), (39, 1), (40, 1), (41, 1), (500, 1)], 2)
+    _run(heads, kv, hd, 1, [(0, 1), (77, 1)], 1)
+
+
+@pytest.mark.parametrize("heads,kv,hd", LAYOUTS)
+def test_prefill_portions(heads, kv, hd):
+    _run(heads, kv, hd, None, [(0, 2), (0, 64), (0, 65), (7, 130), (300, 17), (63, 2)])
+
+
+@pytest.mark.parametrize("heads,kv,hd", [(12, 2, 128), (5, 5, 48)])
+def test_prefill_with_window(heads, kv, hd):
+    _run(heads, kv, hd, 40, [(0, 100), (90, 70), (39, 3)])
+    _run(heads, kv, hd, 200, [(10, 260)])
+
+
+@pytest.mark.parametrize("heads,kv,hd", [(12, 2, 128), (4, 4, 16)])
+def test_mixed_step(heads, kv, hd):
+    _run(heads, kv, hd, None, [(100, 1), (0, 40), (517, 1), (30, 5), (0, 1)], 2)
+
+
+def test_slice_counts_give_the_same_result():
+    a = _run(12, 2, 128, None, [(2047, 1), (700, 1)], 1, seed=3)
+    for s in (2, 7, 16):
+        b = _run(12, 2, 128, None, [(2047, 1), (700, 1)], s, seed=3)
+        assert (a - b).abs().max() < 1e-2
+
+
+def test_spike_at_a_far_key():
+    """One key far back carries nearly all the weight (first, middle, last position of a long context)."""
+    from infer_b200 import fast_ops
+    hd, n = 64, 1500
+    for spike in (0, 777, n - 1):
+        table, kc, vc, ks, vs = _paged_setup(torch.bfloat16, 1, 1, hd, 16, [n], n_pages=100, seed=spike)
+        q = torch.randn(1, hd).bfloat16()
+        pg, off = int(table[0, spike // 16]), spike % 16
+        kc[pg, 0, off] = (q[0].float() * 3.0).bfloat16()
+        out = fast_ops.attention_fast(q.to(DEV), kc.to(DEV), vc.to(DEV), table.to(DEV), torch.tensor([0, 1], dtype=torch.int32, device=DEV),
+                                      torch.tensor([n - 1], dtype=torch.int32, device=DEV), 1, 1, hd, None, 1 / math.sqrt(hd), True, 1, n, n_splits=4)
+        assert (out.cpu().float() - vs[0][spike].view(1, -1)).abs().max() < 0.25
+
+
+def test_refused_shapes_fall_back():
+    from infer_b200 import fast_ops
+    assert not fast_ops.attention_supported(4, 4, 256, 16)
+    assert not fast_ops.attention_supported(4, 4, 24, 16)
+    assert not fast_ops.attention_supported(4, 4, 64, 32)
+    assert not fast_ops.attention_supported(34, 2, 64, 16)
