@@ -241,6 +241,8 @@ def main():
     ap.add_argument("--layers", type=int, default=CONFIG["num_hidden_layers"])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
+    ap.add_argument("--mode", default="all", choices=["all", "decode", "prefill"],
+                    help="decode / prefill: run only that part and print a short line (for profiling small cases)")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "RyanXiaoo/infer is a C++/CUDA CMake project built for sm_120 "
@@ -258,6 +260,14 @@ def main():
     eng = build_engine(n_layers, 64, args.context, 2 * total_steps + 64)
     cfg = CONFIG
 
+    if args.mode == "decode":
+        ms_step, launches = time_decode(eng, args.batch, args.context, args.steps, args.warmup, ops.kernel_launches)
+        print(json.dumps({"mode": "decode", "batch": args.batch, "ms_per_step": round(ms_step, 4), "gpu_launches": launches}))
+        return 0
+    if args.mode == "prefill":
+        ms_p = time_prefill(eng, 2048, max(1, args.steps), args.warmup)
+        print(json.dumps({"mode": "prefill", "tokens": 2048, "ms": round(ms_p, 3)}))
+        return 0
     clocks = ClockSampler()
     clocks.start()
     ms_step, launches = time_decode(eng, args.batch, args.context, args.steps, args.warmup, ops.kernel_launches)

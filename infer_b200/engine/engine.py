@@ -19,6 +19,7 @@ from typing import Dict, Hashable, List, Mapping, Optional, Sequence
 import numpy as np
 import torch
 
+from .. import ops
 from ..cache.manager import CacheManager
 from ..config.registry import load_config
 from ..config.specs import ModelSpec
@@ -68,13 +69,23 @@ def _round_up(x: int, m: int) -> int:
     return (x + m - 1) // m * m
 
 
+GRAPH_WIDTH_PAGES = 32        # decode-only block tables are padded to a multiple of this many pages (512 positions)
+GRAPH_WARMUP_STEPS = 2        # eager steps of a shape before its graph is captured
+MAX_GRAPHS = 48
+
+
+class _GraphEntry:
+    def __init__(self, static: torch.Tensor):
+        self.static, self.graph, self.logits, self.warm, self.n_launches = static, None, None, 0, 0
+
+
 class Engine:
     """A model, its cache and the step function."""
 
     def __init__(self, spec: ModelSpec, weights: Mapping[str, torch.Tensor], dtype=torch.bfloat16,
                  device="cuda:0", max_tokens: int = 4096, max_requests: int = 8, page_size: int = 16,
                  max_seq_len: Optional[int] = None, kernels: Optional[Dict[str, str]] = None,
-                 cache_budget_bytes: int = 0):
+                 cache_budget_bytes: int = 0, cuda_graphs: bool = True):
         """max_tokens: positions the page pool of every cache group holds (rounded up to whole pages).
         max_requests: live requests (state slots). max_seq_len: longest request (default: the
         smaller of the model's position limit and max_tokens). cache_budget_bytes, if given, replaces max_tokens:
@@ -99,6 +110,10 @@ class Engine:
         from ..fast_ops import device_state
         self.status = device_state(self.rt.device).status     # shared with the fast kernels of this device
         self.steps_run = 0
+        # Decode-only steps of the bfloat16 path are captured into CUDA graphs, one per (batch, wanted rows, table widths).
+        self.use_graphs = bool(cuda_graphs) and dtype == torch.bfloat16
+        self._graphs: Dict[tuple, _GraphEntry] = {}
+        self._graph_pool = torch.cuda.graph_pool_handle() if self.use_graphs else None
 
     # ------------------------------------------------------------------ construction helpers
 
@@ -122,7 +137,10 @@ class Engine:
 
     # ------------------------------------------------------------------ the step
 
-    def _build_context(self, entries: Sequence[StepEntry]) -> StepContext:
+    def _build_context(self, entries: Sequence[StepEntry], graphs: bool = False):
+        """Packs the step's integers on the host and places them on the device. With ``graphs`` and a decode-only
+        step, the integers go into the static buffer of the step's shape (tokens, wanted rows, table widths), whose
+        tensors a captured CUDA graph reads; returns (context, graph entry or None)."""
         V, cache = self.spec.vocab_size, self.cache
         S = len(entries)
         T = sum(len(e.tokens) for e in entries)
@@ -133,7 +151,8 @@ class Engine:
         widths = []
         for gi in range(n_groups):
             w = max(-(-(p + n) // cache.page_size) for p, n in zip(pos0, seg_lens))
-            widths.append(_round_up(max(w, 1), 8))
+            # decode-only steps round the table width up further, so that one captured graph serves many steps
+            widths.append(_round_up(max(w, 1), GRAPH_WIDTH_PAGES if (graphs and T == S) else 8))
         # layout of the packed buffer
         sizes = [T, T, T, S + 1, S, S, max(n_want, 1)] + [S * w for w in widths]
         offs = np.concatenate([[0], np.cumsum([_round_up(s, 4) for s in sizes])])
@@ -173,21 +192,38 @@ class Engine:
             for s, e in enumerate(entries):
                 t = cache.block_table(e.rid, gi)
                 tab[s, :len(t)] = t
-        dev = torch.from_numpy(buf).pin_memory().to(self.rt.device, non_blocking=True)
+        host = torch.from_numpy(buf).pin_memory()
+        entry = None
+        if graphs and T == S:
+            key = (S, n_want, tuple(widths))
+            entry = self._graphs.get(key)
+            if entry is None:
+                if len(self._graphs) >= MAX_GRAPHS:
+                    self._graphs.pop(next(iter(self._graphs)))
+                entry = self._graphs[key] = _GraphEntry(torch.empty(buf.size, dtype=torch.int32, device=self.rt.device))
+            dev = entry.static
+            dev.copy_(host, non_blocking=True)
+        else:
+            dev = host.to(self.rt.device, non_blocking=True)
         self.last_h2d_bytes = buf.nbytes
 
         def cut(i, n):
             return dev[int(offs[i]):int(offs[i]) + n]
-        return StepContext(
+        ctx = StepContext(
             n_tokens=T, n_segments=S, n_want=n_want,
             token_ids=cut(0, T), positions=cut(1, T), token_seg=cut(2, T), seg_start=cut(3, S + 1),
             seg_pos0=cut(4, S), seg_slot=cut(5, S), want_rows=cut(6, n_want),
             block_tables=[cut(7 + gi, S * widths[gi]).view(S, widths[gi]) for gi in range(n_groups)],
             status=self.status, seg_lens=seg_lens, seg_pos0_host=pos0, max_q_len=max(seg_lens),
             max_ctx_len=max(p + n for p, n in zip(pos0, seg_lens)), decode_only=all(n == 1 for n in seg_lens))
+        if entry is not None:
+            # a graph's launch shapes must not depend on the step: bound the context by the table width
+            ctx.max_ctx_len = max(widths) * cache.page_size if widths else ctx.max_ctx_len
+        return ctx, entry
 
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
-        """Runs one batch; returns float32 logits [wanted places, vocab] on the device."""
+        """Runs one batch; returns float32 logits [wanted places, vocab] on the device. With CUDA graphs on, the
+        tensor returned by a decode-only step is reused by the next step of the same shape: read it before."""
         entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
         if not entries:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.rt.device)
@@ -204,13 +240,33 @@ class Engine:
             if not self.cache.reserve(rid, n):
                 raise AssertionError("reserve failed after can_reserve succeeded")
         try:
-            ctx = self._build_context(entries)
+            ctx, entry = self._build_context(entries, self.use_graphs)
         except Exception:
             for rid in rids:
                 self.cache.unreserve(rid)
             raise
         with torch.cuda.device(self.rt.device):
-            logits = self.model.forward(ctx, self.cache_views)
+            if entry is None:
+                logits = self.model.forward(ctx, self.cache_views)
+            elif entry.graph is not None:
+                entry.graph.replay()
+                ops._LAUNCHES[0] += entry.n_launches
+                logits = entry.logits
+            elif entry.warm < GRAPH_WARMUP_STEPS:
+                # The first steps of a shape run eagerly: they build libraries, size workspaces, set attributes.
+                entry.warm += 1
+                logits = self.model.forward(ctx, self.cache_views)
+            else:
+                graph = torch.cuda.CUDAGraph()
+                n0 = ops.kernel_launches()
+                with torch.cuda.graph(graph, pool=self._graph_pool):
+                    entry.logits = self.model.forward(ctx, self.cache_views)
+                entry.n_launches = ops.kernel_launches() - n0        # kernels of this package inside the graph
+                ops._LAUNCHES[0] = n0
+                entry.graph = graph
+                graph.replay()
+                ops._LAUNCHES[0] += entry.n_launches
+                logits = entry.logits
         for rid, n in wanted:
             self.cache.advance(rid, n)
         self.steps_run += 1

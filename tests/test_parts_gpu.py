@@ -31,7 +31,7 @@ def _step(cache, entries):
         if rid not in cache.requests:
             cache.admit(rid)
         assert cache.reserve(rid, n)
-    ctx = eng._build_context([StepEntry(rid, [0] * n, []) for rid, n in entries])
+    ctx, _ = eng._build_context([StepEntry(rid, [0] * n, []) for rid, n in entries])
     return ctx
 
 
