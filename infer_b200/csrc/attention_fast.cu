@@ -39,10 +39,11 @@ constexpr int KS = HD / 16;                     // k-steps over the head dimensi
 constexpr float LOG2E = 1.4426950408889634f;
 
 constexpr int DEC_WARPS = 4, DEC_STAGES = 3;
+constexpr int MAX_SPLITS = 64;                  // slices of the key range per (segment, kv head)
 constexpr int DEC_STAGE_BYTES = 2 * PAGE * ROW_BYTES;                       // K page + V page
 constexpr int DEC_SMEM = DEC_WARPS * DEC_STAGES * DEC_STAGE_BYTES;
 constexpr int DEC_MERGE_BYTES = DEC_WARPS * (16 * HD + 32) * 4;
-static_assert(DEC_MERGE_BYTES <= DEC_SMEM, "merge area must fit the stage area");
+static_assert(DEC_MERGE_BYTES <= DEC_SMEM && 16 * MAX_SPLITS * 4 <= DEC_SMEM, "merge areas must fit the stage area");
 
 constexpr int PF_BM = 64, PF_BN = 64, PF_WARPS = 4;
 constexpr int PF_TILE_BYTES = PF_BN * ROW_BYTES;
@@ -299,20 +300,43 @@ attn_decode_kernel(const AttnParams p) {
     __syncthreads();
     if (!is_last) return;
     __threadfence();
+    // Merge of the slices. Per head of the group one warp reads every slice's (max, sum) at once (lanes = slices),
+    // reduces them with shuffles in a fixed order and leaves the weight of each slice, already divided by the total
+    // sum, in shared memory. Then each thread adds its output element over the slices, eight loads in flight.
     const float* base = p.workspace + unit * p.n_splits * (16 * HD + 32);
+    float* wgt = reinterpret_cast<float*>(smem);                    // [16][MAX_SPLITS]
+    for (int row = warp; row < G; row += DEC_WARPS) {
+        float mz[MAX_SPLITS / 32], lz[MAX_SPLITS / 32], M = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < MAX_SPLITS / 32; i++) {
+            const int z = lane + 32 * i;
+            mz[i] = z < n_eff ? __ldcg(base + z * (16 * HD + 32) + 16 * HD + row * 2) : -INFINITY;
+            lz[i] = z < n_eff ? __ldcg(base + z * (16 * HD + 32) + 16 * HD + row * 2 + 1) : 0.0f;
+            M = fmaxf(M, mz[i]);
+        }
+        M = ib::warp_max(M);
+        const float Ms = M == -INFINITY ? 0.0f : M;
+        float L = 0.0f;
+#pragma unroll
+        for (int i = 0; i < MAX_SPLITS / 32; i++) { mz[i] = exp2f(mz[i] - Ms); L += lz[i] * mz[i]; }
+        L = ib::warp_sum(L);
+        const float inv = L > 0.0f ? 1.0f / L : 0.0f;
+#pragma unroll
+        for (int i = 0; i < MAX_SPLITS / 32; i++) wgt[row * MAX_SPLITS + lane + 32 * i] = mz[i] * inv;
+    }
+    __syncthreads();
     for (int idx = threadIdx.x; idx < G * HD; idx += DEC_WARPS * 32) {
         const int row = idx / HD, d = idx - row * HD;
-        float M = -INFINITY;
-        for (int z = 0; z < n_eff; z++) M = fmaxf(M, __ldcg(base + z * (16 * HD + 32) + 16 * HD + row * 2));
-        const float Ms = M == -INFINITY ? 0.0f : M;
-        float L = 0.0f, acc = 0.0f;
-        for (int z = 0; z < n_eff; z++) {
-            const float* b = base + z * (16 * HD + 32);
-            const float f = exp2f(__ldcg(b + 16 * HD + row * 2) - Ms);
-            L += __ldcg(b + 16 * HD + row * 2 + 1) * f;
-            acc += __ldcg(b + row * HD + d) * f;
+        float acc = 0.0f;
+        for (int z0 = 0; z0 < n_eff; z0 += 8) {
+            float v[8];
+#pragma unroll
+            for (int zz = 0; zz < 8; zz++)
+                v[zz] = z0 + zz < n_eff ? __ldcg(base + (z0 + zz) * (16 * HD + 32) + row * HD + d) : 0.0f;
+#pragma unroll
+            for (int zz = 0; zz < 8; zz++) acc += v[zz] * wgt[row * MAX_SPLITS + min(z0 + zz, MAX_SPLITS - 1)];
         }
-        p.out[(int64_t(t) * p.n_heads + int64_t(kvh) * G + row) * HD + d] = __float2bfloat16_rn(L > 0.0f ? acc / L : 0.0f);
+        p.out[(int64_t(t) * p.n_heads + int64_t(kvh) * G + row) * HD + d] = __float2bfloat16_rn(acc);
     }
 }
 
@@ -444,7 +468,7 @@ IB_EXPORT int ib_attention_fast(const void* q, const void* k_cache, const void* 
     if (n_heads / n_kv > 16) return ib::fail(IB_ERR_ARG, "attention_fast: more than 16 query heads per kv head");
     if (n_heads > 65535 || n_segments > 65535) return ib::fail(IB_ERR_ARG, "attention_fast: too many heads or segments");
     if (n_splits < 1) n_splits = 1;
-    if (n_splits > 65535) return ib::fail(IB_ERR_ARG, "attention_fast: too many splits");
+    if (n_splits > MAX_SPLITS) return ib::fail(IB_ERR_ARG, "attention_fast: at most %d splits", MAX_SPLITS);
     if (!status) return ib::fail(IB_ERR_ARG, "attention_fast: a status word is required");
     AttnParams p;
     p.q = (const bf16*)q; p.k_cache = (const bf16*)k_cache; p.v_cache = (const bf16*)v_cache; p.out = (bf16*)out;

@@ -29,12 +29,13 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", 
 # module name -> source file; headers that every module depends on
 MODULES: Dict[str, str] = {
     "plain": "plain_ops.cu",
-    "fused": "fused_ops.cu",
     "gemv": "gemv.cu",
     "gemm": "gemm_tcgen05.cu",
     "attn": "attention_fast.cu",
 }
 HEADERS = ["common.cuh"]
+# modules that are compiled per model size: the variant that build_all() makes (others are built at first use)
+DEFAULT_DEFINES = {"attn": {"IB_HEAD_DIM": 128}}
 
 
 class BuildError(RuntimeError):
@@ -51,7 +52,19 @@ def _find_nvcc() -> str:
                      "the CUDA kernels of infer_b200 cannot be built and there is no fallback")
 
 
+_BUILD_DIR = None
+_BUILD_DIR_LOCK = threading.Lock()
+
+
 def _build_dir() -> str:
+    global _BUILD_DIR
+    with _BUILD_DIR_LOCK:
+        if _BUILD_DIR is None:
+            _BUILD_DIR = _find_build_dir()
+        return _BUILD_DIR
+
+
+def _find_build_dir() -> str:
     env = os.environ.get("INFER_B200_BUILD_DIR")
     cands = [env] if env else []
     cands.append(os.path.join(HERE, "_build"))
@@ -59,7 +72,7 @@ def _build_dir() -> str:
     for d in cands:
         try:
             os.makedirs(d, exist_ok=True)
-            probe = os.path.join(d, f".w{os.getpid()}")
+            probe = os.path.join(d, f".w{os.getpid()}_{threading.get_ident()}")
             with open(probe, "w"):
                 pass
             os.remove(probe)
@@ -160,6 +173,7 @@ def build_all(modules: Optional[Sequence[str]] = None, verbose: bool = False) ->
     """Compiles every module (in parallel); used by the build check and before GPU runs."""
     from concurrent.futures import ThreadPoolExecutor
     names = [m for m in (modules or MODULES) if os.path.isfile(os.path.join(HERE, MODULES[m]))]
-    with ThreadPoolExecutor(max_workers=min(8, len(names) or 1)) as pool:
-        paths = list(pool.map(lambda m: compile_module(m, None, verbose), names))
+    jobs = [(m, DEFAULT_DEFINES.get(m)) for m in names]
+    with ThreadPoolExecutor(max_workers=min(8, len(jobs) or 1)) as pool:
+        paths = list(pool.map(lambda j: compile_module(j[0], j[1], verbose), jobs))
     return dict(zip(names, paths))

@@ -138,6 +138,7 @@ struct GemmParams {
     int64_t rows_a, rows_b, K;           // extents on the 128-row side, the BN side, and the reduction
     int kb_total, kb_per_split, splits;
     int swap;                            // 0: A = x (tokens), B = w (features); 1: A = w, B = x
+    int epi;                             // 0: bias/residual; 2: SwiGLU over feature rows interleaved by 8 -> [M, N/2]
     int64_t M, N;                        // logical output [M tokens, N features], leading dimension N
     const float* bias;                   // [N] or null
     const float* residual;               // [M, N] or null (may alias out)
@@ -164,6 +165,34 @@ template <> __device__ __forceinline__ void store_elem<bf16>(bf16* p, float v) {
 template <typename TOut>
 __device__ __forceinline__ void epilogue_store(const GemmParams& p, const float* v, int64_t a_row, int64_t b_row0) {
     TOut* out = reinterpret_cast<TOut*>(p.out);
+    if (p.epi == 2) {
+        // Feature rows come in blocks of 16: 8 gate rows, then the 8 matching up rows. out[m, 8 blk + r] = silu(g) * u.
+        const int64_t half = p.N / 2;
+        if (p.swap) {
+            // lanes 0-7 and 16-23 of a warp hold gate rows, lanes 8-15 and 24-31 the matching up rows
+            const int64_t n = a_row;
+            const bool is_gate = (n & 8) == 0;
+#pragma unroll
+            for (int j = 0; j < 16; j++) {
+                const float other = __shfl_xor_sync(0xffffffffu, v[j], 8);
+                const int64_t m = b_row0 + j;
+                if (is_gate && n < p.N && m < p.M) {
+                    const float gte = v[j];
+                    store_elem<TOut>(out + m * half + (n >> 4) * 8 + (n & 7), gte / (1.0f + expf(-gte)) * other);
+                }
+            }
+        } else {
+            const int64_t m = a_row, n0 = b_row0;
+            if (m < p.M && n0 < p.N) {
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    const float gte = v[j];
+                    store_elem<TOut>(out + m * half + (n0 >> 1) + j, gte / (1.0f + expf(-gte)) * v[j + 8]);
+                }
+            }
+        }
+        return;
+    }
     if (p.swap) {
         // a_row = output feature n; b rows = tokens m. A warp's 32 lanes hold 32 consecutive features of one token.
         const int64_t n = a_row;
@@ -360,13 +389,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                         float v[16];
 #pragma unroll
                         for (int j = 0; j < 16; j++) v[j] = 0.0f;
-                        for (int z = 0; z < p.splits; z++) {
-                            const float4* src = reinterpret_cast<const float4*>(
-                                p.workspace + ((int64_t(z) * n_tiles + tile) * BM + r) * BN + c);
+                        // Four slices per round: their 16 loads are in flight together; sums stay in slice order.
+                        for (int z0 = 0; z0 < p.splits; z0 += 4) {
+                            float4 t[4][4];
 #pragma unroll
-                            for (int j = 0; j < 4; j++) {
-                                const float4 t = __ldcg(src + j);
-                                v[4 * j] += t.x; v[4 * j + 1] += t.y; v[4 * j + 2] += t.z; v[4 * j + 3] += t.w;
+                            for (int zz = 0; zz < 4; zz++) {
+                                const int z = min(z0 + zz, p.splits - 1);
+                                const float4* src = reinterpret_cast<const float4*>(
+                                    p.workspace + ((int64_t(z) * n_tiles + tile) * BM + r) * BN + c);
+#pragma unroll
+                                for (int j = 0; j < 4; j++) t[zz][j] = __ldcg(src + j);
+                            }
+#pragma unroll
+                            for (int zz = 0; zz < 4; zz++) {
+                                if (z0 + zz < p.splits) {
+#pragma unroll
+                                    for (int j = 0; j < 4; j++) {
+                                        v[4 * j] += t[zz][j].x; v[4 * j + 1] += t[zz][j].y;
+                                        v[4 * j + 2] += t[zz][j].z; v[4 * j + 3] += t[zz][j].w;
+                                    }
+                                }
                             }
                         }
                         epilogue_store<TOut>(p, v, a_row, int64_t(tile_b) * BN + c);
@@ -482,19 +524,23 @@ IB_EXPORT int ib_gemm_tc_plan(int64_t M, int64_t N, int64_t K, int sm_count, int
     return IB_OK;
 }
 
-// out[M, N] = x[M, K] . w[N, K]^T (+ bias) (+ residual). x, w bfloat16 with 16-byte aligned bases; out float or
+// out[M, N] = x[M, K] . w[N, K]^T (+ bias) (+ residual), or with epi = 2 out[M, N/2] = SwiGLU of feature rows
+// interleaved in blocks of 8 (8 gate rows, then the 8 matching up rows). x, w bfloat16 with 16-byte aligned bases; out float or
 // bfloat16; bias, residual float. swap/bn/splits come from ib_gemm_tc_plan (or a caller's override within the same
 // rules); workspace holds splits * tiles * 128 * bn floats and counters `tiles` zeroed words when splits > 1.
 // The workspace and counters are shared by every call that passes them: calls on different streams must not overlap.
 IB_EXPORT int ib_gemm_tc(const void* x, const void* w, const float* bias, const float* residual, void* out, int64_t M,
-                         int64_t N, int64_t K, int out_dtype, int swap, int bn, int splits, float* workspace,
+                         int64_t N, int64_t K, int out_dtype, int epi, int swap, int bn, int splits, float* workspace,
                          unsigned int* counters, int* status, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return IB_OK;
     if (K <= 0 || K % 8) return ib::fail(IB_ERR_ARG, "gemm_tc: K = %lld must be a positive multiple of 8", (long long)K);
     if ((uintptr_t(x) & 15) || (uintptr_t(w) & 15)) return ib::fail(IB_ERR_ARG, "gemm_tc: operand bases must be 16-byte aligned");
     if (bn != 16 && bn != 32 && bn != 64 && bn != 128) return ib::fail(IB_ERR_ARG, "gemm_tc: bn must be 16, 32, 64 or 128");
     if (!status) return ib::fail(IB_ERR_ARG, "gemm_tc: a status word is required");
+    if (epi != 0 && epi != 2) return ib::fail(IB_ERR_ARG, "gemm_tc: unknown epilogue %d", epi);
+    if (epi == 2 && (N % 16 || bias || residual)) return ib::fail(IB_ERR_ARG, "gemm_tc: the SwiGLU epilogue needs N %% 16 == 0 and no bias or residual");
     GemmParams p;
+    p.epi = epi;
     p.swap = swap ? 1 : 0;
     p.M = M; p.N = N; p.K = K;
     p.rows_a = swap ? N : M;

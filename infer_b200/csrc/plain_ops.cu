@@ -249,14 +249,18 @@ attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T
 }
 
 // ------------------------------------------------------------------------------------------------
-// SwiGLU: out[t, i] = silu(gate) * up, silu(g) = g / (1 + exp(-g)); input rows are [gate | up].
+// SwiGLU: out[t, i] = silu(gate) * up, silu(g) = g / (1 + exp(-g)); input rows are [gate | up], or with
+// `interleave8` blocks of 16: gate features 8b..8b+7, then up features 8b..8b+7.
 template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int64_t n_tokens, int64_t inter) {
+__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int64_t n_tokens, int64_t inter,
+                              int interleave8) {
     const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
     if (i >= n_tokens * inter) return;
     const int64_t t = i / inter, c = i - t * inter;
-    const float g = ib::to_f32(gate_up[t * 2 * inter + c]);
-    const float u = ib::to_f32(gate_up[t * 2 * inter + inter + c]);
+    const int64_t gi = interleave8 ? (c >> 3) * 16 + (c & 7) : c;
+    const int64_t ui = interleave8 ? gi + 8 : inter + c;
+    const float g = ib::to_f32(gate_up[t * 2 * inter + gi]);
+    const float u = ib::to_f32(gate_up[t * 2 * inter + ui]);
     out[i] = ib::from_f32<T>(g / (1.0f + expf(-g)) * u);
 }
 
@@ -492,13 +496,15 @@ IB_EXPORT int ib_attention_plain(const void* q, const void* k_cache, const void*
     return ib::check_launch("ib_attention_plain");
 }
 
-IB_EXPORT int ib_swiglu(const void* gate_up, void* out, int64_t n_tokens, int64_t inter, int dtype, cudaStream_t stream) {
+IB_EXPORT int ib_swiglu(const void* gate_up, void* out, int64_t n_tokens, int64_t inter, int dtype, int interleave8,
+                        cudaStream_t stream) {
     if (n_tokens <= 0 || inter <= 0) return IB_OK;
+    if (interleave8 && inter % 8) return ib::fail(IB_ERR_ARG, "ib_swiglu: interleaved rows need a multiple of 8 features");
     const int64_t n = n_tokens * inter;
     if (dtype == IB_F32)
-        swiglu_kernel<float><<<blocks_for(n, 256), 256, 0, stream>>>((const float*)gate_up, (float*)out, n_tokens, inter);
+        swiglu_kernel<float><<<blocks_for(n, 256), 256, 0, stream>>>((const float*)gate_up, (float*)out, n_tokens, inter, interleave8);
     else if (dtype == IB_BF16)
-        swiglu_kernel<bf16><<<blocks_for(n, 256), 256, 0, stream>>>((const bf16*)gate_up, (bf16*)out, n_tokens, inter);
+        swiglu_kernel<bf16><<<blocks_for(n, 256), 256, 0, stream>>>((const bf16*)gate_up, (bf16*)out, n_tokens, inter, interleave8);
     else
         return ib::fail(IB_ERR_ARG, "ib_swiglu: unknown dtype %d", dtype);
     return ib::check_launch("ib_swiglu");

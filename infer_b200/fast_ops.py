@@ -73,9 +73,11 @@ def gemm_plan(M: int, N: int, K: int, sm_count: int):
 
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None,
-            out_dtype: torch.dtype = torch.bfloat16, out: Optional[torch.Tensor] = None, plan=None) -> Optional[torch.Tensor]:
+            out_dtype: torch.dtype = torch.bfloat16, out: Optional[torch.Tensor] = None, plan=None,
+            swiglu: bool = False) -> Optional[torch.Tensor]:
     """out = x @ w.T (+ bias) (+ residual) on the tcgen05 tensor cores; None if the sizes are refused.
-    x [M, K], w [N, K] bfloat16; bias float32 [N]; residual float32 [M, N] (may be `out`)."""
+    x [M, K], w [N, K] bfloat16; bias float32 [N]; residual float32 [M, N] (may be `out`). With ``swiglu`` the
+    rows of w are gate/up features interleaved in blocks of 8 and the result is silu(gate) * up, [M, N/2]."""
     _check(x, "x", torch.bfloat16)
     _check(w, "w", torch.bfloat16)
     M, K = x.shape
@@ -84,29 +86,67 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = Non
         raise KernelError(f"gemm_tc: x is [{M},{K}] but w is {tuple(w.shape)}")
     st = device_state(x.device)
     plan = plan or gemm_plan(M, N, K, st.sm_count)
-    if plan is None or (x.data_ptr() & 15) or (w.data_ptr() & 15):
+    if plan is None or (x.data_ptr() & 15) or (w.data_ptr() & 15) or (swiglu and N % 16):
         return None
     swap, bn, splits, ws_floats, n_counters = plan
     if bias is not None:
         _check(bias, "bias", torch.float32, (N,))
     if residual is not None:
         _check(residual, "residual", torch.float32, (M, N))
+    n_out = N // 2 if swiglu else N
     if out is None:
-        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+        out = torch.empty((M, n_out), dtype=out_dtype, device=x.device)
     else:
-        _check(out, "out", out_dtype, (M, N))
+        _check(out, "out", out_dtype, (M, n_out))
     ws = st.workspace(ws_floats) if splits > 1 else None
     cnt = st.counters(n_counters) if splits > 1 else None
-    f = _fn("gemm", "ib_gemm_tc", [c_void_p] * 5 + [c_int64] * 3 + [c_int] * 4 + [c_void_p] * 4)
+    f = _fn("gemm", "ib_gemm_tc", [c_void_p] * 5 + [c_int64] * 3 + [c_int] * 5 + [c_void_p] * 4)
     _call(f, x.data_ptr(), w.data_ptr(), _ptr(bias), _ptr(residual), out.data_ptr(), M, N, K, dtype_code(out_dtype),
-          swap, bn, splits, _ptr(ws), _ptr(cnt), st.status.data_ptr(), _stream())
+          2 if swiglu else 0, swap, bn, splits, _ptr(ws), _ptr(cnt), st.status.data_ptr(), _stream())
     return out
 
 
-def linear(x, weight, bias, residual, out_dtype, out):
+SKINNY_MAX_ROWS = 16
+
+
+def linear_skinny(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                  residual: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16,
+                  out: Optional[torch.Tensor] = None, swiglu: bool = False) -> Optional[torch.Tensor]:
+    """The decode kernel: x [M <= 16, K] against w [N, K], weights streamed once; same epilogues as gemm_tc."""
+    _check(x, "x", torch.bfloat16)
+    _check(w, "w", torch.bfloat16)
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K:
+        raise KernelError(f"linear_skinny: x is [{M},{K}] but w is {tuple(w.shape)}")
+    if M > SKINNY_MAX_ROWS or K % 8 or (x.data_ptr() & 15) or (w.data_ptr() & 15) or (swiglu and N % 16):
+        return None
+    if bias is not None:
+        _check(bias, "bias", torch.float32, (N,))
+    if residual is not None:
+        _check(residual, "residual", torch.float32, (M, N))
+        out_dtype = torch.float32
+    n_out = N // 2 if swiglu else N
+    if out is None:
+        out = torch.empty((M, n_out), dtype=out_dtype, device=x.device)
+    else:
+        _check(out, "out", out_dtype, (M, n_out))
+    f = _fn("gemv", "ib_linear_skinny", [c_void_p] * 5 + [c_int64] * 3 + [c_int] * 2 + [c_void_p])
+    _call(f, x.data_ptr(), w.data_ptr(), _ptr(bias), _ptr(residual), out.data_ptr(), M, N, K, dtype_code(out_dtype),
+          2 if swiglu else (1 if residual is not None else 0), _stream())
+    return out
+
+
+def linear(x, weight, bias, residual, out_dtype, out, swiglu=False):
+    """The bfloat16 matrix product of the serving path: the streaming kernel for up to 16 rows, the tcgen05 kernel
+    above that; None if neither takes the shape."""
     if x.dtype != torch.bfloat16:
         return None
-    return gemm_tc(x, weight, bias, residual, out_dtype, out)
+    if x.shape[0] <= SKINNY_MAX_ROWS:
+        y = linear_skinny(x, weight, bias, residual, out_dtype, out, swiglu)
+        if y is not None:
+            return y
+    return gemm_tc(x, weight, bias, residual, out_dtype, out, swiglu=swiglu)
 
 
 def rope_kv_write(qkv, cos, sin, step, table, cache, n_heads, n_kv, head_dim, write_cache):
@@ -144,7 +184,8 @@ def attention_fast(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor
             units = max(1, (n_decode if n_decode is not None else S) * n_kv)
             visible = min(max_ctx_len, window) if window else max_ctx_len
             pages = max(1, -(-visible // 16))
-            n_splits = max(1, min(-(-2 * st.sm_count // units), pages // 8, 64))
+            # enough CTAs for two per SM, but at least 16 pages (4 per warp) in a slice
+            n_splits = max(1, min(-(-2 * st.sm_count // units), pages // 16, 64))
     defines = {"IB_HEAD_DIM": head_dim}
     ws = cnt = None
     if has_decode and n_splits > 1:
@@ -166,5 +207,6 @@ def attention(q, cache, table, step, n_heads, n_kv, head_dim, window, scale):
                           scale, n_decode > 0, step.max_q_len, step.max_ctx_len, n_decode)
 
 
-def gate_up_swiglu(x, gate_up):
-    return None
+def gate_up_swiglu(x, gate_up_weight):
+    """silu(x Wg^T) * (x Wu^T) in one kernel; gate_up_weight rows interleaved in blocks of 8."""
+    return linear(x, gate_up_weight, None, None, torch.bfloat16, None, swiglu=True)

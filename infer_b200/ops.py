@@ -189,15 +189,15 @@ def attention_plain(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     return out
 
 
-def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
-    """rows [gate | up] -> silu(gate) * up."""
+def swiglu(gate_up: torch.Tensor, interleave8: bool = False) -> torch.Tensor:
+    """rows [gate | up] -> silu(gate) * up. With interleave8 the rows are blocks of 8 gate then 8 up features."""
     _check(gate_up, "gate_up")
     T, two_i = gate_up.shape
     if two_i % 2:
         raise KernelError("swiglu input rows must hold gate and up halves")
     out = torch.empty((T, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
-    f = _fn("plain", "ib_swiglu", [c_void_p, c_void_p, c_int64, c_int64, c_int, c_void_p])
-    _call(f, gate_up.data_ptr(), out.data_ptr(), T, two_i // 2, dtype_code(gate_up.dtype), _stream())
+    f = _fn("plain", "ib_swiglu", [c_void_p, c_void_p, c_int64, c_int64, c_int, c_int, c_void_p])
+    _call(f, gate_up.data_ptr(), out.data_ptr(), T, two_i // 2, dtype_code(gate_up.dtype), int(interleave8), _stream())
     return out
 
 

@@ -26,14 +26,23 @@ class SwiGLU(FeedForward):
         return {"gate_proj.weight": (I, H), "up_proj.weight": (I, H), "down_proj.weight": (H, I)}
 
     def load(self, params):
-        self.gate_up = Linear(self.rt, torch.cat([params["gate_proj.weight"], params["up_proj.weight"]], dim=0))
+        g, u = params["gate_proj.weight"], params["up_proj.weight"]
+        # For the fused kernels, gate and up rows alternate in blocks of 8, so that one thread (or two lanes of a
+        # warp) holds a gate value and its up value.
+        self.interleaved = self.rt.dtype == torch.bfloat16 and self.inter % 8 == 0
+        if self.interleaved:
+            w = torch.stack([g.reshape(self.inter // 8, 8, self.hidden), u.reshape(self.inter // 8, 8, self.hidden)], dim=1)
+            w = w.reshape(2 * self.inter, self.hidden)
+        else:
+            w = torch.cat([g, u], dim=0)
+        self.gate_up = Linear(self.rt, w)
         self.down = Linear(self.rt, params["down_proj.weight"])
 
     def forward(self, x, residual):
         act = None
-        if self.rt.fast("swiglu"):
+        if self.interleaved and self.rt.fast("swiglu") and self.rt.fast("linear"):
             from .. import fast_ops
-            act = fast_ops.gate_up_swiglu(x, self.gate_up)
+            act = fast_ops.gate_up_swiglu(x, self.gate_up.weight)
         if act is None:
-            act = ops.swiglu(self.gate_up(x))
+            act = ops.swiglu(self.gate_up(x), self.interleaved)
         return self.down(act, residual=residual)

@@ -88,3 +88,55 @@ def test_gemm_tc_refuses_what_it_cannot_do():
     x = torch.randn(4, 100, device=DEV).bfloat16()            # K = 100 is not a multiple of 8
     w = torch.randn(32, 100, device=DEV).bfloat16()
     assert fast_ops.gemm_tc(x, w) is None
+
+
+SKINNY = [(1, 1536, 1536), (8, 2048, 1536), (8, 1536, 8960), (3, 300, 520), (16, 96, 224), (9, 301, 80), (5, 17, 8),
+          (2, 320, 96), (1, 151936, 64)]
+
+
+@pytest.mark.parametrize("M,N,K", SKINNY)
+def test_skinny_matches_plain(M, N, K):
+    from infer_b200 import fast_ops
+    g = torch.Generator(device=DEV).manual_seed(M + N + K)
+    x = torch.randn(M, K, device=DEV, generator=g).bfloat16()
+    w = (torch.randn(N, K, device=DEV, generator=g) * 0.05).bfloat16()
+    bias = torch.randn(N, device=DEV, generator=g)
+    res = torch.randn(M, N, device=DEV, generator=g)
+    cond = x.float().abs() @ w.float().abs().T + 1.0
+    for b, r in ((None, None), (bias, None), (bias, res), (None, res)):
+        ref = _ref(x, w, b, r)
+        got = fast_ops.linear_skinny(x, w, b, r.clone() if r is not None else None, torch.float32)
+        assert got is not None
+        assert ((got - ref).abs() / cond).max().item() < 2e-6
+    low = fast_ops.linear_skinny(x, w, bias, None, torch.bfloat16)
+    ref16 = _ref(x, w, bias, None)
+    assert ((low.float() - ref16).abs() <= ref16.abs() * 2 ** -8 + 1e-6 * cond).all()
+    r2 = res.clone()
+    fast_ops.linear_skinny(x, w, None, r2, out=r2)
+    assert ((r2 - _ref(x, w, None, res)).abs() / cond).max().item() < 2e-6
+    # rows of the result do not depend on how many rows there are
+    one = fast_ops.linear_skinny(x[:1].contiguous(), w, bias, None, torch.float32)
+    assert torch.equal(one, fast_ops.linear_skinny(x, w, bias, None, torch.float32)[:1])
+
+
+@pytest.mark.parametrize("M", [1, 8, 13, 40, 64, 200])
+@pytest.mark.parametrize("I,H", [(8960, 1536), (224, 96), (176, 80)])
+def test_fused_swiglu_matches_the_two_kernels(M, I, H):
+    """gate/up product with the SwiGLU epilogue (rows interleaved in blocks of 8) against plain product + plain SwiGLU,
+    through all three kernels: streaming (M <= 16), tcgen05 swapped (M <= 64), tcgen05 plain."""
+    from infer_b200 import fast_ops, ops
+    g = torch.Generator(device=DEV).manual_seed(M + I)
+    x = torch.randn(M, H, device=DEV, generator=g).bfloat16()
+    wg = (torch.randn(I, H, device=DEV, generator=g) * 0.1).bfloat16()
+    wu = (torch.randn(I, H, device=DEV, generator=g) * 0.1).bfloat16()
+    w_il = torch.stack([wg.view(I // 8, 8, H), wu.view(I // 8, 8, H)], 1).reshape(2 * I, H).contiguous()
+    gate = ops.linear_plain(x, wg, out_dtype=torch.float32)
+    up = ops.linear_plain(x, wu, out_dtype=torch.float32)
+    ref = gate / (1 + torch.exp(-gate)) * up
+    two = ops.swiglu(ops.linear_plain(x, w_il), interleave8=True)                       # plain kernels, interleaved rows
+    assert (two.float() - ref).abs().max() < 0.05 * ref.abs().max() + 1e-3
+    for fn in ([fast_ops.linear_skinny] if M <= 16 else []) + [fast_ops.gemm_tc]:
+        got = fn(x, w_il, out_dtype=torch.bfloat16, swiglu=True)
+        assert got is not None and got.shape == (M, I)
+        assert ((got.float() - ref).abs() <= ref.abs() * 2 ** -7 + 1e-4 * ref.abs().max()).all(), fn.__name__
+    assert fast_ops.device_state(DEV).status.item() == 0
