@@ -176,6 +176,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32)
 attn_decode_kernel(const AttnParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ unsigned int is_last;
+    ib::pdl_wait();
     const int seg = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
     const int t = p.seg_start[seg];
     if (p.seg_start[seg + 1] - t != 1) return;
@@ -247,6 +248,7 @@ attn_decode_kernel(const AttnParams p) {
         issue(i + DEC_STAGES - 1);
     }
     cp_wait<0>();
+    ib::pdl_launch_dependents();
 #pragma unroll
     for (int h = 0; h < 2; h++) {
         l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
@@ -345,6 +347,7 @@ attn_decode_kernel(const AttnParams p) {
 __global__ void __launch_bounds__(PF_WARPS * 32)
 attn_prefill_kernel(const AttnParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
+    ib::pdl_wait();
     const int qt = blockIdx.x, h = blockIdx.y, seg = blockIdx.z;
     const int t0 = p.seg_start[seg];
     const int q_len = p.seg_start[seg + 1] - t0;
@@ -427,6 +430,7 @@ attn_prefill_kernel(const AttnParams p) {
         __syncthreads();
     }
     cp_wait<0>();
+    ib::pdl_launch_dependents();
 #pragma unroll
     for (int hh = 0; hh < 2; hh++) {
         l[hh] += __shfl_xor_sync(0xffffffffu, l[hh], 1);
@@ -486,14 +490,12 @@ IB_EXPORT int ib_attention_fast(const void* q, const void* k_cache, const void* 
     if (has_decode) {
         if (n_splits > 1 && (!workspace || !counters)) return ib::fail(IB_ERR_ARG, "attention_fast: splits need a workspace and counters");
         const dim3 grid{unsigned(n_segments), unsigned(n_kv), unsigned(n_splits)};
-        attn_decode_kernel<<<grid, DEC_WARPS * 32, DEC_SMEM, stream>>>(p);
-        int rc = ib::check_launch("attention_fast (decode)");
+        int rc = ib::launch("attention_fast (decode)", attn_decode_kernel, grid, dim3(DEC_WARPS * 32), size_t(DEC_SMEM), stream, 1u, p);
         if (rc) return rc;
     }
     if (max_q_len > 1) {
         const dim3 grid{unsigned((max_q_len + PF_BM - 1) / PF_BM), unsigned(n_heads), unsigned(n_segments)};
-        attn_prefill_kernel<<<grid, PF_WARPS * 32, PF_SMEM, stream>>>(p);
-        return ib::check_launch("attention_fast (prefill)");
+        return ib::launch("attention_fast (prefill)", attn_prefill_kernel, grid, dim3(PF_WARPS * 32), size_t(PF_SMEM), stream, 1u, p);
     }
     return IB_OK;
 }

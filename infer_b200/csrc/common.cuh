@@ -41,6 +41,51 @@ inline int check_launch(const char* what) {
     return IB_OK;
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Programmatic dependent launch. Every kernel of this library is launched with the "programmatic stream
+// serialization" attribute: it may be scheduled while its predecessor in the stream is still draining, and runs its
+// own set-up (and, in the streaming kernels, its first weight loads, which no predecessor writes) before pdl_wait(),
+// which returns once every predecessor grid has completed and its writes are visible. A kernel therefore touches
+// nothing that a predecessor may read or write before pdl_wait(). pdl_launch_dependents() lets the successor be
+// scheduled once all CTAs of this grid have passed it; a kernel that never calls it releases the successor at exit.
+// Inside a captured CUDA graph the attribute becomes a programmatic edge between the kernel nodes.
+inline bool& pdl_enabled() {
+    static bool enabled = true;
+    return enabled;
+}
+
+template <typename... KArgs, typename... Args>
+inline int launch(const char* what, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                  unsigned cluster_x, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attrs[2];
+    unsigned n = 0;
+    if (pdl_enabled()) {
+        attrs[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attrs[n].val.programmaticStreamSerializationAllowed = 1;
+        n++;
+    }
+    if (cluster_x > 1) {
+        attrs[n].id = cudaLaunchAttributeClusterDimension;
+        attrs[n].val.clusterDim.x = cluster_x;
+        attrs[n].val.clusterDim.y = 1;
+        attrs[n].val.clusterDim.z = 1;
+        n++;
+    }
+    cfg.attrs = attrs;
+    cfg.numAttrs = n;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+    if (e != cudaSuccess) return fail(IB_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+    return IB_OK;
+}
+
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 template <typename T> __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
@@ -89,4 +134,5 @@ __device__ __forceinline__ float block_max(float v, float* red) {
 #define IB_EXPORT extern "C" __attribute__((visibility("default")))
 
 #define IB_DEFINE_LAST_ERROR() \
-    IB_EXPORT const char* ib_last_error() { return ib::error_buffer(); }
+    IB_EXPORT const char* ib_last_error() { return ib::error_buffer(); } \
+    IB_EXPORT void ib_set_pdl(int on) { ib::pdl_enabled() = on != 0; }

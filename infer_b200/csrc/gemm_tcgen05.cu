@@ -293,9 +293,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = slots[0];
+    ib::pdl_wait();                       // set-up above overlapped the predecessor; operands are touched from here on
 
     if (warp == 0) {
         // ---------------------------------------------------------------- TMA producer
+        if (lane != 0) ib::pdl_launch_dependents();
         if (lane == 0) {
             int issued = 0;
             for (int i = 0; i < n_kb; i++) {
@@ -338,6 +340,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             }
             umma_commit(tmem_full_bar);
         }
+        ib::pdl_launch_dependents();
     } else {
         // ---------------------------------------------------------------- epilogue (warps 2..5)
         const int quad = warp & 3;                                  // this warp may touch TMEM lanes [32 quad, 32 quad + 32)
@@ -362,17 +365,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     epilogue_store<TOut>(p, v, a_row, int64_t(tile_b) * BN + c);
                 }
             } else {
-                float* mine = p.workspace + ((int64_t(split) * n_tiles + tile) * BM + r) * BN;
+                // Slices are stored column-major within the tile (element (r, col) at col * 128 + r), so that the 32 lanes
+                // of a warp, which hold 32 consecutive rows, write and later read 128 contiguous bytes per column.
+                float* mine = p.workspace + (int64_t(split) * n_tiles + tile) * (BM * BN) + r;
 #pragma unroll 1
                 for (int c = 0; c < BN; c += 16) {
                     uint32_t raw[16];
                     tmem_ld16(tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(c), raw);
                     tmem_ld_wait();
-                    float4* dst = reinterpret_cast<float4*>(mine + c);
 #pragma unroll
-                    for (int j = 0; j < 4; j++)
-                        dst[j] = make_float4(__uint_as_float(raw[4 * j]), __uint_as_float(raw[4 * j + 1]),
-                                             __uint_as_float(raw[4 * j + 2]), __uint_as_float(raw[4 * j + 3]));
+                    for (int j = 0; j < 16; j++) mine[(c + j) * BM] = __uint_as_float(raw[j]);
                 }
                 __threadfence();
                 asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -389,27 +391,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                         float v[16];
 #pragma unroll
                         for (int j = 0; j < 16; j++) v[j] = 0.0f;
-                        // Four slices per round: their 16 loads are in flight together; sums stay in slice order.
-                        for (int z0 = 0; z0 < p.splits; z0 += 4) {
-                            float4 t[4][4];
+                        // Slices are added in ascending order; the 16 loads of a slice are in flight together, and the
+                        // next slice's loads are issued before the current one is added.
+                        const float* src = p.workspace + int64_t(tile) * (BM * BN) + int64_t(c) * BM + r;
+                        const int64_t zstride = int64_t(n_tiles) * (BM * BN);
+                        float cur[16], nxt[16];
 #pragma unroll
-                            for (int zz = 0; zz < 4; zz++) {
-                                const int z = min(z0 + zz, p.splits - 1);
-                                const float4* src = reinterpret_cast<const float4*>(
-                                    p.workspace + ((int64_t(z) * n_tiles + tile) * BM + r) * BN + c);
+                        for (int j = 0; j < 16; j++) cur[j] = __ldcg(src + j * BM);
+                        for (int z = 0; z < p.splits; z++) {
+                            if (z + 1 < p.splits) {
 #pragma unroll
-                                for (int j = 0; j < 4; j++) t[zz][j] = __ldcg(src + j);
+                                for (int j = 0; j < 16; j++) nxt[j] = __ldcg(src + (z + 1) * zstride + j * BM);
                             }
 #pragma unroll
-                            for (int zz = 0; zz < 4; zz++) {
-                                if (z0 + zz < p.splits) {
-#pragma unroll
-                                    for (int j = 0; j < 4; j++) {
-                                        v[4 * j] += t[zz][j].x; v[4 * j + 1] += t[zz][j].y;
-                                        v[4 * j + 2] += t[zz][j].z; v[4 * j + 3] += t[zz][j].w;
-                                    }
-                                }
-                            }
+                            for (int j = 0; j < 16; j++) { v[j] += cur[j]; cur[j] = nxt[j]; }
                         }
                         epilogue_store<TOut>(p, v, a_row, int64_t(tile_b) * BN + c);
                     }
@@ -491,8 +486,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, di
         if (e != cudaSuccess) return ib::fail(IB_ERR_CUDA, "gemm_tc: cannot set shared memory size: %s", cudaGetErrorString(e));
         configured = true;
     }
-    gemm_tc_kernel<BN, TOut><<<grid, NUM_THREADS, C::SMEM_BYTES, stream>>>(ma, mb, p);
-    return ib::check_launch("gemm_tc");
+    return ib::launch("gemm_tc", gemm_tc_kernel<BN, TOut>, grid, dim3(NUM_THREADS), size_t(C::SMEM_BYTES), stream, 1u, ma, mb, p);
 }
 
 }  // namespace
@@ -510,11 +504,12 @@ IB_EXPORT int ib_gemm_tc_plan(int64_t M, int64_t N, int64_t K, int sm_count, int
     const int64_t rows_a = *swap ? N : M, rows_b = *swap ? M : N;
     const int64_t tiles = ((rows_a + BM - 1) / BM) * ((rows_b + *bn - 1) / *bn);
     if ((rows_b + *bn - 1) / *bn > 65535) return ib::fail(IB_ERR_ARG, "gemm_tc: too many tiles on the grid's second axis");
+    // Slices of K only when the tiles alone leave most of the GPU idle; each slice keeps at least four k-blocks.
     int s = 1;
-    if (sm_count > 0 && tiles < 2 * sm_count) {
-        s = int((2 * sm_count + tiles - 1) / tiles);
+    if (sm_count > 0 && tiles * 2 < sm_count) {
+        s = int((sm_count + tiles - 1) / tiles);
         if (s > 16) s = 16;
-        if (s > kb_total / 2) s = kb_total / 2 > 0 ? kb_total / 2 : 1;    // at least two k-blocks per slice
+        if (s > kb_total / 4) s = kb_total / 4 > 0 ? kb_total / 4 : 1;
     }
     const int per = (kb_total + s - 1) / s;
     s = (kb_total + per - 1) / per;

@@ -17,6 +17,13 @@
 
 IB_DEFINE_LAST_ERROR()
 
+// Launch on `stream` with the library's launch attributes; a failure returns from the calling entry point.
+#define IB_LAUNCH(kernel, grid, block, smem, ...)                                                              \
+    do {                                                                                                       \
+        const int rc_ = ib::launch(#kernel, kernel, dim3(grid), dim3(block), size_t(smem), stream, 1u, __VA_ARGS__); \
+        if (rc_) return rc_;                                                                                   \
+    } while (0)
+
 namespace {
 
 using bf16 = __nv_bfloat16;
@@ -27,6 +34,7 @@ using bf16 = __nv_bfloat16;
 template <typename T>
 __global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids, int64_t n_tokens,
                                  int64_t hidden, int64_t vocab, float* __restrict__ out, int* status) {
+    ib::pdl_wait();
     const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
     if (i >= n_tokens * hidden) return;
     const int64_t t = i / hidden, c = i - t * hidden;
@@ -45,6 +53,7 @@ __global__ void embedding_kernel(const T* __restrict__ table, const int* __restr
 template <typename TOut>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, float eps, int64_t hidden,
                                const int* __restrict__ rows, TOut* __restrict__ out) {
+    ib::pdl_wait();
     __shared__ float red[32];
     const int64_t r_out = blockIdx.x;
     const int64_t r_in = rows ? rows[r_out] : r_out;
@@ -70,6 +79,7 @@ template <typename TIn, typename TOut>
 __global__ void __launch_bounds__(256)
 linear_kernel(const TIn* __restrict__ x, const TIn* __restrict__ w, const float* __restrict__ bias,
               const float* residual, TOut* out, int64_t M, int64_t N, int64_t K) {
+    ib::pdl_wait();
     __shared__ float xs[LK][LT + 1];
     __shared__ float ws[LK][LT + 1];
     const int tid = threadIdx.x;
@@ -136,6 +146,7 @@ __global__ void rope_kv_write_kernel(const T* __restrict__ qkv, const float* __r
                                      int64_t max_blocks, T* __restrict__ q_out, T* __restrict__ k_cache,
                                      T* __restrict__ v_cache, int64_t n_tokens, int n_heads, int n_kv, int head_dim,
                                      int page_size, int write_cache, int64_t n_pages, int* status) {
+    ib::pdl_wait();
     const int half = head_dim / 2;
     const int units = (n_heads + 2 * n_kv) * half;   // one unit = one (head, j) pair
     const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -187,6 +198,7 @@ attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T
                  const int* __restrict__ block_table, int64_t max_blocks, const int* __restrict__ token_seg,
                  const int* __restrict__ positions, T* __restrict__ out, int n_heads, int n_kv, int head_dim,
                  int page_size, int window, float scale, int64_t n_pages, int* status) {
+    ib::pdl_wait();
     extern __shared__ float smem[];
     float* qs = smem;                      // [head_dim]
     float* ps = qs + head_dim;             // [AT]
@@ -254,6 +266,7 @@ attention_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int64_t n_tokens, int64_t inter,
                               int interleave8) {
+    ib::pdl_wait();
     const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
     if (i >= n_tokens * inter) return;
     const int64_t t = i / inter, c = i - t * inter;
@@ -283,6 +296,7 @@ __device__ __forceinline__ float hash_uniform(uint64_t seed, uint64_t step, uint
 __global__ void sample_kernel(const float* __restrict__ logits, int64_t vocab, const float* __restrict__ temperature,
                               const int64_t* __restrict__ seed, const int64_t* __restrict__ step,
                               int* __restrict__ out) {
+    ib::pdl_wait();
     __shared__ float sv[256];
     __shared__ int si[256];
     const int b = blockIdx.x;
@@ -325,6 +339,7 @@ __global__ void __launch_bounds__(1024)
 sample_filtered_kernel(const float* __restrict__ logits, int64_t vocab, const float* __restrict__ temperature,
                        const int64_t* __restrict__ seed, const int64_t* __restrict__ step,
                        const int64_t* __restrict__ top_k, const float* __restrict__ top_p, int* __restrict__ out) {
+    ib::pdl_wait();
     __shared__ float red[32];
     __shared__ float sv[1024];
     __shared__ int si[1024];
@@ -413,9 +428,9 @@ IB_EXPORT int ib_embedding(const void* table, int table_dtype, const int* ids, i
     if (n_tokens <= 0) return IB_OK;
     const int64_t n = n_tokens * hidden;
     if (table_dtype == IB_F32)
-        embedding_kernel<float><<<blocks_for(n, 256), 256, 0, stream>>>((const float*)table, ids, n_tokens, hidden, vocab, out, status);
+        IB_LAUNCH(embedding_kernel<float>, blocks_for(n, 256), 256, 0, (const float*)table, ids, n_tokens, hidden, vocab, out, status);
     else if (table_dtype == IB_BF16)
-        embedding_kernel<bf16><<<blocks_for(n, 256), 256, 0, stream>>>((const bf16*)table, ids, n_tokens, hidden, vocab, out, status);
+        IB_LAUNCH(embedding_kernel<bf16>, blocks_for(n, 256), 256, 0, (const bf16*)table, ids, n_tokens, hidden, vocab, out, status);
     else
         return ib::fail(IB_ERR_ARG, "ib_embedding: unknown table dtype %d", table_dtype);
     return ib::check_launch("ib_embedding");
@@ -427,9 +442,9 @@ IB_EXPORT int ib_rmsnorm(const float* x, const float* w, float eps, int64_t n_ro
     if (hidden <= 0) return ib::fail(IB_ERR_ARG, "ib_rmsnorm: hidden must be positive");
     const int threads = hidden >= 1024 ? 256 : 128;
     if (out_dtype == IB_F32)
-        rmsnorm_kernel<float><<<unsigned(n_rows), threads, 0, stream>>>(x, w, eps, hidden, rows, (float*)out);
+        IB_LAUNCH(rmsnorm_kernel<float>, unsigned(n_rows), threads, 0, x, w, eps, hidden, rows, (float*)out);
     else if (out_dtype == IB_BF16)
-        rmsnorm_kernel<bf16><<<unsigned(n_rows), threads, 0, stream>>>(x, w, eps, hidden, rows, (bf16*)out);
+        IB_LAUNCH(rmsnorm_kernel<bf16>, unsigned(n_rows), threads, 0, x, w, eps, hidden, rows, (bf16*)out);
     else
         return ib::fail(IB_ERR_ARG, "ib_rmsnorm: unknown output dtype %d", out_dtype);
     return ib::check_launch("ib_rmsnorm");
@@ -442,11 +457,11 @@ IB_EXPORT int ib_linear_plain(const void* x, const void* w, const float* bias, c
     const dim3 grid{unsigned((N + LT - 1) / LT), unsigned((M + LT - 1) / LT), 1u};
     if (grid.y > 65535) return ib::fail(IB_ERR_ARG, "ib_linear_plain: too many rows (%lld)", (long long)M);
     if (in_dtype == IB_F32 && out_dtype == IB_F32)
-        linear_kernel<float, float><<<grid, 256, 0, stream>>>((const float*)x, (const float*)w, bias, residual, (float*)out, M, N, K);
+        IB_LAUNCH((linear_kernel<float, float>), grid, 256, 0, (const float*)x, (const float*)w, bias, residual, (float*)out, M, N, K);
     else if (in_dtype == IB_BF16 && out_dtype == IB_BF16)
-        linear_kernel<bf16, bf16><<<grid, 256, 0, stream>>>((const bf16*)x, (const bf16*)w, bias, residual, (bf16*)out, M, N, K);
+        IB_LAUNCH((linear_kernel<bf16, bf16>), grid, 256, 0, (const bf16*)x, (const bf16*)w, bias, residual, (bf16*)out, M, N, K);
     else if (in_dtype == IB_BF16 && out_dtype == IB_F32)
-        linear_kernel<bf16, float><<<grid, 256, 0, stream>>>((const bf16*)x, (const bf16*)w, bias, residual, (float*)out, M, N, K);
+        IB_LAUNCH((linear_kernel<bf16, float>), grid, 256, 0, (const bf16*)x, (const bf16*)w, bias, residual, (float*)out, M, N, K);
     else
         return ib::fail(IB_ERR_ARG, "ib_linear_plain: unsupported dtypes in=%d out=%d", in_dtype, out_dtype);
     return ib::check_launch("ib_linear_plain");
@@ -462,12 +477,10 @@ IB_EXPORT int ib_rope_kv_write(const void* qkv, const float* cos_t, const float*
     if (n_heads <= 0 || n_kv <= 0 || page_size <= 0) return ib::fail(IB_ERR_ARG, "ib_rope_kv_write: bad sizes");
     const int64_t n = n_tokens * (n_heads + 2 * n_kv) * (head_dim / 2);
     if (dtype == IB_F32)
-        rope_kv_write_kernel<float><<<blocks_for(n, 256), 256, 0, stream>>>(
-            (const float*)qkv, cos_t, sin_t, positions, token_seg, block_table, max_blocks, (float*)q_out,
+        IB_LAUNCH(rope_kv_write_kernel<float>, blocks_for(n, 256), 256, 0, (const float*)qkv, cos_t, sin_t, positions, token_seg, block_table, max_blocks, (float*)q_out,
             (float*)k_cache, (float*)v_cache, n_tokens, n_heads, n_kv, head_dim, page_size, write_cache, n_pages, status);
     else if (dtype == IB_BF16)
-        rope_kv_write_kernel<bf16><<<blocks_for(n, 256), 256, 0, stream>>>(
-            (const bf16*)qkv, cos_t, sin_t, positions, token_seg, block_table, max_blocks, (bf16*)q_out,
+        IB_LAUNCH(rope_kv_write_kernel<bf16>, blocks_for(n, 256), 256, 0, (const bf16*)qkv, cos_t, sin_t, positions, token_seg, block_table, max_blocks, (bf16*)q_out,
             (bf16*)k_cache, (bf16*)v_cache, n_tokens, n_heads, n_kv, head_dim, page_size, write_cache, n_pages, status);
     else
         return ib::fail(IB_ERR_ARG, "ib_rope_kv_write: unknown dtype %d", dtype);
@@ -486,10 +499,10 @@ IB_EXPORT int ib_attention_plain(const void* q, const void* k_cache, const void*
     const dim3 grid{unsigned(n_tokens), unsigned(n_heads), 1u};
     const size_t smem = size_t(head_dim + AT) * sizeof(float) + AT * sizeof(int64_t) + 8;
     if (dtype == IB_F32)
-        attention_kernel<float><<<grid, AT, smem, stream>>>((const float*)q, (const float*)k_cache, (const float*)v_cache,
+        IB_LAUNCH(attention_kernel<float>, grid, AT, smem, (const float*)q, (const float*)k_cache, (const float*)v_cache,
             block_table, max_blocks, token_seg, positions, (float*)out, n_heads, n_kv, head_dim, page_size, window, scale, n_pages, status);
     else if (dtype == IB_BF16)
-        attention_kernel<bf16><<<grid, AT, smem, stream>>>((const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache,
+        IB_LAUNCH(attention_kernel<bf16>, grid, AT, smem, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache,
             block_table, max_blocks, token_seg, positions, (bf16*)out, n_heads, n_kv, head_dim, page_size, window, scale, n_pages, status);
     else
         return ib::fail(IB_ERR_ARG, "ib_attention_plain: unknown dtype %d", dtype);
@@ -502,9 +515,9 @@ IB_EXPORT int ib_swiglu(const void* gate_up, void* out, int64_t n_tokens, int64_
     if (interleave8 && inter % 8) return ib::fail(IB_ERR_ARG, "ib_swiglu: interleaved rows need a multiple of 8 features");
     const int64_t n = n_tokens * inter;
     if (dtype == IB_F32)
-        swiglu_kernel<float><<<blocks_for(n, 256), 256, 0, stream>>>((const float*)gate_up, (float*)out, n_tokens, inter, interleave8);
+        IB_LAUNCH(swiglu_kernel<float>, blocks_for(n, 256), 256, 0, (const float*)gate_up, (float*)out, n_tokens, inter, interleave8);
     else if (dtype == IB_BF16)
-        swiglu_kernel<bf16><<<blocks_for(n, 256), 256, 0, stream>>>((const bf16*)gate_up, (bf16*)out, n_tokens, inter, interleave8);
+        IB_LAUNCH(swiglu_kernel<bf16>, blocks_for(n, 256), 256, 0, (const bf16*)gate_up, (bf16*)out, n_tokens, inter, interleave8);
     else
         return ib::fail(IB_ERR_ARG, "ib_swiglu: unknown dtype %d", dtype);
     return ib::check_launch("ib_swiglu");
@@ -514,7 +527,7 @@ IB_EXPORT int ib_sample(const float* logits, int64_t n_rows, int64_t vocab, cons
                         const int64_t* seed, const int64_t* step, int* out, cudaStream_t stream) {
     if (n_rows <= 0) return IB_OK;
     if (vocab <= 0 || vocab >= 0x7fffffff) return ib::fail(IB_ERR_ARG, "ib_sample: vocabulary %lld out of range", (long long)vocab);
-    sample_kernel<<<unsigned(n_rows), 256, 0, stream>>>(logits, vocab, temperature, seed, step, out);
+    IB_LAUNCH(sample_kernel, unsigned(n_rows), 256, 0, logits, vocab, temperature, seed, step, out);
     return ib::check_launch("ib_sample");
 }
 
@@ -523,6 +536,6 @@ IB_EXPORT int ib_sample_filtered(const float* logits, int64_t n_rows, int64_t vo
                                  int* out, cudaStream_t stream) {
     if (n_rows <= 0) return IB_OK;
     if (vocab <= 0 || vocab >= 0x7fffffff) return ib::fail(IB_ERR_ARG, "ib_sample_filtered: vocabulary %lld out of range", (long long)vocab);
-    sample_filtered_kernel<<<unsigned(n_rows), 1024, 0, stream>>>(logits, vocab, temperature, seed, step, top_k, top_p, out);
+    IB_LAUNCH(sample_filtered_kernel, unsigned(n_rows), 1024, 0, logits, vocab, temperature, seed, step, top_k, top_p, out);
     return ib::check_launch("ib_sample_filtered");
 }

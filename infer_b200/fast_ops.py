@@ -111,8 +111,9 @@ SKINNY_MAX_ROWS = 16
 
 def linear_skinny(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
                   residual: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16,
-                  out: Optional[torch.Tensor] = None, swiglu: bool = False) -> Optional[torch.Tensor]:
-    """The decode kernel: x [M <= 16, K] against w [N, K], weights streamed once; same epilogues as gemm_tc."""
+                  out: Optional[torch.Tensor] = None, swiglu: bool = False, cluster: int = 0) -> Optional[torch.Tensor]:
+    """The decode kernel: x [M <= 16, K] against w [N, K], weights streamed once; same epilogues as gemm_tc.
+    cluster: CTAs sharing one tile's K range (0 = chosen by the kernel)."""
     _check(x, "x", torch.bfloat16)
     _check(w, "w", torch.bfloat16)
     M, K = x.shape
@@ -131,9 +132,9 @@ def linear_skinny(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor]
         out = torch.empty((M, n_out), dtype=out_dtype, device=x.device)
     else:
         _check(out, "out", out_dtype, (M, n_out))
-    f = _fn("gemv", "ib_linear_skinny", [c_void_p] * 5 + [c_int64] * 3 + [c_int] * 2 + [c_void_p])
+    f = _fn("gemv", "ib_linear_skinny", [c_void_p] * 5 + [c_int64] * 3 + [c_int] * 4 + [c_void_p])
     _call(f, x.data_ptr(), w.data_ptr(), _ptr(bias), _ptr(residual), out.data_ptr(), M, N, K, dtype_code(out_dtype),
-          2 if swiglu else (1 if residual is not None else 0), _stream())
+          2 if swiglu else (1 if residual is not None else 0), int(cluster), device_state(x.device).sm_count, _stream())
     return out
 
 
