@@ -33,7 +33,7 @@ MODULES: Dict[str, str] = {
     "gemm": "gemm_tcgen05.cu",
     "attn": "attention_fast.cu",
 }
-HEADERS = ["common.cuh"]
+HEADERS = ["common.cuh", "gemm_static.h"]
 # modules that are compiled per model size: the variant that build_all() makes (others are built at first use)
 DEFAULT_DEFINES = {"attn": {"IB_HEAD_DIM": 128}}
 
@@ -165,6 +165,8 @@ def load_module(module: str, defines: Optional[Mapping[str, object]] = None) -> 
         except OSError as e:
             raise BuildError(f"cannot load {path}: {e}") from None
         lib.ib_last_error.restype = ctypes.c_char_p
+        if os.environ.get("INFER_B200_PDL", "1") == "0":
+            lib.ib_set_pdl(0)           # launch every kernel fully serialised (for comparisons)
         _LOADED[path] = lib
     return lib
 

@@ -564,3 +564,64 @@ IB_EXPORT int ib_gemm_tc(const void* x, const void* w, const float* bias, const 
         default: return f32 ? launch<128, float>(ma, mb, p, grid, stream) : launch<128, bf16>(ma, mb, p, grid, stream);
     }
 }
+
+// ================================================================================================
+// The variant that allocates nothing (declared and explained in gemm_static.h).
+#include "gemm_static.h"
+
+namespace {
+
+// Split-K scratch of ib_gemm_tc_static: [counters: IB_STATIC_COUNTERS words][partial tiles: the rest, as floats].
+// In host code this name is only a handle for cudaGetSymbolAddress, never a device address.
+static __device__ __align__(256) unsigned char g_static_scratch[IB_GEMM_STATIC_SCRATCH_BYTES];
+constexpr int64_t IB_STATIC_COUNTERS = 4096;                                    // per-tile arrival counters (16 KiB)
+constexpr int IB_STATIC_MAX_DEVICES = 64;
+
+// Device address of g_static_scratch on `device`, looked up once per device with that device current.
+int static_scratch(int device, unsigned char** ptr) {
+    static unsigned char* addr[IB_STATIC_MAX_DEVICES] = {};
+    static std::mutex mu;
+    if (device < 0 || device >= IB_STATIC_MAX_DEVICES) return ib::fail(IB_ERR_ARG, "gemm_tc_static: device %d out of range", device);
+    std::lock_guard<std::mutex> lock(mu);
+    if (!addr[device]) {
+        void* p = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);      // the current device is `device`
+        if (e != cudaSuccess) return ib::fail(IB_ERR_CUDA, "gemm_tc_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+        addr[device] = static_cast<unsigned char*>(p);
+    }
+    *ptr = addr[device];
+    return IB_OK;
+}
+
+}  // namespace
+
+IB_EXPORT int ib_gemm_tc_static(const void* x, const void* w, const float* bias, const float* residual, void* out, int64_t M,
+                                int64_t N, int64_t K, int out_dtype, int sm_count, int* status, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return IB_OK;
+    int swap = 0, bn = 0, splits = 1;
+    int64_t ws_floats = 0, n_counters = 0;
+    int rc = ib_gemm_tc_plan(M, N, K, sm_count > 0 ? sm_count : 148, &swap, &bn, &splits, &ws_floats, &n_counters);
+    if (rc) return rc;
+    float* workspace = nullptr;
+    unsigned int* counters = nullptr;
+    if (splits > 1) {
+        const int64_t room = (int64_t(IB_GEMM_STATIC_SCRATCH_BYTES) - IB_STATIC_COUNTERS * 4) / 4;
+        if (ws_floats > room || n_counters > IB_STATIC_COUNTERS)
+            return ib::fail(IB_ERR_ARG, "gemm_tc_static: M=%lld N=%lld K=%lld needs %lld bytes of split-K scratch and %lld counters; "
+                            "the built-in array holds %lld bytes and %lld counters",
+                            (long long)M, (long long)N, (long long)K, (long long)(ws_floats * 4), (long long)n_counters,
+                            (long long)(room * 4), (long long)IB_STATIC_COUNTERS);
+        int device = 0;
+        cudaError_t e = cudaGetDevice(&device);
+        if (e != cudaSuccess) return ib::fail(IB_ERR_CUDA, "gemm_tc_static: cudaGetDevice failed: %s", cudaGetErrorString(e));
+        unsigned char* base = nullptr;
+        rc = static_scratch(device, &base);
+        if (rc) return rc;
+        counters = reinterpret_cast<unsigned int*>(base);
+        workspace = reinterpret_cast<float*>(base + IB_STATIC_COUNTERS * 4);
+        // The counters must start at zero; earlier calls leave them so, but a call that was cut short would not.
+        e = cudaMemsetAsync(counters, 0, size_t(n_counters) * 4, stream);
+        if (e != cudaSuccess) return ib::fail(IB_ERR_CUDA, "gemm_tc_static: clearing the counters failed: %s", cudaGetErrorString(e));
+    }
+    return ib_gemm_tc(x, w, bias, residual, out, M, N, K, out_dtype, 0, swap, bn, splits, workspace, counters, status, stream);
+}
