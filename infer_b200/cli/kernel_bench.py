@@ -61,6 +61,7 @@ def main(argv=None) -> int:
     ap.add_argument("--head-dim", type=int, default=128)
     ap.add_argument("--splits", type=int, default=0)
     ap.add_argument("--cluster", type=int, default=0)
+    ap.add_argument("--norm", action="store_true", help="skinny kernel with the fused RMSNorm prologue")
     ap.add_argument("--reps", type=int, default=50)
     args = ap.parse_args(argv)
     import torch
@@ -73,6 +74,7 @@ def main(argv=None) -> int:
         copies = max(4, min(64, L2 // (N * K * 2) + 1))
         ws = [(torch.randn(N, K, device=dev) * 0.05).bfloat16() for _ in range(copies)]
         x = torch.randn(M, K, device=dev).bfloat16()
+        hx, nw = torch.randn(M, K, device=dev), torch.ones(K, device=dev)
         n_out = N // 2 if args.epi == "swiglu" else N
         res = torch.randn(M, n_out, device=dev) if args.epi == "residual" else None
         swiglu = args.epi == "swiglu"
@@ -86,6 +88,8 @@ def main(argv=None) -> int:
         def run(i):
             r = res
             if args.kernel == "skinny":
+                if args.norm:
+                    return fast_ops.linear_skinny(hx, ws[i], None, r, odt, r, swiglu, args.cluster, nw, 1e-6)
                 return fast_ops.linear_skinny(x, ws[i], None, r, odt, r, swiglu, args.cluster)
             if args.kernel == "tc":
                 return fast_ops.gemm_tc(x, ws[i], None, r, odt, r, swiglu=swiglu, plan=plan)

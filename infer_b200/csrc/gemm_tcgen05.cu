@@ -184,11 +184,22 @@ __device__ __forceinline__ void epilogue_store(const GemmParams& p, const float*
         } else {
             const int64_t m = a_row, n0 = b_row0;
             if (m < p.M && n0 < p.N) {
+                float act[8];
 #pragma unroll
-                for (int j = 0; j < 8; j++) {
-                    const float gte = v[j];
-                    store_elem<TOut>(out + m * half + (n0 >> 1) + j, gte / (1.0f + expf(-gte)) * v[j + 8]);
+                for (int j = 0; j < 8; j++) act[j] = v[j] / (1.0f + __expf(-v[j])) * v[j + 8];
+                if constexpr (sizeof(TOut) == 2) {
+                    if ((half & 7) == 0) {                      // 8 bfloat16 = one 16-byte store
+                        __nv_bfloat162 h0 = __floats2bfloat162_rn(act[0], act[1]), h1 = __floats2bfloat162_rn(act[2], act[3]);
+                        __nv_bfloat162 h2 = __floats2bfloat162_rn(act[4], act[5]), h3 = __floats2bfloat162_rn(act[6], act[7]);
+                        uint4 u;
+                        u.x = *reinterpret_cast<uint32_t*>(&h0); u.y = *reinterpret_cast<uint32_t*>(&h1);
+                        u.z = *reinterpret_cast<uint32_t*>(&h2); u.w = *reinterpret_cast<uint32_t*>(&h3);
+                        *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(p.out) + m * half + (n0 >> 1)) = u;
+                        return;
+                    }
                 }
+#pragma unroll
+                for (int j = 0; j < 8; j++) store_elem<TOut>(out + m * half + (n0 >> 1) + j, act[j]);
             }
         }
         return;

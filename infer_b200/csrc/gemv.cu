@@ -1,20 +1,24 @@
-// Skinny matrix product for decode steps: out[M, N] = x[M, K] . w[N, K]^T with M <= 16 tokens.
+// Streaming matrix product for decode steps: out[M, N] = f(x)[M, K] . w[N, K]^T with M <= 16 tokens, where f is the
+// identity (x bfloat16) or a fused RMSNorm (x = the float residual stream, normalised on the fly).
 //
 // The weights are read exactly once, straight from global memory into registers with 16-byte loads, and used as
 // the 16-row operand of mma.sync m16n8k16 (bfloat16 in, float accumulation); the tokens are the 8-wide operand.
 // The kernel is bound by HBM bandwidth, so the tensor-core shape only has to keep the instruction count low.
 //
-// Work split. A tile is 16 output features. A thread-block cluster of CL CTAs (1, 2, 4 or 8, chosen so that the
-// grid fills the GPU even when N is small) owns one tile; each CTA of the cluster takes a contiguous slice of K, each
-// of its 8 warps a slice of that. Partial tiles are added in shared memory in warp order, then, across the cluster,
-// the first CTA reads the other CTAs' sums through distributed shared memory in rank order. No global scratch, no
-// atomics, and a result that does not depend on timing.
+// Work split. A tile is 16 output features and one CTA (many small CTAs, eight and more per SM, keep enough loads in
+// flight to saturate HBM; a persistent variant with a register ping-pong across tiles measured slower). The CTA's 8
+// warps split K and add their partial tiles in shared memory in warp order. For small N a thread-block cluster of 2,
+// 4 or 8 CTAs shares each tile, each CTA taking a slice of K, and the cluster's first CTA adds the slices through
+// distributed shared memory in rank order: no global scratch, no atomics, a result that does not depend on timing.
+// The first weight loads are issued before the kernel waits for its predecessor (weights have no producer kernel).
+//
+// Fused norm. With norm_w the activations are the float residual stream: each warp normalises rows into shared
+// memory, y = x * rsqrt(mean(x^2) + eps) * g in float, rounded to bfloat16 as the separate norm kernel would
+// (K <= 4096; padded rows give conflict-free 16-byte reads). Without it activations are read through L1.
 //
 // Loads are 16 bytes per lane and 64 contiguous bytes per weight row and 32-element chunk: lane (g, t) of a warp
 // holds elements [8t, 8t+8) of rows g and g+8. The two MMAs of a chunk pair those elements in an order that differs
 // from the natural k order, identically for weights and activations, which leaves every dot product unchanged.
-// Weight loads run one iteration (4 chunks) ahead of the MMAs, and the first of them are issued before the kernel
-// waits for its predecessor (weights are never written by a kernel), so HBM stays busy across kernel boundaries.
 //
 // Epilogues: (0) + bias -> bfloat16 or float; (1) + residual (float, may alias out) -> float; (2) SwiGLU for a
 // gate/up matrix whose rows are interleaved in blocks of 8 (rows 16b..16b+7 = gate features 8b..8b+7, rows
@@ -33,6 +37,8 @@ using bf16 = __nv_bfloat16;
 constexpr int WARPS = 8;
 constexpr int ROWS = 16;
 constexpr int UNROLL = 4;
+constexpr int XS_MAX_K = 4096;            // activations are staged in shared memory up to this K
+constexpr int XS_PAD = 64;                // bytes of padding per staged row (rows start 16 banks apart)
 
 __device__ __forceinline__ uint4 ld_stream(const void* p) {
     uint4 v;
@@ -46,55 +52,45 @@ __device__ __forceinline__ void mma_bf16(float* c, uint32_t a0, uint32_t a1, uin
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// One tile step: the MMAs of UNROLL chunks starting at chunk c, weights in (a0, a1), activations loaded here.
-template <int NT>
-__device__ __forceinline__ void tile_step(float (*acc)[4], const uint4* a0, const uint4* a1, const bf16* const* xr,
-                                          const bool* x_ok, int64_t c, int64_t c_end, int64_t K, int t) {
-    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-    uint4 b[UNROLL][NT];
-#pragma unroll
-    for (int u = 0; u < UNROLL; u++) {
-        const int64_t k = (c + u) * 32;
-        const bool k_ok = c + u < c_end && k + t * 8 < K;
-#pragma unroll
-        for (int nt = 0; nt < NT; nt++)
-            b[u][nt] = (k_ok && x_ok[nt]) ? __ldg(reinterpret_cast<const uint4*>(xr[nt] + k)) : zero;
-    }
-#pragma unroll
-    for (int u = 0; u < UNROLL; u++)
-#pragma unroll
-        for (int nt = 0; nt < NT; nt++) {
-            mma_bf16(acc[nt], a0[u].x, a1[u].x, a0[u].y, a1[u].y, b[u][nt].x, b[u][nt].y);
-            mma_bf16(acc[nt], a0[u].z, a1[u].z, a0[u].w, a1[u].w, b[u][nt].z, b[u][nt].w);
-        }
-}
+struct GemvParams {
+    const bf16* x;            // [M, K] bfloat16 activations (NORM = false)
+    const float* h;           // [M, K] float residual stream (NORM = true)
+    const float* norm_w;      // [K]
+    float eps;
+    const bf16* w;            // [N, K]
+    const float* bias;        // [N] or null
+    const float* residual;    // [M, N] or null
+    void* out;
+    int M;
+    int64_t N, K, tiles;
+    int cluster, groups;      // CTAs per tile; tile groups in the grid (grid = groups * cluster)
+    int stage_x;              // activations staged in shared memory
+};
 
-// WPT = warps per tile: 8 (the CTA's warps split K and add their partial tiles in shared memory; with a cluster,
-// CTAs split K further) or 1 (every warp owns a tile and the whole K range: no reduction at all, for very large N).
-template <int NT, int EPI, int WPT, typename TOut>
-__global__ void __launch_bounds__(WARPS * 32, 2)
-skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const float* __restrict__ bias,
-              const float* residual, TOut* out, int M, int64_t N, int64_t K, int cluster) {
-    __shared__ float red[WPT == 1 ? 1 : WARPS][NT][8][ROWS];
+// Occupancy matters more than anything else here (resident warps = bytes in flight): 64 registers for up to 8
+// tokens, so that four CTAs share an SM.
+template <int NT, int EPI, bool NORM, typename TOut>
+__global__ void __launch_bounds__(WARPS * 32, NT == 1 ? 4 : 2)
+stream_gemv_kernel(const GemvParams p) {
+    extern __shared__ __align__(16) uint8_t xs[];        // staged activations [8 NT][K + pad] bfloat16 (fused norm only)
+    __shared__ float red[WARPS][NT][8][ROWS];
     __shared__ float part[NT][8][ROWS];                  // this CTA's sum; read by the cluster's first CTA
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
+    const int cluster = p.cluster;
     const int rank = cluster > 1 ? int(blockIdx.x % cluster) : 0;
-    const int64_t tile = WPT == 1 ? int64_t(blockIdx.x) * WARPS + warp : blockIdx.x / cluster;
+    const int64_t tile = blockIdx.x / cluster;
+    const int64_t K = p.K, N = p.N;
     const int64_t n0 = tile * ROWS;
     const int64_t chunks = (K + 31) / 32;
-    int64_t c_begin = 0, c_end = chunks;
-    if (WPT != 1) {
-        const int64_t per_cta = (chunks + cluster - 1) / cluster;
-        const int64_t cta_begin = rank * per_cta, cta_end = min(chunks, cta_begin + per_cta);
-        const int64_t per_warp = (max(int64_t(0), cta_end - cta_begin) + WARPS - 1) / WARPS;
-        c_begin = cta_begin + warp * per_warp;
-        c_end = min(cta_end, c_begin + per_warp);
-    }
-    const bool row0_ok = n0 + g < N, row1_ok = n0 + g + 8 < N;
-    const bf16* w0 = w + (n0 + g) * K + t * 8;
-    const bf16* w1 = w + (n0 + g + 8) * K + t * 8;
+    const int64_t per_cta = (chunks + cluster - 1) / cluster;
+    const int64_t cta_begin = rank * per_cta, cta_end = min(chunks, cta_begin + per_cta);
+    const int64_t per_warp = (per_cta + WARPS - 1) / WARPS;
+    const int64_t c_begin = min(cta_end, cta_begin + warp * per_warp), c_end = min(cta_end, c_begin + per_warp);
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    const bool row0_ok = n0 + g < N, row1_ok = n0 + g + 8 < N;
+    const bf16* w0 = p.w + (n0 + g) * K + t * 8;
+    const bf16* w1 = p.w + (n0 + g + 8) * K + t * 8;
 
     auto load_w = [&](int64_t c, uint4* a0, uint4* a1) {
 #pragma unroll
@@ -105,55 +101,64 @@ skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const floa
             a1[u] = (k_ok && row1_ok) ? ld_stream(w1 + k) : zero;
         }
     };
-    // Two register sets of weights alternate: while one is multiplied, the other is in flight.
-    uint4 pa0[UNROLL], pa1[UNROLL], qa0[UNROLL], qa1[UNROLL];
-    load_w(c_begin, pa0, pa1);                           // before the wait: weights have no producer kernel
+    uint4 a0[UNROLL], a1[UNROLL];
+    load_w(c_begin, a0, a1);                             // before the wait: weights have no producer kernel
+    ib::pdl_launch_dependents();                         // the successor may start its own weight loads as SMs free up
     ib::pdl_wait();
 
-    const bf16* xr[NT];
+    // ---------------------------------------------------------------- fused RMSNorm: normalised rows in shared memory
+    const int64_t xs_pitch = K * 2 + XS_PAD;             // bytes per staged row
+    if constexpr (NORM) {
+        for (int row = warp; row < p.M; row += WARPS) {
+            const float* hr = p.h + int64_t(row) * K;
+            float ss = 0.0f;
+            for (int64_t i = lane * 4; i < K; i += 128) {
+                const float4 v = *reinterpret_cast<const float4*>(hr + i);
+                ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+            }
+            ss = ib::warp_sum(ss);
+            const float scale = rsqrtf(ss / float(K) + p.eps);
+            for (int64_t i = lane * 4; i < K; i += 128) {
+                const float4 v = *reinterpret_cast<const float4*>(hr + i);
+                const float4 gw = *reinterpret_cast<const float4*>(p.norm_w + i);
+                __nv_bfloat162 lo = __floats2bfloat162_rn(v.x * scale * gw.x, v.y * scale * gw.y);
+                __nv_bfloat162 hi = __floats2bfloat162_rn(v.z * scale * gw.z, v.w * scale * gw.w);
+                uint2 pk;
+                pk.x = *reinterpret_cast<uint32_t*>(&lo);
+                pk.y = *reinterpret_cast<uint32_t*>(&hi);
+                *reinterpret_cast<uint2*>(xs + row * xs_pitch + i * 2) = pk;
+            }
+        }
+        __syncthreads();
+    }
     bool x_ok[NT];
 #pragma unroll
-    for (int nt = 0; nt < NT; nt++) {
-        x_ok[nt] = nt * 8 + g < M;
-        xr[nt] = x + int64_t(nt * 8 + g) * K + t * 8;
-    }
+    for (int nt = 0; nt < NT; nt++) x_ok[nt] = nt * 8 + g < p.M;
     float acc[NT][4];
 #pragma unroll
     for (int nt = 0; nt < NT; nt++) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.0f;
 
-    for (int64_t c = c_begin; c < c_end; c += 2 * UNROLL) {
-        load_w(c + UNROLL, qa0, qa1);
-        tile_step<NT>(acc, pa0, pa1, xr, x_ok, c, c_end, K, t);
-        load_w(c + 2 * UNROLL, pa0, pa1);
-        tile_step<NT>(acc, qa0, qa1, xr, x_ok, c + UNROLL, c_end, K, t);
-    }
-    ib::pdl_launch_dependents();
-
-    if constexpr (WPT == 1) {
-        // The warp's C fragments are the tile: rows g and g+8 (features), columns 2t and 2t+1 (tokens).
+    for (int64_t c = c_begin; c < c_end; c += UNROLL) {
+        if (c != c_begin) load_w(c, a0, a1);
+        uint4 b[UNROLL][NT];
 #pragma unroll
-        for (int nt = 0; nt < NT; nt++)
+        for (int u = 0; u < UNROLL; u++) {
+            const int64_t k = (c + u) * 32 + t * 8;
+            const bool k_ok = c + u < c_end && k < K;
 #pragma unroll
-            for (int e = 0; e < 2; e++) {
-                const int m = nt * 8 + 2 * t + e;
-                if (m >= M) continue;
-                if constexpr (EPI == 2) {
-                    const float gate = acc[nt][e], up = acc[nt][2 + e];
-                    const int64_t f = tile * 8 + g;
-                    if (f < N / 2) out[int64_t(m) * (N / 2) + f] = ib::from_f32<TOut>(gate / (1.0f + expf(-gate)) * up);
-                } else {
-#pragma unroll
-                    for (int hh = 0; hh < 2; hh++) {
-                        const int64_t n = n0 + g + 8 * hh;
-                        if (n >= N) continue;
-                        float v = acc[nt][2 * hh + e];
-                        if (bias) v += bias[n];
-                        if constexpr (EPI == 1) v += residual[int64_t(m) * N + n];
-                        out[int64_t(m) * N + n] = ib::from_f32<TOut>(v);
-                    }
-                }
+            for (int nt = 0; nt < NT; nt++) {
+                if (!(k_ok && x_ok[nt])) b[u][nt] = zero;
+                else if (NORM) b[u][nt] = *reinterpret_cast<const uint4*>(xs + (nt * 8 + g) * xs_pitch + k * 2);
+                else b[u][nt] = __ldg(reinterpret_cast<const uint4*>(p.x + int64_t(nt * 8 + g) * K + k));
             }
-        return;
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; u++)
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) {
+                mma_bf16(acc[nt], a0[u].x, a1[u].x, a0[u].y, a1[u].y, b[u][nt].x, b[u][nt].y);
+                mma_bf16(acc[nt], a0[u].z, a1[u].z, a0[u].w, a1[u].w, b[u][nt].z, b[u][nt].w);
+            }
     }
 #pragma unroll
     for (int nt = 0; nt < NT; nt++) {
@@ -178,16 +183,16 @@ skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const floa
             for (int other = 1; other < cluster; other++)
                 v += cl.map_shared_rank(&part[0][0][0], other)[(nt * 8 + col) * ROWS + r];
         }
-        if (rank == 0 && EPI == 2 && active) part[nt][col][r] = v;     // the SwiGLU epilogue pairs rows r and r + 8
         cl.sync();                                       // the others' shared memory stays alive until it was read
         if (rank != 0) return;
-    } else if (EPI == 2) {
-        if (active) part[nt][col][r] = v;
+    }
+    if (EPI == 2) {
+        if (active) part[nt][col][r] = v;                // the SwiGLU epilogue pairs rows r and r + 8
         __syncthreads();
     }
-    if (!active) return;
     const int m = nt * 8 + col;
-    if (m >= M) return;
+    if (!active || m >= p.M) return;
+    TOut* out = reinterpret_cast<TOut*>(p.out);
     if constexpr (EPI == 2) {
         if (r >= 8) return;
         const float gate = v, up = part[nt][col][r + 8];
@@ -196,69 +201,83 @@ skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const floa
     } else {
         const int64_t n = n0 + r;
         if (n >= N) return;
-        if (bias) v += bias[n];
-        if constexpr (EPI == 1) v += residual[int64_t(m) * N + n];
+        if (p.bias) v += p.bias[n];
+        if constexpr (EPI == 1) v += p.residual[int64_t(m) * N + n];
         out[int64_t(m) * N + n] = ib::from_f32<TOut>(v);
     }
 }
 
-template <int NT, int WPT>
-int launch(const bf16* x, const bf16* w, const float* bias, const float* residual, void* out, int M, int64_t N, int64_t K,
-           int out_dtype, int epi, int cluster, cudaStream_t stream) {
-    const int64_t tiles = (N + ROWS - 1) / ROWS;
-    const dim3 grid{WPT == 1 ? unsigned((tiles + WARPS - 1) / WARPS) : unsigned(tiles) * unsigned(cluster), 1u, 1u};
+template <int NT, bool NORM>
+int launch(const GemvParams& p, int out_dtype, int epi, int grid_ctas, size_t smem, cudaStream_t stream) {
+    const dim3 grid{unsigned(grid_ctas), 1u, 1u};
     const dim3 block{WARPS * 32, 1u, 1u};
-    const unsigned cl = unsigned(cluster);
+    const unsigned cl = unsigned(p.cluster);
+#define IB_GEMV_LAUNCH(EPI_, T_)                                                                                   \
+    do {                                                                                                           \
+        static bool configured = false;                                                                            \
+        if (!configured) {                                                                                         \
+            cudaError_t e = cudaFuncSetAttribute(stream_gemv_kernel<NT, EPI_, NORM, T_>,                           \
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, 16 * (XS_MAX_K * 2 + XS_PAD)); \
+            if (e != cudaSuccess) return ib::fail(IB_ERR_CUDA, "linear_skinny: cannot set shared memory size: %s", cudaGetErrorString(e)); \
+            configured = true;                                                                                     \
+        }                                                                                                          \
+        return ib::launch("linear_skinny", stream_gemv_kernel<NT, EPI_, NORM, T_>, grid, block, smem, stream, cl, p);  \
+    } while (0)
     if (epi == 2) {
         if (out_dtype != IB_BF16) return ib::fail(IB_ERR_ARG, "linear_skinny: the SwiGLU epilogue writes bfloat16");
-        return ib::launch("linear_skinny", skinny_kernel<NT, 2, WPT, bf16>, grid, block, 0, stream, cl, x, w,
-                          (const float*)nullptr, (const float*)nullptr, (bf16*)out, M, N, K, cluster);
+        IB_GEMV_LAUNCH(2, bf16);
     }
     if (epi == 1) {
-        if (out_dtype != IB_F32 || !residual) return ib::fail(IB_ERR_ARG, "linear_skinny: the residual epilogue needs a float residual and output");
-        return ib::launch("linear_skinny", skinny_kernel<NT, 1, WPT, float>, grid, block, 0, stream, cl, x, w, bias,
-                          residual, (float*)out, M, N, K, cluster);
+        if (out_dtype != IB_F32 || !p.residual) return ib::fail(IB_ERR_ARG, "linear_skinny: the residual epilogue needs a float residual and output");
+        IB_GEMV_LAUNCH(1, float);
     }
-    if (out_dtype == IB_F32)
-        return ib::launch("linear_skinny", skinny_kernel<NT, 0, WPT, float>, grid, block, 0, stream, cl, x, w, bias,
-                          (const float*)nullptr, (float*)out, M, N, K, cluster);
-    if (out_dtype == IB_BF16)
-        return ib::launch("linear_skinny", skinny_kernel<NT, 0, WPT, bf16>, grid, block, 0, stream, cl, x, w, bias,
-                          (const float*)nullptr, (bf16*)out, M, N, K, cluster);
+    if (out_dtype == IB_F32) IB_GEMV_LAUNCH(0, float);
+    if (out_dtype == IB_BF16) IB_GEMV_LAUNCH(0, bf16);
+#undef IB_GEMV_LAUNCH
     return ib::fail(IB_ERR_ARG, "linear_skinny: unknown output dtype %d", out_dtype);
 }
 
 }  // namespace
 
-// epi: 0 = (+ bias), 1 = (+ bias) + residual -> float, 2 = SwiGLU over rows interleaved by 8 -> bfloat16 [M, N/2].
-// cluster: CTAs that share a tile's K range (1, 2, 4 or 8); 0 lets the kernel choose from N, K and sm_count, and
-// -1 asks for the warp-per-tile mapping (no reduction), which the kernel also chooses by itself for very large N.
-IB_EXPORT int ib_linear_skinny(const void* x, const void* w, const float* bias, const float* residual, void* out,
-                               int64_t M, int64_t N, int64_t K, int out_dtype, int epi, int cluster, int sm_count,
-                               cudaStream_t stream) {
+// x: bfloat16 [M, K], or with norm_w != null the float residual stream [M, K] that is RMS-normalised on the fly
+// (y = x * rsqrt(mean(x^2) + eps) * norm_w, K <= 4096). epi: 0 = (+ bias), 1 = (+ bias) + residual -> float,
+// 2 = SwiGLU over rows interleaved by 8 -> bfloat16 [M, N/2]. cluster: CTAs that share a tile's K range (1, 2, 4 or
+// 8); 0 lets the kernel choose from N, K and sm_count.
+IB_EXPORT int ib_linear_skinny(const void* x, const float* norm_w, float eps, const void* w, const float* bias,
+                               const float* residual, void* out, int64_t M, int64_t N, int64_t K, int out_dtype, int epi,
+                               int cluster, int sm_count, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return IB_OK;
     if (M > 16) return ib::fail(IB_ERR_ARG, "linear_skinny: at most 16 rows, got %lld", (long long)M);
     if (K <= 0 || K % 8) return ib::fail(IB_ERR_ARG, "linear_skinny: K = %lld must be a positive multiple of 8", (long long)K);
     if ((uintptr_t(x) & 15) || (uintptr_t(w) & 15)) return ib::fail(IB_ERR_ARG, "linear_skinny: operands must be 16-byte aligned");
     if (epi == 2 && N % 16) return ib::fail(IB_ERR_ARG, "linear_skinny: the SwiGLU epilogue needs N to be a multiple of 16");
+    if (norm_w && (K > XS_MAX_K || (uintptr_t(norm_w) & 15)))
+        return ib::fail(IB_ERR_ARG, "linear_skinny: the fused norm takes K <= %d and a 16-byte aligned weight", XS_MAX_K);
     const int64_t tiles = (N + ROWS - 1) / ROWS;
-    if (tiles * 8 > 0x7fffffffLL) return ib::fail(IB_ERR_ARG, "linear_skinny: N too large");
+    if (tiles > 0x7fffffffLL / 8) return ib::fail(IB_ERR_ARG, "linear_skinny: N too large");
     const int sms = sm_count > 0 ? sm_count : 148;
     if (cluster == 0) {
-        if (tiles >= 16LL * WARPS * sms / 4) {
-            cluster = -1;                                 // enough tiles for every warp of the GPU to own several
-        } else {
-            // Fill the GPU about twice over, but leave every warp at least four 32-element chunks of K.
-            cluster = 1;
-            const int64_t chunks = (K + 31) / 32;
-            while (cluster < 8 && tiles * cluster < 2LL * sms && chunks / (cluster * 2) >= 4 * WARPS) cluster *= 2;
-        }
-    }
-    if (cluster == -1) {
-        if (M <= 8) return launch<1, 1>((const bf16*)x, (const bf16*)w, bias, residual, out, int(M), N, K, out_dtype, epi, 1, stream);
-        return launch<2, 1>((const bf16*)x, (const bf16*)w, bias, residual, out, int(M), N, K, out_dtype, epi, 1, stream);
+        // Share a tile among CTAs while the tiles alone leave SMs idle and every warp keeps at least four chunks of K.
+        cluster = 1;
+        const int64_t chunks = (K + 31) / 32;
+        while (cluster < 8 && tiles * cluster < 2LL * sms && chunks / (cluster * 2) >= 4 * WARPS) cluster *= 2;
     }
     if (cluster != 1 && cluster != 2 && cluster != 4 && cluster != 8) return ib::fail(IB_ERR_ARG, "linear_skinny: cluster must be 1, 2, 4 or 8");
-    if (M <= 8) return launch<1, 8>((const bf16*)x, (const bf16*)w, bias, residual, out, int(M), N, K, out_dtype, epi, cluster, stream);
-    return launch<2, 8>((const bf16*)x, (const bf16*)w, bias, residual, out, int(M), N, K, out_dtype, epi, cluster, stream);
+    GemvParams p;
+    p.x = norm_w ? nullptr : (const bf16*)x;
+    p.h = norm_w ? (const float*)x : nullptr;
+    p.norm_w = norm_w; p.eps = eps;
+    p.w = (const bf16*)w; p.bias = bias; p.residual = residual; p.out = out;
+    p.M = int(M); p.N = N; p.K = K; p.tiles = tiles; p.cluster = cluster;
+    p.groups = int(tiles);
+    p.stage_x = norm_w ? 1 : 0;
+    const int rows_pad = M <= 8 ? 8 : 16;
+    const size_t smem = norm_w ? size_t(rows_pad) * size_t(K * 2 + XS_PAD) : 0;
+    const int grid_ctas = int(tiles) * cluster;
+    if (norm_w) {
+        if (M <= 8) return launch<1, true>(p, out_dtype, epi, grid_ctas, smem, stream);
+        return launch<2, true>(p, out_dtype, epi, grid_ctas, smem, stream);
+    }
+    if (M <= 8) return launch<1, false>(p, out_dtype, epi, grid_ctas, smem, stream);
+    return launch<2, false>(p, out_dtype, epi, grid_ctas, smem, stream);
 }

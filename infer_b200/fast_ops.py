@@ -111,10 +111,13 @@ SKINNY_MAX_ROWS = 16
 
 def linear_skinny(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
                   residual: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16,
-                  out: Optional[torch.Tensor] = None, swiglu: bool = False, cluster: int = 0) -> Optional[torch.Tensor]:
+                  out: Optional[torch.Tensor] = None, swiglu: bool = False, cluster: int = 0,
+                  norm_weight: Optional[torch.Tensor] = None, norm_eps: float = 0.0) -> Optional[torch.Tensor]:
     """The decode kernel: x [M <= 16, K] against w [N, K], weights streamed once; same epilogues as gemm_tc.
+    With ``norm_weight`` x is the float32 residual stream and is RMS-normalised inside the kernel (K <= 4096).
     cluster: CTAs sharing one tile's K range (0 = chosen by the kernel)."""
-    _check(x, "x", torch.bfloat16)
+    fused = norm_weight is not None
+    _check(x, "x", torch.float32 if fused else torch.bfloat16)
     _check(w, "w", torch.bfloat16)
     M, K = x.shape
     N = w.shape[0]
@@ -122,6 +125,10 @@ def linear_skinny(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor]
         raise KernelError(f"linear_skinny: x is [{M},{K}] but w is {tuple(w.shape)}")
     if M > SKINNY_MAX_ROWS or K % 8 or (x.data_ptr() & 15) or (w.data_ptr() & 15) or (swiglu and N % 16):
         return None
+    if fused:
+        _check(norm_weight, "norm_weight", torch.float32, (K,))
+        if K > 4096 or (norm_weight.data_ptr() & 15):
+            return None
     if bias is not None:
         _check(bias, "bias", torch.float32, (N,))
     if residual is not None:
@@ -132,15 +139,24 @@ def linear_skinny(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor]
         out = torch.empty((M, n_out), dtype=out_dtype, device=x.device)
     else:
         _check(out, "out", out_dtype, (M, n_out))
-    f = _fn("gemv", "ib_linear_skinny", [c_void_p] * 5 + [c_int64] * 3 + [c_int] * 4 + [c_void_p])
-    _call(f, x.data_ptr(), w.data_ptr(), _ptr(bias), _ptr(residual), out.data_ptr(), M, N, K, dtype_code(out_dtype),
-          2 if swiglu else (1 if residual is not None else 0), int(cluster), device_state(x.device).sm_count, _stream())
+    f = _fn("gemv", "ib_linear_skinny", [c_void_p, c_void_p, c_float] + [c_void_p] * 4 + [c_int64] * 3 + [c_int] * 4 + [c_void_p])
+    _call(f, x.data_ptr(), _ptr(norm_weight), float(norm_eps), w.data_ptr(), _ptr(bias), _ptr(residual), out.data_ptr(),
+          M, N, K, dtype_code(out_dtype), 2 if swiglu else (1 if residual is not None else 0), int(cluster),
+          device_state(x.device).sm_count, _stream())
     return out
 
 
 def linear(x, weight, bias, residual, out_dtype, out, swiglu=False):
     """The bfloat16 matrix product of the serving path: the streaming kernel for up to 16 rows, the tcgen05 kernel
-    above that; None if neither takes the shape."""
+    above that; None if neither takes the shape. x may be a DeferredNorm (the float32 residual stream plus the norm
+    that is still to be applied): the streaming kernel then normalises inside, anything else materialises it."""
+    from .parts.base import DeferredNorm
+    if isinstance(x, DeferredNorm):
+        if weight.dtype == torch.bfloat16 and x.h.shape[0] <= SKINNY_MAX_ROWS:
+            y = linear_skinny(x.h, weight, bias, residual, out_dtype, out, swiglu, 0, x.norm.weight, x.norm.eps)
+            if y is not None:
+                return y
+        x = x.materialize()
     if x.dtype != torch.bfloat16:
         return None
     if x.shape[0] <= SKINNY_MAX_ROWS:

@@ -22,6 +22,8 @@ from .linear import Linear
 
 @register_mixer("attention")
 class Attention(Mixer):
+    accepts_deferred_norm = True
+
     def __init__(self, spec: PartSpec, runtime):
         super().__init__(spec, runtime)
         self.hidden = int(spec["hidden_size"])

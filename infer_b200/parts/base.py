@@ -61,6 +61,25 @@ class Part:
         needs to the device, in the layout its kernels want."""
 
 
+class DeferredNorm:
+    """The float32 rows ``h`` with a norm that has not been applied yet. A part that declares
+    ``accepts_deferred_norm`` may receive this instead of the normalised tensor and hand it to a kernel that
+    normalises on the fly; ``materialize()`` applies the norm the ordinary way."""
+
+    def __init__(self, norm: "Norm", h: torch.Tensor):
+        self.norm, self.h = norm, h
+        self._value = None
+
+    @property
+    def shape(self):
+        return self.h.shape
+
+    def materialize(self) -> torch.Tensor:
+        if self._value is None:
+            self._value = self.norm.forward(self.h)
+        return self._value
+
+
 class Norm(Part):
     def forward(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         """x [rows, size] float32 (the residual stream) -> normalised rows in the compute dtype."""
@@ -80,6 +99,8 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    accepts_deferred_norm = False    # True: forward() may get a DeferredNorm as x
+
     def cache_need(self):
         """PagedKVNeed, StateNeed or None."""
         return None
@@ -94,6 +115,8 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    accepts_deferred_norm = False
+
     def forward(self, x: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
         """Returns residual + feed_forward(x), float32 [T, hidden] (may overwrite ``residual``)."""
         raise NotImplementedError

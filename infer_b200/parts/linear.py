@@ -23,9 +23,10 @@ class Linear:
 
     def __call__(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None,
                  out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
-        """x [rows, in] in the compute dtype. With ``residual`` (float32 [rows, out]) the result is
+        """x [rows, in] in the compute dtype (or a DeferredNorm of float32 rows). With ``residual`` (float32 [rows, out]) the result is
         float32 and is written over ``residual``. Otherwise the result has ``out_dtype`` (default:
         the compute dtype)."""
+        from .base import DeferredNorm
         out = residual
         if residual is not None:
             out_dtype = torch.float32
@@ -34,4 +35,6 @@ class Linear:
             y = fast_ops.linear(x, self.weight, self.bias, residual, out_dtype or self.rt.dtype, out)
             if y is not None:
                 return y
+        if isinstance(x, DeferredNorm):
+            x = x.materialize()
         return ops.linear_plain(x, self.weight, self.bias, residual, out_dtype or self.rt.dtype, out)

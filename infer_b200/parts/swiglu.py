@@ -13,6 +13,8 @@ from .linear import Linear
 
 @register_feed_forward("swiglu")
 class SwiGLU(FeedForward):
+    accepts_deferred_norm = True
+
     def __init__(self, spec: PartSpec, runtime):
         super().__init__(spec, runtime)
         self.hidden, self.inter = int(spec["hidden_size"]), int(spec["intermediate_size"])
@@ -44,5 +46,5 @@ class SwiGLU(FeedForward):
             from .. import fast_ops
             act = fast_ops.gate_up_swiglu(x, self.gate_up.weight)
         if act is None:
-            act = ops.swiglu(self.gate_up(x), self.interleaved)
+            act = ops.swiglu(self.gate_up(x), self.interleaved)      # Linear materialises a deferred norm
         return self.down(act, residual=residual)

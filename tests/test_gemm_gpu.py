@@ -140,3 +140,26 @@ def test_fused_swiglu_matches_the_two_kernels(M, I, H):
         assert got is not None and got.shape == (M, I)
         assert ((got.float() - ref).abs() <= ref.abs() * 2 ** -7 + 1e-4 * ref.abs().max()).all(), fn.__name__
     assert fast_ops.device_state(DEV).status.item() == 0
+
+
+@pytest.mark.parametrize("M", [1, 8, 11, 16])
+@pytest.mark.parametrize("N,K", [(2048, 1536), (96, 64), (301, 80), (448, 96)])
+def test_skinny_with_fused_norm(M, N, K):
+    """The streaming kernel normalising the float32 rows itself against norm kernel + plain product."""
+    from infer_b200 import fast_ops, ops
+    g = torch.Generator(device=DEV).manual_seed(M * N + K)
+    h = torch.randn(M, K, device=DEV, generator=g) * 3
+    nw = 1 + 0.1 * torch.randn(K, device=DEV, generator=g)
+    w = (torch.randn(N, K, device=DEV, generator=g) * 0.05).bfloat16()
+    bias = torch.randn(N, device=DEV, generator=g)
+    x = ops.rmsnorm(h, nw, 1e-5, torch.bfloat16)
+    ref = ops.linear_plain(x, w, bias, None, torch.float32)
+    got = fast_ops.linear_skinny(h, w, bias, None, torch.float32, norm_weight=nw, norm_eps=1e-5)
+    assert got is not None
+    cond = x.float().abs() @ w.float().abs().T + 1.0
+    # the normalised rows may differ from the norm kernel's by one bfloat16 rounding where a value sits on a tie
+    assert ((got - ref).abs() / cond).max().item() < 2e-4
+    if N % 16 == 0:
+        act = fast_ops.linear_skinny(h, w, None, None, torch.bfloat16, swiglu=True, norm_weight=nw, norm_eps=1e-5)
+        two = ops.swiglu(ops.linear_plain(x, w), interleave8=True)
+        assert (act.float() - two.float()).abs().max() <= 0.03 * two.float().abs().max() + 1e-3
