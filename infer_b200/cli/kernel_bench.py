@@ -61,6 +61,7 @@ def main(argv=None) -> int:
     ap.add_argument("--head-dim", type=int, default=128)
     ap.add_argument("--splits", type=int, default=0)
     ap.add_argument("--cluster", type=int, default=0)
+    ap.add_argument("--fused", action="store_true", help="attention: the decode kernel that also rotates and stores k/v")
     ap.add_argument("--norm", action="store_true", help="skinny kernel with the fused RMSNorm prologue")
     ap.add_argument("--reps", type=int, default=50)
     args = ap.parse_args(argv)
@@ -115,7 +116,13 @@ def main(argv=None) -> int:
         seg_start = torch.arange(0, (B + 1) * q_len, q_len, dtype=torch.int32, device=dev)
         pos0 = torch.full((B,), ctx, dtype=torch.int32, device=dev)
 
+        qkv = torch.randn(B * q_len, (nh + 2 * nkv) * hd, device=dev).bfloat16()
+        cos, sin = torch.rand(ctx + q_len + 1, hd // 2, device=dev), torch.rand(ctx + q_len + 1, hd // 2, device=dev)
+
         def run(i):
+            if args.fused:
+                return fast_ops.attention_decode_fused(qkv, cos, sin, ks[i], vs[i], table, seg_start, pos0, nh, nkv, hd, None,
+                                                       1 / math.sqrt(hd), ctx + 1, True, args.splits or None)
             return fast_ops.attention_fast(q, ks[i], vs[i], table, seg_start, pos0, nh, nkv, hd, None, 1 / math.sqrt(hd),
                                            q_len == 1, q_len, ctx + q_len, B, args.splits or None)
         med, mn = _time(run, n_layers, args.reps)

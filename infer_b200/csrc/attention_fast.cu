@@ -20,6 +20,8 @@
 // cache contents can never reach a sum. Page ids outside the pool raise the status word and read as zeros.
 #include "common.cuh"
 
+#include <cooperative_groups.h>
+
 IB_DEFINE_LAST_ERROR()
 
 #ifndef IB_HEAD_DIM
@@ -28,6 +30,7 @@ IB_DEFINE_LAST_ERROR()
 
 namespace {
 
+namespace cg = cooperative_groups;
 using bf16 = __nv_bfloat16;
 
 constexpr int HD = IB_HEAD_DIM;
@@ -39,11 +42,11 @@ constexpr int KS = HD / 16;                     // k-steps over the head dimensi
 constexpr float LOG2E = 1.4426950408889634f;
 
 constexpr int DEC_WARPS = 4, DEC_STAGES = 3;
-constexpr int MAX_SPLITS = 64;                  // slices of the key range per (segment, kv head)
+constexpr int MAX_SPLITS = 8;                   // slices of the key range per (segment, kv head) = cluster size
 constexpr int DEC_STAGE_BYTES = 2 * PAGE * ROW_BYTES;                       // K page + V page
 constexpr int DEC_SMEM = DEC_WARPS * DEC_STAGES * DEC_STAGE_BYTES;
 constexpr int DEC_MERGE_BYTES = DEC_WARPS * (16 * HD + 32) * 4;
-static_assert(DEC_MERGE_BYTES <= DEC_SMEM && 16 * MAX_SPLITS * 4 <= DEC_SMEM, "merge areas must fit the stage area");
+static_assert(DEC_MERGE_BYTES <= DEC_SMEM, "merge area must fit the stage area");
 
 constexpr int PF_BM = 64, PF_BN = 64, PF_WARPS = 4;
 constexpr int PF_TILE_BYTES = PF_BN * ROW_BYTES;
@@ -51,6 +54,7 @@ constexpr int PF_SMEM = PF_BM * ROW_BYTES + 2 * 2 * PF_TILE_BYTES;          // Q
 
 struct AttnParams {
     const bf16* q; const bf16* k_cache; const bf16* v_cache; bf16* out;
+    const bf16* qkv; const float* cos; const float* sin; bf16* k_cache_w; bf16* v_cache_w; int write_cache;   // fused decode
     const int* block_table; int max_blocks;
     const int* seg_start; const int* seg_pos0;
     int n_heads, n_kv, group, window;
@@ -171,31 +175,62 @@ __device__ __forceinline__ void pv_tile(float (*o)[4], const float (*s)[4], uint
 }
 
 // ================================================================================================ decode
+//
+// Grid (slices, kv heads, segments); the slices of one (segment, kv head) form a thread-block cluster, and their
+// partial results (running maximum, sum, unnormalised output per head of the group) are merged through distributed
+// shared memory: each CTA of the cluster combines its share of the output elements from all ranks, in rank order.
+//
+// FUSED: the kernel reads the packed projection rows [q | k | v] itself, rotates q in registers (half-split rotation:
+// element j pairs with j + HD/2, both in the same thread's fragments when HD/2 is a multiple of 16), and the warp that
+// owns the page of the new position rotates k, puts k and v into its shared-memory copy of the page and into the
+// cache: one launch instead of two.
 
+template <bool FUSED>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
 attn_decode_kernel(const AttnParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
-    __shared__ unsigned int is_last;
+    __shared__ float wgt[MAX_SPLITS][16];                // weight of every rank's partial, per head of the group
     ib::pdl_wait();
-    const int seg = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    const int split = blockIdx.x, kvh = blockIdx.y, seg = blockIdx.z;
+    const int n_splits = gridDim.x;
     const int t = p.seg_start[seg];
-    if (p.seg_start[seg + 1] - t != 1) return;
+    const bool is_decode = p.seg_start[seg + 1] - t == 1;         // uniform over the cluster
+    if (!is_decode) return;
     const int pos = p.seg_pos0[seg];
     const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
     const int first_page = lo / PAGE, last_page = pos / PAGE;
     const int n_pg = last_page - first_page + 1;
-    const int pps = (n_pg + p.n_splits - 1) / p.n_splits;
-    const int n_eff = (n_pg + pps - 1) / pps;
-    if (split >= n_eff) return;
-    const int pg_begin = first_page + split * pps, pg_end = min(last_page + 1, pg_begin + pps);
+    const int pps = (n_pg + n_splits - 1) / n_splits;
+    const int pg_begin = min(last_page + 1, first_page + split * pps), pg_end = min(last_page + 1, pg_begin + pps);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t4 = lane & 3;
     const int* table = p.block_table + int64_t(seg) * p.max_blocks;
     const int G = p.group;
+    const int64_t qkv_row = int64_t(t) * (p.n_heads + 2 * p.n_kv) * HD;
 
     // Query fragments straight from global memory: tile row = head within the group, zero beyond it.
     uint32_t qf[KS][4];
-    {
+    if constexpr (FUSED) {
+        const bf16* qb = p.qkv + qkv_row + int64_t(kvh) * G * HD;
+        const float* cs = p.cos + int64_t(pos) * (HD / 2);
+        const float* sn = p.sin + int64_t(pos) * (HD / 2);
+#pragma unroll
+        for (int ks = 0; ks < KS / 2; ks++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const int row = g + (e & 1) * 8, d = ks * 16 + t4 * 2 + (e >> 1) * 8;      // d < HD/2
+                if (row < G) {
+                    const float2 x1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(qb + row * HD + d));
+                    const float2 x2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(qb + row * HD + d + HD / 2));
+                    const float2 c = *reinterpret_cast<const float2*>(cs + d), sv = *reinterpret_cast<const float2*>(sn + d);
+                    qf[ks][e] = pack_bf16(x1.x * c.x - x2.x * sv.x, x1.y * c.y - x2.y * sv.y);
+                    qf[ks + KS / 2][e] = pack_bf16(x2.x * c.x + x1.x * sv.x, x2.y * c.y + x1.y * sv.y);
+                } else {
+                    qf[ks][e] = 0u;
+                    qf[ks + KS / 2][e] = 0u;
+                }
+            }
+    } else {
         const bf16* qb = p.q + (int64_t(t) * p.n_heads + int64_t(kvh) * G) * HD;
 #pragma unroll
         for (int ks = 0; ks < KS; ks++) {
@@ -206,7 +241,8 @@ attn_decode_kernel(const AttnParams p) {
             qf[ks][3] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(qb + (g + 8) * HD + d + 8) : 0u;
         }
     }
-    const uint32_t my_smem = smem_u32(smem) + warp * DEC_STAGES * DEC_STAGE_BYTES;
+    uint8_t* my_ptr = smem + warp * DEC_STAGES * DEC_STAGE_BYTES;
+    const uint32_t my_smem = smem_u32(my_ptr);
     const int my_pages = pg_end > pg_begin + warp ? (pg_end - pg_begin - warp + DEC_WARPS - 1) / DEC_WARPS : 0;
 
     auto issue = [&](int i) {
@@ -220,7 +256,8 @@ attn_decode_kernel(const AttnParams p) {
             for (int c = lane; c < PAGE * CHUNKS; c += 32) {
                 const int row = c / CHUNKS, col = c % CHUNKS;
                 const int key = pg * PAGE + row;
-                const int bytes = (page >= 0 && key <= pos) ? 16 : 0;          // rows not written yet read as zeros
+                // rows not written yet read as zeros (with FUSED the row of `pos` itself comes from the projections)
+                const int bytes = (page >= 0 && (FUSED && p.write_cache ? key < pos : key <= pos)) ? 16 : 0;
                 cp_async16(dst + row * ROW_BYTES + col * 16, p.k_cache + base + row * HD + col * 8, bytes);
                 cp_async16(dst + PAGE * ROW_BYTES + row * ROW_BYTES + col * 16, p.v_cache + base + row * HD + col * 8, bytes);
             }
@@ -238,8 +275,39 @@ attn_decode_kernel(const AttnParams p) {
     for (int i = 0; i < my_pages; i++) {
         cp_wait<DEC_STAGES - 2>();
         __syncwarp();
-        const uint32_t k_smem = my_smem + (i % DEC_STAGES) * DEC_STAGE_BYTES, v_smem = k_smem + PAGE * ROW_BYTES;
-        const int key0 = (pg_begin + warp + i * DEC_WARPS) * PAGE;
+        uint8_t* stage = my_ptr + (i % DEC_STAGES) * DEC_STAGE_BYTES;
+        const uint32_t k_smem = smem_u32(stage), v_smem = k_smem + PAGE * ROW_BYTES;
+        const int pg = pg_begin + warp + i * DEC_WARPS;
+        const int key0 = pg * PAGE;
+        if constexpr (FUSED) {
+            if (p.write_cache && pg == last_page) {
+                // The new position: rotate k, store k and v into this page's shared-memory copy and into the cache.
+                const int page = table[pg];
+                const int row = pos - key0;
+                const bf16* kb = p.qkv + qkv_row + (int64_t(p.n_heads) + kvh) * HD;
+                const bf16* vb = p.qkv + qkv_row + (int64_t(p.n_heads) + p.n_kv + kvh) * HD;
+                const float* cs = p.cos + int64_t(pos) * (HD / 2);
+                const float* sn = p.sin + int64_t(pos) * (HD / 2);
+                bf16* ks_row = reinterpret_cast<bf16*>(stage + row * ROW_BYTES);
+                bf16* vs_row = reinterpret_cast<bf16*>(stage + PAGE * ROW_BYTES + row * ROW_BYTES);
+                const bool page_ok = page >= 0 && page < p.n_pages;
+                if (!page_ok && lane == 0) atomicExch(p.status, 2);
+                const int64_t gbase = page_ok ? ((int64_t(page) * p.n_kv + kvh) * PAGE + row) * HD : 0;
+                for (int j = lane; j < HD / 2; j += 32) {
+                    const float x1 = __bfloat162float(kb[j]), x2 = __bfloat162float(kb[j + HD / 2]);
+                    const bf16 r1 = __float2bfloat16_rn(x1 * cs[j] - x2 * sn[j]);
+                    const bf16 r2 = __float2bfloat16_rn(x2 * cs[j] + x1 * sn[j]);
+                    const bf16 v1 = vb[j], v2 = vb[j + HD / 2];
+                    ks_row[j] = r1; ks_row[j + HD / 2] = r2;
+                    vs_row[j] = v1; vs_row[j + HD / 2] = v2;
+                    if (page_ok) {
+                        p.k_cache_w[gbase + j] = r1; p.k_cache_w[gbase + j + HD / 2] = r2;
+                        p.v_cache_w[gbase + j] = v1; p.v_cache_w[gbase + j + HD / 2] = v2;
+                    }
+                }
+                __syncwarp();
+            }
+        }
         float s[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
         qk_tile<2>(s, qf, k_smem);
         softmax_update<2, HD / 8>(s, m, l, o, p.scale_log2, [&](int, int key) { return key0 + key >= lo && key0 + key <= pos; });
@@ -255,8 +323,8 @@ attn_decode_kernel(const AttnParams p) {
         l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
     }
     __syncthreads();                                     // every warp is done with its stages: reuse them for the merge
-    float* mo = reinterpret_cast<float*>(smem);          // [warp][16][HD]
-    float* mml = mo + DEC_WARPS * 16 * HD;               // [warp][16][2]
+    float* mo = reinterpret_cast<float*>(smem);          // [warp][16][HD], after the CTA merge: [0][16][HD] holds the CTA's sum
+    float* mml = mo + DEC_WARPS * 16 * HD;               // [warp][16][2]; after the CTA merge [0][16][2]
 #pragma unroll
     for (int n = 0; n < HD / 8; n++) {
         float* b = mo + (warp * 16) * HD + n * 8 + t4 * 2;
@@ -268,78 +336,83 @@ attn_decode_kernel(const AttnParams p) {
         mml[(warp * 16 + g + 8) * 2] = m[1]; mml[(warp * 16 + g + 8) * 2 + 1] = l[1];
     }
     __syncthreads();
-    const int64_t unit = int64_t(seg) * p.n_kv + kvh;
-    float* ws_o = p.workspace + (unit * p.n_splits + split) * (16 * HD + 32);
-    float* ws_ml = ws_o + 16 * HD;
-    for (int idx = threadIdx.x; idx < G * HD; idx += DEC_WARPS * 32) {
-        const int row = idx / HD, d = idx - row * HD;
-        float M = -INFINITY;
+    // Merge of the CTA's four warps, kept in registers until every thread has read what it needs.
+    float cta_val[(16 * HD + DEC_WARPS * 32 - 1) / (DEC_WARPS * 32)];
+    float cta_m = -INFINITY, cta_l = 0.0f;
+    {
+        int e = 0;
+        for (int idx = threadIdx.x; idx < G * HD; idx += DEC_WARPS * 32, e++) {
+            const int row = idx / HD, d = idx - row * HD;
+            float M = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < DEC_WARPS; w++) M = fmaxf(M, mml[(w * 16 + row) * 2]);
-        const float Ms = M == -INFINITY ? 0.0f : M;
-        float L = 0.0f, acc = 0.0f;
+            for (int w = 0; w < DEC_WARPS; w++) M = fmaxf(M, mml[(w * 16 + row) * 2]);
+            const float Ms = M == -INFINITY ? 0.0f : M;
+            float acc = 0.0f;
 #pragma unroll
-        for (int w = 0; w < DEC_WARPS; w++) {
-            const float f = exp2f(mml[(w * 16 + row) * 2] - Ms);
-            L += mml[(w * 16 + row) * 2 + 1] * f;
-            acc += mo[(w * 16 + row) * HD + d] * f;
+            for (int w = 0; w < DEC_WARPS; w++) acc += mo[(w * 16 + row) * HD + d] * exp2f(mml[(w * 16 + row) * 2] - Ms);
+            cta_val[e] = acc;
         }
-        if (n_eff == 1) {
-            p.out[(int64_t(t) * p.n_heads + int64_t(kvh) * G + row) * HD + d] = __float2bfloat16_rn(L > 0.0f ? acc / L : 0.0f);
-        } else {
-            ws_o[row * HD + d] = acc;
-            if (d == 0) { ws_ml[row * 2] = M; ws_ml[row * 2 + 1] = L; }
+        if (threadIdx.x < G) {
+            const int row = threadIdx.x;
+#pragma unroll
+            for (int w = 0; w < DEC_WARPS; w++) cta_m = fmaxf(cta_m, mml[(w * 16 + row) * 2]);
+            const float Ms = cta_m == -INFINITY ? 0.0f : cta_m;
+#pragma unroll
+            for (int w = 0; w < DEC_WARPS; w++) cta_l += mml[(w * 16 + row) * 2 + 1] * exp2f(mml[(w * 16 + row) * 2] - Ms);
         }
     }
-    if (n_eff == 1) return;
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        const unsigned int prev = atomicAdd(p.counters + unit, 1u);
-        is_last = prev == unsigned(n_eff - 1) ? 1u : 0u;
-        if (is_last) p.counters[unit] = 0;
+    bf16* out_row = p.out + (int64_t(t) * p.n_heads + int64_t(kvh) * G) * HD;
+    if (n_splits == 1) {
+        __shared__ float inv_l[16];
+        if (threadIdx.x < G) inv_l[threadIdx.x] = cta_l > 0.0f ? 1.0f / cta_l : 0.0f;
+        __syncthreads();
+        int e = 0;
+        for (int idx = threadIdx.x; idx < G * HD; idx += DEC_WARPS * 32, e++) out_row[idx] = __float2bfloat16_rn(cta_val[e] * inv_l[idx / HD]);
+        return;
     }
-    __syncthreads();
-    if (!is_last) return;
-    __threadfence();
-    // Merge of the slices. Per head of the group one warp reads every slice's (max, sum) at once (lanes = slices),
-    // reduces them with shuffles in a fixed order and leaves the weight of each slice, already divided by the total
-    // sum, in shared memory. Then each thread adds its output element over the slices, eight loads in flight.
-    const float* base = p.workspace + unit * p.n_splits * (16 * HD + 32);
-    float* wgt = reinterpret_cast<float*>(smem);                    // [16][MAX_SPLITS]
-    for (int row = warp; row < G; row += DEC_WARPS) {
-        float mz[MAX_SPLITS / 32], lz[MAX_SPLITS / 32], M = -INFINITY;
+    __syncthreads();                                     // all reads of the per-warp areas are done
+    {
+        int e = 0;
+        for (int idx = threadIdx.x; idx < G * HD; idx += DEC_WARPS * 32, e++) mo[idx] = cta_val[e];
+        if (threadIdx.x < G) { mml[threadIdx.x * 2] = cta_m; mml[threadIdx.x * 2 + 1] = cta_l; }
+    }
+    cg::cluster_group cl = cg::this_cluster();
+    cl.sync();
+    // Weights of the ranks' partials: exp2(m_r - M) / sum_r l_r exp2(m_r - M), per head, from every rank's (m, l).
+    if (threadIdx.x < G) {
+        const int row = threadIdx.x;
+        float mr[MAX_SPLITS], lr[MAX_SPLITS], M = -INFINITY;
 #pragma unroll
-        for (int i = 0; i < MAX_SPLITS / 32; i++) {
-            const int z = lane + 32 * i;
-            mz[i] = z < n_eff ? __ldcg(base + z * (16 * HD + 32) + 16 * HD + row * 2) : -INFINITY;
-            lz[i] = z < n_eff ? __ldcg(base + z * (16 * HD + 32) + 16 * HD + row * 2 + 1) : 0.0f;
-            M = fmaxf(M, mz[i]);
+        for (int r = 0; r < MAX_SPLITS; r++) {
+            if (r < n_splits) {
+                const float* rml = cl.map_shared_rank(mml, r);
+                mr[r] = rml[row * 2]; lr[r] = rml[row * 2 + 1];
+            } else { mr[r] = -INFINITY; lr[r] = 0.0f; }
+            M = fmaxf(M, mr[r]);
         }
-        M = ib::warp_max(M);
         const float Ms = M == -INFINITY ? 0.0f : M;
         float L = 0.0f;
 #pragma unroll
-        for (int i = 0; i < MAX_SPLITS / 32; i++) { mz[i] = exp2f(mz[i] - Ms); L += lz[i] * mz[i]; }
-        L = ib::warp_sum(L);
+        for (int r = 0; r < MAX_SPLITS; r++) { mr[r] = exp2f(mr[r] - Ms); L += lr[r] * mr[r]; }
         const float inv = L > 0.0f ? 1.0f / L : 0.0f;
 #pragma unroll
-        for (int i = 0; i < MAX_SPLITS / 32; i++) wgt[row * MAX_SPLITS + lane + 32 * i] = mz[i] * inv;
+        for (int r = 0; r < MAX_SPLITS; r++) wgt[r][row] = mr[r] * inv;
     }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < G * HD; idx += DEC_WARPS * 32) {
-        const int row = idx / HD, d = idx - row * HD;
+    // Each rank combines its share of the G * HD output elements from all ranks, in rank order.
+    const int total = G * HD, share = (total + n_splits - 1) / n_splits;
+    const int e_begin = split * share, e_end = min(total, e_begin + share);
+    for (int idx = e_begin + threadIdx.x; idx < e_end; idx += DEC_WARPS * 32) {
+        const int row = idx / HD;
+        float v[MAX_SPLITS];
+#pragma unroll
+        for (int r = 0; r < MAX_SPLITS; r++) v[r] = r < n_splits ? cl.map_shared_rank(mo, r)[idx] : 0.0f;
         float acc = 0.0f;
-        for (int z0 = 0; z0 < n_eff; z0 += 8) {
-            float v[8];
 #pragma unroll
-            for (int zz = 0; zz < 8; zz++)
-                v[zz] = z0 + zz < n_eff ? __ldcg(base + (z0 + zz) * (16 * HD + 32) + row * HD + d) : 0.0f;
-#pragma unroll
-            for (int zz = 0; zz < 8; zz++) acc += v[zz] * wgt[row * MAX_SPLITS + min(z0 + zz, MAX_SPLITS - 1)];
-        }
-        p.out[(int64_t(t) * p.n_heads + int64_t(kvh) * G + row) * HD + d] = __float2bfloat16_rn(acc);
+        for (int r = 0; r < MAX_SPLITS; r++) acc += v[r] * wgt[r][row];
+        out_row[idx] = __float2bfloat16_rn(acc);
     }
+    cl.sync();                                           // shared memory of every rank stays alive until all have read
 }
 
 // ================================================================================================ prefill
@@ -452,45 +525,54 @@ attn_prefill_kernel(const AttnParams p) {
 
 IB_EXPORT int ib_attention_head_dim() { return HD; }
 
-// Floats of workspace and counters a call needs for `n_segments` segments and `n_splits` slices.
-IB_EXPORT int64_t ib_attention_workspace_floats(int64_t n_segments, int n_kv, int n_splits) {
-    return n_segments * n_kv * int64_t(n_splits) * (16 * HD + 32);
-}
+namespace {
 
-// Attention for every segment of a step. q/out [tokens, heads*HD] bfloat16; caches [pages, kv_heads, 16, HD] bfloat16;
-// seg_start [S+1], seg_pos0 [S], block_table [S, max_blocks] int32. has_decode / max_q_len tell which kernels to
-// launch (a kernel skips segments of the other kind). counters: S * kv_heads zeroed words (left zeroed).
-IB_EXPORT int ib_attention_fast(const void* q, const void* k_cache, const void* v_cache, void* out, const int* block_table,
-                                int max_blocks, const int* seg_start, const int* seg_pos0, int n_segments, int n_heads,
-                                int n_kv, int head_dim, int page_size, int window, float scale, int64_t n_pages,
-                                int has_decode, int max_q_len, int n_splits, float* workspace, unsigned int* counters,
-                                int* status, cudaStream_t stream) {
-    if (n_segments <= 0) return IB_OK;
+int check_common(int n_segments, int n_heads, int n_kv, int head_dim, int page_size, int n_splits, const int* status) {
     if (head_dim != HD) return ib::fail(IB_ERR_ARG, "attention_fast: built for head_dim %d, called with %d", HD, head_dim);
     if (page_size != PAGE) return ib::fail(IB_ERR_ARG, "attention_fast: pages must hold %d positions, got %d", PAGE, page_size);
     if (n_kv <= 0 || n_heads % n_kv) return ib::fail(IB_ERR_ARG, "attention_fast: heads %d not a multiple of kv heads %d", n_heads, n_kv);
     if (n_heads / n_kv > 16) return ib::fail(IB_ERR_ARG, "attention_fast: more than 16 query heads per kv head");
     if (n_heads > 65535 || n_segments > 65535) return ib::fail(IB_ERR_ARG, "attention_fast: too many heads or segments");
-    if (n_splits < 1) n_splits = 1;
-    if (n_splits > MAX_SPLITS) return ib::fail(IB_ERR_ARG, "attention_fast: at most %d splits", MAX_SPLITS);
+    if (n_splits != 1 && n_splits != 2 && n_splits != 4 && n_splits != 8) return ib::fail(IB_ERR_ARG, "attention_fast: splits must be 1, 2, 4 or 8");
     if (!status) return ib::fail(IB_ERR_ARG, "attention_fast: a status word is required");
-    AttnParams p;
-    p.q = (const bf16*)q; p.k_cache = (const bf16*)k_cache; p.v_cache = (const bf16*)v_cache; p.out = (bf16*)out;
-    p.block_table = block_table; p.max_blocks = max_blocks; p.seg_start = seg_start; p.seg_pos0 = seg_pos0;
-    p.n_heads = n_heads; p.n_kv = n_kv; p.group = n_heads / n_kv; p.window = window;
-    p.scale_log2 = scale * LOG2E; p.n_pages = n_pages; p.n_splits = n_splits;
-    p.workspace = workspace; p.counters = counters; p.status = status;
+    return IB_OK;
+}
+
+int configure() {
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM);
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM);
         if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM);
         if (e != cudaSuccess) return ib::fail(IB_ERR_CUDA, "attention_fast: cannot set shared memory size: %s", cudaGetErrorString(e));
         configured = true;
     }
+    return IB_OK;
+}
+
+}  // namespace
+
+// Attention for every segment of a step. q/out [tokens, heads*HD] bfloat16; caches [pages, kv_heads, 16, HD] bfloat16;
+// seg_start [S+1], seg_pos0 [S], block_table [S, max_blocks] int32. has_decode / max_q_len tell which kernels to
+// launch (a kernel skips segments of the other kind). n_splits: slices per (segment, kv head) of the decode kernel,
+// 1, 2, 4 or 8 (they form a thread-block cluster).
+IB_EXPORT int ib_attention_fast(const void* q, const void* k_cache, const void* v_cache, void* out, const int* block_table,
+                                int max_blocks, const int* seg_start, const int* seg_pos0, int n_segments, int n_heads,
+                                int n_kv, int head_dim, int page_size, int window, float scale, int64_t n_pages,
+                                int has_decode, int max_q_len, int n_splits, int* status, cudaStream_t stream) {
+    if (n_segments <= 0) return IB_OK;
+    int rc = check_common(n_segments, n_heads, n_kv, head_dim, page_size, n_splits, status);
+    if (rc) return rc;
+    AttnParams p = {};
+    p.q = (const bf16*)q; p.k_cache = (const bf16*)k_cache; p.v_cache = (const bf16*)v_cache; p.out = (bf16*)out;
+    p.block_table = block_table; p.max_blocks = max_blocks; p.seg_start = seg_start; p.seg_pos0 = seg_pos0;
+    p.n_heads = n_heads; p.n_kv = n_kv; p.group = n_heads / n_kv; p.window = window;
+    p.scale_log2 = scale * LOG2E; p.n_pages = n_pages; p.n_splits = n_splits; p.status = status;
+    if ((rc = configure())) return rc;
     if (has_decode) {
-        if (n_splits > 1 && (!workspace || !counters)) return ib::fail(IB_ERR_ARG, "attention_fast: splits need a workspace and counters");
-        const dim3 grid{unsigned(n_segments), unsigned(n_kv), unsigned(n_splits)};
-        int rc = ib::launch("attention_fast (decode)", attn_decode_kernel, grid, dim3(DEC_WARPS * 32), size_t(DEC_SMEM), stream, 1u, p);
+        const dim3 grid{unsigned(n_splits), unsigned(n_kv), unsigned(n_segments)};
+        rc = ib::launch("attention_fast (decode)", attn_decode_kernel<false>, grid, dim3(DEC_WARPS * 32), size_t(DEC_SMEM), stream,
+                        unsigned(n_splits), p);
         if (rc) return rc;
     }
     if (max_q_len > 1) {
@@ -498,4 +580,31 @@ IB_EXPORT int ib_attention_fast(const void* q, const void* k_cache, const void* 
         return ib::launch("attention_fast (prefill)", attn_prefill_kernel, grid, dim3(PF_WARPS * 32), size_t(PF_SMEM), stream, 1u, p);
     }
     return IB_OK;
+}
+
+// Decode-only steps (every segment one token): rotation of q and k, the cache write of the new position and the
+// attention in one launch. qkv [tokens, (heads + 2 kv_heads) * HD] bfloat16 packed [q | k | v] rows with the bias
+// already added; cos/sin float [positions, HD/2]; caches are written (write_cache != 0) and read. HD/2 must be a
+// multiple of 16.
+IB_EXPORT int ib_attention_decode_fused(const void* qkv, const float* cos_t, const float* sin_t, void* k_cache, void* v_cache,
+                                        void* out, const int* block_table, int max_blocks, const int* seg_start,
+                                        const int* seg_pos0, int n_segments, int n_heads, int n_kv, int head_dim,
+                                        int page_size, int window, float scale, int64_t n_pages, int write_cache,
+                                        int n_splits, int* status, cudaStream_t stream) {
+    if (n_segments <= 0) return IB_OK;
+    int rc = check_common(n_segments, n_heads, n_kv, head_dim, page_size, n_splits, status);
+    if (rc) return rc;
+    if ((HD / 2) % 16) return ib::fail(IB_ERR_ARG, "attention_decode_fused: head_dim/2 must be a multiple of 16, head_dim is %d", HD);
+    if (!cos_t || !sin_t) return ib::fail(IB_ERR_ARG, "attention_decode_fused: rotation tables are required");
+    AttnParams p = {};
+    p.qkv = (const bf16*)qkv; p.cos = cos_t; p.sin = sin_t; p.write_cache = write_cache ? 1 : 0;
+    p.k_cache = (const bf16*)k_cache; p.v_cache = (const bf16*)v_cache; p.k_cache_w = (bf16*)k_cache; p.v_cache_w = (bf16*)v_cache;
+    p.out = (bf16*)out;
+    p.block_table = block_table; p.max_blocks = max_blocks; p.seg_start = seg_start; p.seg_pos0 = seg_pos0;
+    p.n_heads = n_heads; p.n_kv = n_kv; p.group = n_heads / n_kv; p.window = window;
+    p.scale_log2 = scale * LOG2E; p.n_pages = n_pages; p.n_splits = n_splits; p.status = status;
+    if ((rc = configure())) return rc;
+    const dim3 grid{unsigned(n_splits), unsigned(n_kv), unsigned(n_segments)};
+    return ib::launch("attention_decode_fused", attn_decode_kernel<true>, grid, dim3(DEC_WARPS * 32), size_t(DEC_SMEM), stream,
+                      unsigned(n_splits), p);
 }

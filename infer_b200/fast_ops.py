@@ -174,6 +174,17 @@ def attention_supported(n_heads: int, n_kv: int, head_dim: int, page_size: int) 
     return head_dim % 16 == 0 and 16 <= head_dim <= 128 and page_size == 16 and n_heads // n_kv <= 16
 
 
+def _decode_splits(st, n_decode: int, n_kv: int, visible: int) -> int:
+    """Slices per (segment, kv head): a power of two up to 8 (they form a cluster), enough CTAs for about one per SM,
+    and at least 8 pages (two per warp) in a slice."""
+    units = max(1, n_decode * n_kv)
+    pages = max(1, -(-visible // 16))
+    n = 1
+    while n < 8 and units * n < st.sm_count and pages // (2 * n) >= 8:
+        n *= 2
+    return n
+
+
 def attention_fast(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
                    seg_start: torch.Tensor, seg_pos0: torch.Tensor, n_heads: int, n_kv: int, head_dim: int,
                    window: Optional[int], scale: float, has_decode: bool, max_q_len: int, max_ctx_len: int,
@@ -196,24 +207,55 @@ def attention_fast(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor
     _check(block_table, "block_table", torch.int32)
     st = device_state(q.device)
     if n_splits is None:
-        n_splits = 1
-        if has_decode:
-            units = max(1, (n_decode if n_decode is not None else S) * n_kv)
-            visible = min(max_ctx_len, window) if window else max_ctx_len
-            pages = max(1, -(-visible // 16))
-            # enough CTAs for two per SM, but at least 16 pages (4 per warp) in a slice
-            n_splits = max(1, min(-(-2 * st.sm_count // units), pages // 16, 64))
-    defines = {"IB_HEAD_DIM": head_dim}
-    ws = cnt = None
-    if has_decode and n_splits > 1:
-        ws = st.workspace(S * n_kv * n_splits * (16 * head_dim + 32))
-        cnt = st.counters(S * n_kv)
+        visible = min(max_ctx_len, window) if window else max_ctx_len
+        n_splits = _decode_splits(st, n_decode if n_decode is not None else S, n_kv, visible) if has_decode else 1
     out = torch.empty_like(q)
     f = _fn("attn", "ib_attention_fast", [c_void_p] * 5 + [c_int] + [c_void_p] * 2 + [c_int] * 6 + [c_float, c_int64] +
-            [c_int] * 3 + [c_void_p] * 4, defines)
+            [c_int] * 3 + [c_void_p] * 2, {"IB_HEAD_DIM": head_dim})
     _call(f, q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), block_table.data_ptr(),
           block_table.shape[1], seg_start.data_ptr(), seg_pos0.data_ptr(), S, n_heads, n_kv, head_dim, page_size,
-          int(window or 0), float(scale), n_pages, int(has_decode), int(max_q_len), int(n_splits), _ptr(ws), _ptr(cnt),
+          int(window or 0), float(scale), n_pages, int(has_decode), int(max_q_len), int(n_splits),
+          st.status.data_ptr(), _stream())
+    return out
+
+
+def decode_fused_supported(n_heads: int, n_kv: int, head_dim: int, page_size: int) -> bool:
+    return attention_supported(n_heads, n_kv, head_dim, page_size) and head_dim % 32 == 0
+
+
+def attention_decode_fused(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, k_cache: torch.Tensor,
+                           v_cache: torch.Tensor, block_table: torch.Tensor, seg_start: torch.Tensor,
+                           seg_pos0: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, window: Optional[int],
+                           scale: float, max_ctx_len: int, write_cache: bool = True,
+                           n_splits: Optional[int] = None) -> Optional[torch.Tensor]:
+    """Decode-only steps: rotation of q and k, the cache write of the new positions and attention in ONE kernel.
+    qkv [S, (heads + 2 kv) * head_dim] packed rows with the bias added. Returns [S, heads * head_dim]."""
+    n_pages, ckv, page_size, chd = k_cache.shape
+    if qkv.dtype != torch.bfloat16 or not decode_fused_supported(n_heads, n_kv, head_dim, page_size):
+        return None
+    S = seg_pos0.numel()
+    _check(qkv, "qkv", torch.bfloat16, (S, (n_heads + 2 * n_kv) * head_dim))
+    _check(k_cache, "k_cache", torch.bfloat16)
+    _check(v_cache, "v_cache", torch.bfloat16, k_cache.shape)
+    if ckv != n_kv or chd != head_dim:
+        raise KernelError(f"cache shape {tuple(k_cache.shape)} does not match kv_heads={n_kv}, head_dim={head_dim}")
+    _check(cos, "cos", torch.float32)
+    _check(sin, "sin", torch.float32, cos.shape)
+    if cos.shape[1] != head_dim // 2:
+        raise KernelError("rotary tables must be [max_positions, head_dim/2]")
+    _check(seg_start, "seg_start", torch.int32, (S + 1,))
+    _check(seg_pos0, "seg_pos0", torch.int32, (S,))
+    _check(block_table, "block_table", torch.int32)
+    st = device_state(qkv.device)
+    if n_splits is None:
+        visible = min(max_ctx_len, window) if window else max_ctx_len
+        n_splits = _decode_splits(st, S, n_kv, visible)
+    out = torch.empty((S, n_heads * head_dim), dtype=torch.bfloat16, device=qkv.device)
+    f = _fn("attn", "ib_attention_decode_fused", [c_void_p] * 7 + [c_int] + [c_void_p] * 2 + [c_int] * 6 + [c_float, c_int64] +
+            [c_int] * 2 + [c_void_p] * 2, {"IB_HEAD_DIM": head_dim})
+    _call(f, qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
+          block_table.data_ptr(), block_table.shape[1], seg_start.data_ptr(), seg_pos0.data_ptr(), S, n_heads, n_kv,
+          head_dim, page_size, int(window or 0), float(scale), n_pages, int(write_cache), int(n_splits),
           st.status.data_ptr(), _stream())
     return out
 

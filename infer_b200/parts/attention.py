@@ -75,6 +75,14 @@ class Attention(Mixer):
             k_view = qkv[:, self.n_heads * self.head_dim: (self.n_heads + self.n_kv) * self.head_dim].view(T, self.n_kv, self.head_dim)
             self.position.apply(q_view, k_view, step.positions)
         cos, sin = tables if tables is not None else (None, None)
+        if step.decode_only and cos is not None and self.rt.fast("rope") and self.rt.fast("attention"):
+            # one token per request: rotation, cache write and attention in one kernel
+            from .. import fast_ops
+            ctx = fast_ops.attention_decode_fused(qkv, cos, sin, cache.k, cache.v, table, step.seg_start, step.seg_pos0,
+                                                  self.n_heads, self.n_kv, self.head_dim, self.window, self.scale,
+                                                  step.max_ctx_len, write_cache)
+            if ctx is not None:
+                return self.o(ctx, residual=residual)
         if self.rt.fast("rope"):
             from .. import fast_ops
             q = fast_ops.rope_kv_write(qkv, cos, sin, step, table, cache, self.n_heads, self.n_kv, self.head_dim, write_cache)
