@@ -61,6 +61,7 @@ def main(argv=None) -> int:
     ap.add_argument("--head-dim", type=int, default=128)
     ap.add_argument("--splits", type=int, default=0)
     ap.add_argument("--cluster", type=int, default=0)
+    ap.add_argument("--regs", action="store_true", help="skinny: the register-streaming kernel instead of the bulk-copy one")
     ap.add_argument("--fused", action="store_true", help="attention: the decode kernel that also rotates and stores k/v")
     ap.add_argument("--norm", action="store_true", help="skinny kernel with the fused RMSNorm prologue")
     ap.add_argument("--reps", type=int, default=50)
@@ -91,7 +92,7 @@ def main(argv=None) -> int:
             if args.kernel == "skinny":
                 if args.norm:
                     return fast_ops.linear_skinny(hx, ws[i], None, r, odt, r, swiglu, args.cluster, nw, 1e-6)
-                return fast_ops.linear_skinny(x, ws[i], None, r, odt, r, swiglu, args.cluster)
+                return fast_ops.linear_skinny(x, ws[i], None, r, odt, r, swiglu, args.cluster, bulk=not args.regs)
             if args.kernel == "tc":
                 return fast_ops.gemm_tc(x, ws[i], None, r, odt, r, swiglu=swiglu, plan=plan)
             if args.kernel == "plain":

@@ -30,6 +30,7 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", 
 MODULES: Dict[str, str] = {
     "plain": "plain_ops.cu",
     "gemv": "gemv.cu",
+    "gemvb": "gemv_bulk.cu",
     "gemm": "gemm_tcgen05.cu",
     "attn": "attention_fast.cu",
 }

@@ -1,0 +1,334 @@
+// Streaming matrix product for decode steps, fed by bulk asynchronous copies:
+// out[M, N] = x[M, K] . w[N, K]^T with M <= 16 tokens.
+//
+// The kernel is bound by HBM bandwidth: the weights are read exactly once and everything is arranged so that as many
+// bytes as possible are in flight per SM without costing registers or issue slots.
+//
+// A tile is 16 output features. For small N a thread-block cluster of 2, 4 or 8 CTAs owns a tile and each CTA takes
+// a slice of K; for large N the grid is three CTAs per SM and a CTA walks over many tiles, its copy ring running ahead
+// into the next tile while the current one is reduced. A producer warp streams the tile's rows into a ring of shared-memory stages with bulk
+// asynchronous copies (cp.async.bulk, one per row and stage, completion counted on an mbarrier); eight consumer
+// warps wait for a stage, read weight fragments from it with conflict-free 16-byte loads, multiply them with the
+// tokens on mma.sync m16n8k16 (bfloat16 in, float accumulation; the tokens are the 8-wide operand) and hand the
+// stage back through a second mbarrier. Bytes in flight per SM = resident CTAs x stages x 16 KB.
+// The producer issues its first stages BEFORE the kernel waits for its predecessor (weights have no producer kernel),
+// and lets the successor be scheduled at once, so the weight stream continues across kernel boundaries.
+//
+// Partial tiles of the eight warps are added in shared memory in warp order; across a cluster the first CTA reads the
+// other CTAs' sums through distributed shared memory in rank order: no global scratch, no atomics, a result that
+// does not depend on timing. Every mbarrier wait is bounded; one that runs out raises the status word.
+//
+// Lane (g, t) of a warp holds elements [8t, 8t+8) of rows g and g+8 of a 32-element chunk. The two MMAs of a chunk
+// pair those elements in an order that differs from the natural k order, identically for weights and activations,
+// which leaves every dot product unchanged.
+//
+// Epilogues: (0) + bias -> bfloat16 or float; (1) + residual (float, may alias out) -> float; (2) SwiGLU for a
+// gate/up matrix whose rows are interleaved in blocks of 8 (rows 16b..16b+7 = gate features 8b..8b+7, rows
+// 16b+8..16b+15 = the matching up features): out[m, 8b + r] = silu(gate) * up, bfloat16 [M, N/2].
+// K must be a multiple of 8 (16-byte alignment of every row); anything else is refused.
+#include "common.cuh"
+
+#include <cooperative_groups.h>
+
+IB_DEFINE_LAST_ERROR()
+
+namespace {
+
+namespace cg = cooperative_groups;
+using bf16 = __nv_bfloat16;
+constexpr int WARPS = 8;                  // consumer warps; warp 8 is the producer
+constexpr int THREADS = (WARPS + 1) * 32;
+constexpr int ROWS = 16;
+constexpr int KC = 512;                   // elements of K per stage and row (1 KB)
+constexpr int PITCH = KC * 2 + 64;        // bytes between rows of a stage: consecutive rows start 16 banks apart
+constexpr int STAGE_BYTES = ROWS * PITCH;
+constexpr int NS = 4;                     // stages in the ring
+constexpr int SMEM_BYTES = NS * STAGE_BYTES;
+constexpr uint32_t SPIN_LIMIT = 1u << 22;
+constexpr int STATUS_TIMEOUT = 104;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return uint32_t(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait (about a second): false if the phase did not complete.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < SPIN_LIMIT; i++) {
+        if (mbar_test(bar, parity)) return true;
+        if (i > 2048) __nanosleep(64);
+    }
+    return false;
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void mma_bf16(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+struct GemvParams {
+    const bf16* x;            // [M, K]
+    const bf16* w;            // [N, K]
+    const float* bias;        // [N] or null
+    const float* residual;    // [M, N] or null
+    void* out;
+    int M;
+    int64_t N, K;
+    int cluster;              // CTAs per tile
+    int64_t tiles;
+    int groups;               // tile walkers in the grid (grid = groups * cluster); a walker takes every groups-th tile
+    int* status;
+};
+
+template <int NT, int EPI, typename TOut>
+__global__ void __launch_bounds__(THREADS)
+bulk_gemv_kernel(const GemvParams p) {
+    extern __shared__ __align__(128) uint8_t stages[];   // [NS][ROWS][PITCH]
+    __shared__ __align__(8) uint64_t bars[2 * NS];       // full[NS], empty[NS]
+    __shared__ float red[WARPS][NT][8][ROWS];
+    __shared__ float part[NT][8][ROWS];                  // this CTA's sum; read by the cluster's first CTA
+    __shared__ int failed;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int cluster = p.cluster;
+    const int rank = cluster > 1 ? int(blockIdx.x % cluster) : 0;
+    const int group = blockIdx.x / cluster;              // this CTA walks tiles group, group + groups, ...
+    const int64_t K = p.K, N = p.N;
+    // This CTA's slice of K, in stages of KC elements.
+    const int64_t total_stages = (K + KC - 1) / KC;
+    const int64_t per_cta = (total_stages + cluster - 1) / cluster;
+    const int64_t s_begin = min(total_stages, rank * per_cta), s_end = min(total_stages, s_begin + per_cta);
+    const int spt = int(s_end - s_begin);                // stages per tile
+    const int64_t my_tiles = group < p.tiles ? (p.tiles - group + p.groups - 1) / p.groups : 0;
+    const int64_t n_iter = my_tiles * spt;
+    const uint32_t stage0 = smem_u32(stages), bar0 = smem_u32(bars);
+    auto full_bar = [&](int s) { return bar0 + 8u * s; };
+    auto empty_bar = [&](int s) { return bar0 + 8u * (NS + s); };
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < NS; s++) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), WARPS); }
+        failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    // Rows beyond N (last tile only) are never copied: start from zeros. A stage that held an earlier tile's rows is
+    // harmless there, because those rows' results are not stored.
+    if (N % ROWS != 0 && (p.tiles - 1 - group) % p.groups == 0) {     // this CTA takes the last, partial tile
+        for (int i = threadIdx.x; i < SMEM_BYTES / 16; i += THREADS) reinterpret_cast<uint4*>(stages)[i] = make_uint4(0u, 0u, 0u, 0u);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+
+    if (warp == WARPS) {
+        // ---------------------------------------------------------------- producer: lane r copies row r of every stage
+        for (int64_t i = 0; i < n_iter; i++) {
+            const int s = int(i % NS);
+            if (i >= NS) {
+                int ok = 1;
+                if (lane == 0) ok = mbar_wait(empty_bar(s), uint32_t((i / NS) - 1) & 1u) ? 1 : 0;
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) { if (lane == 0) { atomicExch(p.status, STATUS_TIMEOUT); failed = 1; } break; }
+            }
+            const int64_t n0 = (group + (i / spt) * p.groups) * ROWS;
+            const int64_t k0 = (s_begin + i % spt) * KC;
+            const int live_rows = int(min(int64_t(ROWS), N - n0));
+            const uint32_t bytes = uint32_t(min(int64_t(KC), K - k0) * 2);
+            if (lane == 0) mbar_expect_tx(full_bar(s), bytes * uint32_t(live_rows));
+            __syncwarp();
+            if (lane < live_rows) bulk_load(stage0 + s * STAGE_BYTES + lane * PITCH, p.w + (n0 + lane) * K + k0, bytes, full_bar(s));
+            if (i == NS - 1 || i == n_iter - 1) ib::pdl_launch_dependents();     // the first ring is on its way
+        }
+        if (n_iter == 0) ib::pdl_launch_dependents();
+        if (cluster > 1) {                               // the cluster barriers below count every thread
+            cg::cluster_group cl = cg::this_cluster();
+            cl.sync();
+            cl.sync();
+        }
+        return;
+    }
+    // -------------------------------------------------------------------- consumers (warps 0..7)
+    ib::pdl_wait();                                      // activations come from the predecessor
+    bool x_ok[NT];
+    const bf16* xr[NT];
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) {
+        x_ok[nt] = nt * 8 + g < p.M;
+        xr[nt] = p.x + int64_t(nt * 8 + g) * K + t * 8;
+    }
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    constexpr int CPW = KC / 32 / WARPS;                 // 32-element chunks per warp and stage
+    float acc[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.0f;
+    const bool active = threadIdx.x < NT * 128;
+    const int r = threadIdx.x & 15, col = (threadIdx.x >> 4) & 7, ant = active ? threadIdx.x >> 7 : 0;
+    TOut* out = reinterpret_cast<TOut*>(p.out);
+
+    for (int64_t i = 0; i < n_iter; i++) {
+        const int s = int(i % NS);
+        const int64_t k0 = (s_begin + i % spt) * KC;
+        // activations of this warp's chunks: independent of the weights, so they are loaded before the wait
+        uint4 b[CPW][NT];
+        bool k_ok[CPW];
+#pragma unroll
+        for (int u = 0; u < CPW; u++) {
+            const int64_t k = k0 + (warp * CPW + u) * 32;
+            k_ok[u] = k + t * 8 < K;
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++)
+                b[u][nt] = (k_ok[u] && x_ok[nt]) ? __ldg(reinterpret_cast<const uint4*>(xr[nt] + k)) : zero;
+        }
+        if (!mbar_wait(full_bar(s), uint32_t(i / NS) & 1u)) {
+            if (lane == 0) { atomicExch(p.status, STATUS_TIMEOUT); failed = 1; }
+            break;
+        }
+        const uint8_t* st = stages + s * STAGE_BYTES;
+#pragma unroll
+        for (int u = 0; u < CPW; u++) {
+            const int cb = ((warp * CPW + u) * 32 + t * 8) * 2;
+            const uint4 a0 = k_ok[u] ? *reinterpret_cast<const uint4*>(st + g * PITCH + cb) : zero;
+            const uint4 a1 = k_ok[u] ? *reinterpret_cast<const uint4*>(st + (g + 8) * PITCH + cb) : zero;
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) {
+                mma_bf16(acc[nt], a0.x, a1.x, a0.y, a1.y, b[u][nt].x, b[u][nt].y);
+                mma_bf16(acc[nt], a0.z, a1.z, a0.w, a1.w, b[u][nt].z, b[u][nt].w);
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty_bar(s));
+        if ((i + 1) % spt != 0) continue;
+
+        // ---------------------------------------------------------------- the tile is complete
+        const int64_t tile = group + (i / spt) * p.groups;
+        const int64_t n0 = tile * ROWS;
+        asm volatile("bar.sync 1, 256;" ::: "memory");   // the previous tile's sums have been read (consumers only)
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+            red[warp][nt][2 * t][g] = acc[nt][0];
+            red[warp][nt][2 * t + 1][g] = acc[nt][1];
+            red[warp][nt][2 * t][g + 8] = acc[nt][2];
+            red[warp][nt][2 * t + 1][g + 8] = acc[nt][3];
+            acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.0f;
+        }
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        float v = 0.0f;
+        if (active) {
+#pragma unroll
+            for (int wi = 0; wi < WARPS; wi++) v += red[wi][ant][col][r];
+        }
+        bool writer = true;
+        if (cluster > 1) {
+            cg::cluster_group cl = cg::this_cluster();
+            if (active) part[ant][col][r] = v;
+            cl.sync();
+            if (rank == 0 && active) {
+                for (int other = 1; other < cluster; other++)
+                    v += cl.map_shared_rank(&part[0][0][0], other)[(ant * 8 + col) * ROWS + r];
+            }
+            cl.sync();                                   // the others' shared memory stays alive until it was read
+            writer = rank == 0;
+        }
+        if (EPI == 2 && writer) {
+            if (active) part[ant][col][r] = v;           // the SwiGLU epilogue pairs rows r and r + 8
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+        }
+        const int m = ant * 8 + col;
+        if (!writer || !active || m >= p.M || failed) continue;
+        if constexpr (EPI == 2) {
+            if (r < 8) {
+                const float gate = v, up = part[ant][col][r + 8];
+                const int64_t f = tile * 8 + r;
+                if (f < N / 2) out[int64_t(m) * (N / 2) + f] = ib::from_f32<TOut>(gate / (1.0f + expf(-gate)) * up);
+            }
+        } else {
+            const int64_t n = n0 + r;
+            if (n < N) {
+                if (p.bias) v += p.bias[n];
+                if constexpr (EPI == 1) v += p.residual[int64_t(m) * N + n];
+                out[int64_t(m) * N + n] = ib::from_f32<TOut>(v);
+            }
+        }
+    }
+}
+
+template <int NT>
+int launch(const GemvParams& p, int out_dtype, int epi, int grid_ctas, cudaStream_t stream) {
+    const dim3 grid{unsigned(grid_ctas), 1u, 1u};
+    const dim3 block{THREADS, 1u, 1u};
+    const unsigned cl = unsigned(p.cluster);
+#define IB_GEMV_LAUNCH(EPI_, T_)                                                                                   \
+    do {                                                                                                           \
+        static bool configured = false;                                                                            \
+        if (!configured) {                                                                                         \
+            cudaError_t e = cudaFuncSetAttribute(bulk_gemv_kernel<NT, EPI_, T_>,                                   \
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);         \
+            if (e != cudaSuccess) return ib::fail(IB_ERR_CUDA, "linear_skinny_bulk: cannot set shared memory size: %s", cudaGetErrorString(e)); \
+            configured = true;                                                                                     \
+        }                                                                                                          \
+        return ib::launch("linear_skinny_bulk", bulk_gemv_kernel<NT, EPI_, T_>, grid, block, size_t(SMEM_BYTES), stream, cl, p); \
+    } while (0)
+    if (epi == 2) {
+        if (out_dtype != IB_BF16) return ib::fail(IB_ERR_ARG, "linear_skinny_bulk: the SwiGLU epilogue writes bfloat16");
+        IB_GEMV_LAUNCH(2, bf16);
+    }
+    if (epi == 1) {
+        if (out_dtype != IB_F32 || !p.residual) return ib::fail(IB_ERR_ARG, "linear_skinny_bulk: the residual epilogue needs a float residual and output");
+        IB_GEMV_LAUNCH(1, float);
+    }
+    if (out_dtype == IB_F32) IB_GEMV_LAUNCH(0, float);
+    if (out_dtype == IB_BF16) IB_GEMV_LAUNCH(0, bf16);
+#undef IB_GEMV_LAUNCH
+    return ib::fail(IB_ERR_ARG, "linear_skinny_bulk: unknown output dtype %d", out_dtype);
+}
+
+}  // namespace
+
+// x: bfloat16 [M, K]. epi: 0 = (+ bias), 1 = (+ bias) + residual -> float, 2 = SwiGLU over rows interleaved by 8 ->
+// bfloat16 [M, N/2]. cluster: CTAs that share a tile's K range (1, 2, 4 or 8); 0 lets the kernel choose from N, K and
+// sm_count. status: one int in device memory, raised if a bounded wait runs out.
+IB_EXPORT int ib_linear_skinny_bulk(const void* x, const void* w, const float* bias, const float* residual, void* out,
+                                    int64_t M, int64_t N, int64_t K, int out_dtype, int epi, int cluster, int sm_count,
+                                    int* status, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return IB_OK;
+    if (M > 16) return ib::fail(IB_ERR_ARG, "linear_skinny_bulk: at most 16 rows, got %lld", (long long)M);
+    if (K <= 0 || K % 8) return ib::fail(IB_ERR_ARG, "linear_skinny_bulk: K = %lld must be a positive multiple of 8", (long long)K);
+    if ((uintptr_t(x) & 15) || (uintptr_t(w) & 15)) return ib::fail(IB_ERR_ARG, "linear_skinny_bulk: operands must be 16-byte aligned");
+    if (epi == 2 && N % 16) return ib::fail(IB_ERR_ARG, "linear_skinny_bulk: the SwiGLU epilogue needs N to be a multiple of 16");
+    if (!status) return ib::fail(IB_ERR_ARG, "linear_skinny_bulk: a status word is required");
+    const int64_t tiles = (N + ROWS - 1) / ROWS;
+    if (tiles > 0x7fffffffLL / 8) return ib::fail(IB_ERR_ARG, "linear_skinny_bulk: N too large");
+    const int sms = sm_count > 0 ? sm_count : 148;
+    if (cluster == 0) {
+        // Share a tile among CTAs while the tiles alone leave SMs idle and every CTA keeps at least two stages of K.
+        cluster = 1;
+        const int64_t n_stages = (K + KC - 1) / KC;
+        while (cluster < 8 && tiles * cluster < 2LL * sms && n_stages / (cluster * 2) >= 2) cluster *= 2;
+    }
+    if (cluster != 1 && cluster != 2 && cluster != 4 && cluster != 8) return ib::fail(IB_ERR_ARG, "linear_skinny_bulk: cluster must be 1, 2, 4 or 8");
+    GemvParams p;
+    p.x = (const bf16*)x; p.w = (const bf16*)w; p.bias = bias; p.residual = residual; p.out = out;
+    p.M = int(M); p.N = N; p.K = K; p.cluster = cluster; p.status = status; p.tiles = tiles;
+    // Three CTAs fit an SM; with more tiles than that, a CTA walks over several and its ring never drains between them.
+    int64_t groups = cluster > 1 ? tiles : (tiles < 3LL * sms ? tiles : 3LL * sms);
+    p.groups = int(groups);
+    const int grid_ctas = int(groups) * cluster;
+    if (M <= 8) return launch<1>(p, out_dtype, epi, grid_ctas, stream);
+    return launch<2>(p, out_dtype, epi, grid_ctas, stream);
+}

@@ -9,6 +9,7 @@ range, a bounded wait that ran out).
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Dict, Optional
 
 import torch
@@ -107,12 +108,16 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = Non
 
 
 SKINNY_MAX_ROWS = 16
+# Which streaming kernel serves up to 16 rows: the one fed by bulk asynchronous copies (gemv_bulk.cu) or the one
+# that loads weights straight into registers (gemv.cu). INFER_B200_GEMV=regs selects the latter.
+GEMV_BULK = os.environ.get("INFER_B200_GEMV", "bulk") != "regs"
 
 
 def linear_skinny(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
                   residual: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16,
                   out: Optional[torch.Tensor] = None, swiglu: bool = False, cluster: int = 0,
-                  norm_weight: Optional[torch.Tensor] = None, norm_eps: float = 0.0) -> Optional[torch.Tensor]:
+                  norm_weight: Optional[torch.Tensor] = None, norm_eps: float = 0.0,
+                  bulk: Optional[bool] = None) -> Optional[torch.Tensor]:
     """The decode kernel: x [M <= 16, K] against w [N, K], weights streamed once; same epilogues as gemm_tc.
     With ``norm_weight`` x is the float32 residual stream and is RMS-normalised inside the kernel (K <= 4096).
     cluster: CTAs sharing one tile's K range (0 = chosen by the kernel)."""
@@ -139,10 +144,20 @@ def linear_skinny(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor]
         out = torch.empty((M, n_out), dtype=out_dtype, device=x.device)
     else:
         _check(out, "out", out_dtype, (M, n_out))
+    st = device_state(x.device)
+    epi = 2 if swiglu else (1 if residual is not None else 0)
+    if bulk is None:
+        # measured on B200: the copy-ring kernel wins while a product has few tiles (q/k/v, o, down), the
+        # register-streaming one when there are thousands (gate/up, the output matrix)
+        bulk = GEMV_BULK and N <= 8192
+    if bulk and not fused:
+        f = _fn("gemvb", "ib_linear_skinny_bulk", [c_void_p] * 5 + [c_int64] * 3 + [c_int] * 4 + [c_void_p] * 2)
+        _call(f, x.data_ptr(), w.data_ptr(), _ptr(bias), _ptr(residual), out.data_ptr(), M, N, K, dtype_code(out_dtype),
+              epi, int(cluster), st.sm_count, st.status.data_ptr(), _stream())
+        return out
     f = _fn("gemv", "ib_linear_skinny", [c_void_p, c_void_p, c_float] + [c_void_p] * 4 + [c_int64] * 3 + [c_int] * 4 + [c_void_p])
     _call(f, x.data_ptr(), _ptr(norm_weight), float(norm_eps), w.data_ptr(), _ptr(bias), _ptr(residual), out.data_ptr(),
-          M, N, K, dtype_code(out_dtype), 2 if swiglu else (1 if residual is not None else 0), int(cluster),
-          device_state(x.device).sm_count, _stream())
+          M, N, K, dtype_code(out_dtype), epi, int(cluster), st.sm_count, _stream())
     return out
 
 

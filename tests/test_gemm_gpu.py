@@ -94,9 +94,12 @@ SKINNY = [(1, 1536, 1536), (8, 2048, 1536), (8, 1536, 8960), (3, 300, 520), (16,
           (2, 320, 96), (1, 151936, 64)]
 
 
+@pytest.mark.parametrize("bulk", [True, False], ids=["bulk", "regs"])
 @pytest.mark.parametrize("M,N,K", SKINNY)
-def test_skinny_matches_plain(M, N, K):
+def test_skinny_matches_plain(M, N, K, bulk):
     from infer_b200 import fast_ops
+    import functools
+    fast_ops = type("F", (), {"linear_skinny": staticmethod(functools.partial(fast_ops.linear_skinny, bulk=bulk))})
     g = torch.Generator(device=DEV).manual_seed(M + N + K)
     x = torch.randn(M, K, device=DEV, generator=g).bfloat16()
     w = (torch.randn(N, K, device=DEV, generator=g) * 0.05).bfloat16()
