@@ -77,6 +77,7 @@ MAX_GRAPHS = 48
 class _GraphEntry:
     def __init__(self, static: torch.Tensor):
         self.static, self.graph, self.logits, self.warm, self.n_launches = static, None, None, 0, 0
+        self.pinned, self.flip = None, 0
 
 
 class Engine:
@@ -165,6 +166,26 @@ class Engine:
         r = w_i = 0
         for s, e in enumerate(entries):
             n = seg_lens[s]
+            if n == 1:
+                # a decoded token: the common case, kept free of array work
+                tok = int(e.tokens[0])
+                if not 0 <= tok < V:
+                    raise ValueError(f"request {e.rid!r}: token id {tok} is outside the vocabulary [0, {V})")
+                if pos0[s] + 1 > self.max_seq_len:
+                    raise ValueError(f"request {e.rid!r}: {pos0[s] + 1} positions exceed the limit of {self.max_seq_len}")
+                ids[r] = tok
+                pos[r] = pos0[s]
+                seg[r] = s
+                seg_start[s] = r
+                seg_pos0[s] = pos0[s]
+                seg_slot[s] = cache.slot(e.rid)
+                for wi in e.want:
+                    if int(wi) != 0:
+                        raise ValueError(f"request {e.rid!r}: wanted place {wi} is outside its 1 tokens")
+                    want[w_i] = r
+                    w_i += 1
+                r += 1
+                continue
             toks = np.asarray(e.tokens, dtype=np.int64)
             if toks.ndim != 1 or n == 0:
                 raise ValueError(f"request {e.rid!r}: a step entry needs at least one token")
@@ -192,7 +213,6 @@ class Engine:
             for s, e in enumerate(entries):
                 t = cache.block_table(e.rid, gi)
                 tab[s, :len(t)] = t
-        host = torch.from_numpy(buf).pin_memory()
         entry = None
         if graphs and T == S:
             key = (S, n_want, tuple(widths))
@@ -201,10 +221,15 @@ class Engine:
                 if len(self._graphs) >= MAX_GRAPHS:
                     self._graphs.pop(next(iter(self._graphs)))
                 entry = self._graphs[key] = _GraphEntry(torch.empty(buf.size, dtype=torch.int32, device=self.rt.device))
+                entry.pinned = [torch.empty(buf.size, dtype=torch.int32).pin_memory() for _ in range(2)]
+            # two pinned staging buffers alternate, so that one is free while the other's copy may still be in flight
+            entry.flip ^= 1
+            host = entry.pinned[entry.flip]
+            host.numpy()[:] = buf
             dev = entry.static
             dev.copy_(host, non_blocking=True)
         else:
-            dev = host.to(self.rt.device, non_blocking=True)
+            dev = torch.from_numpy(buf).pin_memory().to(self.rt.device, non_blocking=True)
         self.last_h2d_bytes = buf.nbytes
 
         def cut(i, n):

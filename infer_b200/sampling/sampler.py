@@ -20,6 +20,7 @@ from .. import ops
 class Sampler:
     def __init__(self, device):
         self.device = torch.device(device)
+        self._pinned, self._flip = {}, 0
 
     def sample(self, logits: torch.Tensor, params: Sequence, positions: Sequence[int]) -> torch.Tensor:
         """logits float32 [B, vocab] on the device; params: objects with temperature, seed, top_k, top_p;
@@ -39,8 +40,17 @@ class Sampler:
             top_p[i] = float(getattr(p, "top_p", 1.0))
             if temp[i] > 0 and (host[i, 2] > 0 or top_p[i] < 1.0):
                 filtered = True
-        ints = torch.from_numpy(host).pin_memory().to(self.device, non_blocking=True)
-        t = torch.from_numpy(temp).pin_memory().to(self.device, non_blocking=True)
+        # one pinned staging buffer per batch size and parity, reused step after step
+        self._flip ^= 1
+        key = (B, self._flip)
+        stage = self._pinned.get(key)
+        if stage is None:
+            stage = self._pinned[key] = (torch.empty((B, 4), dtype=torch.int64).pin_memory(),
+                                         torch.empty(B, dtype=torch.float32).pin_memory())
+        stage[0].numpy()[:] = host
+        stage[1].numpy()[:] = temp
+        ints = stage[0].to(self.device, non_blocking=True)
+        t = stage[1].to(self.device, non_blocking=True)
         self.last_h2d_bytes = host.nbytes + temp.nbytes
         seed, step = ints[:, 0].contiguous(), ints[:, 1].contiguous()
         if not filtered:
