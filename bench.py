@@ -200,35 +200,41 @@ def prefill_flops(cfg, n_layers, T):
 
 
 def time_e2e(eng, batch, context, steps, warmup):
-    """Decode through the scheduler of the Python entry point: every step packs host token ids into pinned memory,
-    copies them to the device, runs the step, samples on the device and reads the sampled ids back to the host."""
+    """Decode through the scheduler of the Python entry point, as LLM.generate drives it: requests with prompts of
+    `context` random host token ids are submitted and prefilled; then K scheduler steps are timed. Every step packs
+    that step's integers into pinned host memory and copies them to the device, launches the step, samples on the
+    device and copies the sampled ids to pinned host memory, where the scheduler reads them (one step late: the
+    next step is launched first and takes its input tokens from the device)."""
+    import numpy as np
     import torch
     from infer_b200.engine.generation import GenerationEngine
-    from infer_b200.engine.scheduler import BatchItem, SampleParams
-    fill_contexts(eng, batch, context)
+    from infer_b200.engine.scheduler import Request, SampleParams, Scheduler, SchedulerConfig
     ge = GenerationEngine(eng)
-    toks = {r: (7 * r + 1) % eng.spec.vocab_size for r in range(batch)}
-    sp = SampleParams()
-    pos = context
-
-    def one(pos):
-        out = ge.run([BatchItem(r, [toks[r]], sp, pos) for r in range(batch)])
-        for r, t in out.items():
-            toks[r] = t
+    got = []
+    sch = Scheduler(ge, SchedulerConfig(eos_id=-1, max_batch_tokens=2048, overlap=True,
+                                        on_token=lambda rid, tok: got.append(tok)))
+    rng = np.random.default_rng(1)
+    for r in range(batch):
+        sch.submit(Request(r, rng.integers(0, eng.spec.vocab_size, context).tolist(), warmup + steps + 8, 0, SampleParams()))
+    while sch.queue or any(not a.decoding for a in sch.active.values()):
+        sch.step()
     for _ in range(warmup):
-        one(pos)
-        pos += 1
+        sch.step()
     torch.cuda.synchronize()
+    n0 = len(got)
     t0 = time.perf_counter()
     for _ in range(steps):
-        one(pos)
-        pos += 1
+        sch.step()
     torch.cuda.synchronize()
     dt = time.perf_counter() - t0
-    # per step: the packed int32 buffer and the sampler's parameters in, `batch` int32 token ids out
+    n_tokens = batch * steps                 # tokens generated on the device in the timed steps
+    assert len(got) - n0 >= batch * (steps - 1), "the scheduler did not hand the tokens to the host"
     h2d = eng.last_h2d_bytes + ge.sampler.last_h2d_bytes
+    for rid in list(sch.active):
+        sch.cancel(rid)
+    sch.run_until_idle()
     release_all(eng)
-    return batch * steps / dt, h2d, 4 * batch
+    return n_tokens / dt, h2d, 4 * batch
 
 
 def main():

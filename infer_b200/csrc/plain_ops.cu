@@ -30,15 +30,20 @@ using bf16 = __nv_bfloat16;
 
 // ------------------------------------------------------------------------------------------------
 // Embedding: out[t, :] = float(table[ids[t], :]). Ids are validated on the host; an id outside the
-// table writes zeros and raises the status word rather than reading out of bounds.
+// table writes zeros and raises the status word rather than reading out of bounds. An id of -1 stands for "the
+// token sampled last for this request", which the sampling kernel left in feedback[slot of the request].
 template <typename T>
 __global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids, int64_t n_tokens,
-                                 int64_t hidden, int64_t vocab, float* __restrict__ out, int* status) {
+                                 int64_t hidden, int64_t vocab, float* __restrict__ out, int* status,
+                                 const int* __restrict__ feedback, const int* __restrict__ token_seg,
+                                 const int* __restrict__ seg_slot) {
     ib::pdl_wait();
     const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
     if (i >= n_tokens * hidden) return;
     const int64_t t = i / hidden, c = i - t * hidden;
-    const int id = ids[t];
+    int id = ids[t];
+    // id -1: the token that was sampled last for this token's request, still on the device (feedback[slot])
+    if (id == -1 && feedback) id = feedback[seg_slot[token_seg[t]]];
     if (id < 0 || id >= vocab) {
         out[i] = 0.0f;
         if (status) atomicExch(status, 1);
@@ -295,19 +300,37 @@ __device__ __forceinline__ float hash_uniform(uint64_t seed, uint64_t step, uint
 
 __global__ void sample_kernel(const float* __restrict__ logits, int64_t vocab, const float* __restrict__ temperature,
                               const int64_t* __restrict__ seed, const int64_t* __restrict__ step,
-                              int* __restrict__ out) {
+                              int* __restrict__ out, int* feedback, const int64_t* __restrict__ slots) {
     ib::pdl_wait();
-    __shared__ float sv[256];
-    __shared__ int si[256];
+    __shared__ float sv[1024];
+    __shared__ int si[1024];
     const int b = blockIdx.x;
     const float* row = logits + int64_t(b) * vocab;
     const float T = temperature[b];
+    const uint64_t sd = uint64_t(seed[b]), stp = uint64_t(step[b]);
     float best = -INFINITY;
     int besti = 0x7fffffff;
-    for (int64_t v = threadIdx.x; v < vocab; v += blockDim.x) {
-        float x = row[v];
-        if (T > 0.0f) x = x / T - logf(-logf(hash_uniform(uint64_t(seed[b]), uint64_t(step[b]), uint64_t(v))));
+    auto take = [&](float x, int64_t v) {
+        if (T > 0.0f) x = x / T - logf(-logf(hash_uniform(sd, stp, uint64_t(v))));
         if (x > best || (x == best && v < besti)) { best = x; besti = int(v); }
+    };
+    if ((vocab & 3) == 0) {
+        // rows are 16-byte aligned: four logits per load, two loads in flight per thread
+        const float4* row4 = reinterpret_cast<const float4*>(row);
+        const int64_t n4 = vocab >> 2;
+        int64_t i = threadIdx.x;
+        for (; i + blockDim.x < n4; i += 2 * blockDim.x) {
+            const float4 a = row4[i], c = row4[i + blockDim.x];
+            take(a.x, 4 * i); take(a.y, 4 * i + 1); take(a.z, 4 * i + 2); take(a.w, 4 * i + 3);
+            const int64_t j = i + blockDim.x;
+            take(c.x, 4 * j); take(c.y, 4 * j + 1); take(c.z, 4 * j + 2); take(c.w, 4 * j + 3);
+        }
+        if (i < n4) {
+            const float4 a = row4[i];
+            take(a.x, 4 * i); take(a.y, 4 * i + 1); take(a.z, 4 * i + 2); take(a.w, 4 * i + 3);
+        }
+    } else {
+        for (int64_t v = threadIdx.x; v < vocab; v += blockDim.x) take(row[v], v);
     }
     sv[threadIdx.x] = best;
     si[threadIdx.x] = besti;
@@ -323,7 +346,11 @@ __global__ void sample_kernel(const float* __restrict__ logits, int64_t vocab, c
         }
         __syncthreads();
     }
-    if (threadIdx.x == 0) out[b] = si[0] == 0x7fffffff ? 0 : si[0];
+    if (threadIdx.x == 0) {
+        const int tok = si[0] == 0x7fffffff ? 0 : si[0];
+        out[b] = tok;
+        if (feedback) feedback[slots[b]] = tok;          // stays on the device for the request's next step
+    }
 }
 
 // Sampling with top-k / top-p filters (src/sampler.cpp:8-63): x = logit / T; keep the k largest x; among
@@ -338,7 +365,8 @@ __device__ __forceinline__ uint32_t ordered_key(float x) {
 __global__ void __launch_bounds__(1024)
 sample_filtered_kernel(const float* __restrict__ logits, int64_t vocab, const float* __restrict__ temperature,
                        const int64_t* __restrict__ seed, const int64_t* __restrict__ step,
-                       const int64_t* __restrict__ top_k, const float* __restrict__ top_p, int* __restrict__ out) {
+                       const int64_t* __restrict__ top_k, const float* __restrict__ top_p, int* __restrict__ out,
+                       int* feedback, const int64_t* __restrict__ slots) {
     ib::pdl_wait();
     __shared__ float red[32];
     __shared__ float sv[1024];
@@ -413,7 +441,11 @@ sample_filtered_kernel(const float* __restrict__ logits, int64_t vocab, const fl
         }
         __syncthreads();
     }
-    if (threadIdx.x == 0) out[b] = si[0] == 0x7fffffff ? 0 : si[0];
+    if (threadIdx.x == 0) {
+        const int tok = si[0] == 0x7fffffff ? 0 : si[0];
+        out[b] = tok;
+        if (feedback) feedback[slots[b]] = tok;          // stays on the device for the request's next step
+    }
 }
 
 inline unsigned blocks_for(int64_t n, int threads) { return unsigned((n + threads - 1) / threads); }
@@ -424,13 +456,14 @@ inline unsigned blocks_for(int64_t n, int threads) { return unsigned((n + thread
 // C entry points. dtype arguments: 0 = float, 1 = bfloat16.
 
 IB_EXPORT int ib_embedding(const void* table, int table_dtype, const int* ids, int64_t n_tokens, int64_t hidden,
-                           int64_t vocab, float* out, int* status, cudaStream_t stream) {
+                           int64_t vocab, float* out, int* status, const int* feedback, const int* token_seg,
+                           const int* seg_slot, cudaStream_t stream) {
     if (n_tokens <= 0) return IB_OK;
     const int64_t n = n_tokens * hidden;
     if (table_dtype == IB_F32)
-        IB_LAUNCH(embedding_kernel<float>, blocks_for(n, 256), 256, 0, (const float*)table, ids, n_tokens, hidden, vocab, out, status);
+        IB_LAUNCH(embedding_kernel<float>, blocks_for(n, 256), 256, 0, (const float*)table, ids, n_tokens, hidden, vocab, out, status, feedback, token_seg, seg_slot);
     else if (table_dtype == IB_BF16)
-        IB_LAUNCH(embedding_kernel<bf16>, blocks_for(n, 256), 256, 0, (const bf16*)table, ids, n_tokens, hidden, vocab, out, status);
+        IB_LAUNCH(embedding_kernel<bf16>, blocks_for(n, 256), 256, 0, (const bf16*)table, ids, n_tokens, hidden, vocab, out, status, feedback, token_seg, seg_slot);
     else
         return ib::fail(IB_ERR_ARG, "ib_embedding: unknown table dtype %d", table_dtype);
     return ib::check_launch("ib_embedding");
@@ -524,18 +557,19 @@ IB_EXPORT int ib_swiglu(const void* gate_up, void* out, int64_t n_tokens, int64_
 }
 
 IB_EXPORT int ib_sample(const float* logits, int64_t n_rows, int64_t vocab, const float* temperature,
-                        const int64_t* seed, const int64_t* step, int* out, cudaStream_t stream) {
+                        const int64_t* seed, const int64_t* step, int* out, int* feedback, const int64_t* slots,
+                        cudaStream_t stream) {
     if (n_rows <= 0) return IB_OK;
     if (vocab <= 0 || vocab >= 0x7fffffff) return ib::fail(IB_ERR_ARG, "ib_sample: vocabulary %lld out of range", (long long)vocab);
-    IB_LAUNCH(sample_kernel, unsigned(n_rows), 256, 0, logits, vocab, temperature, seed, step, out);
+    IB_LAUNCH(sample_kernel, unsigned(n_rows), 1024, 0, logits, vocab, temperature, seed, step, out, feedback, slots);
     return ib::check_launch("ib_sample");
 }
 
 IB_EXPORT int ib_sample_filtered(const float* logits, int64_t n_rows, int64_t vocab, const float* temperature,
                                  const int64_t* seed, const int64_t* step, const int64_t* top_k, const float* top_p,
-                                 int* out, cudaStream_t stream) {
+                                 int* out, int* feedback, const int64_t* slots, cudaStream_t stream) {
     if (n_rows <= 0) return IB_OK;
     if (vocab <= 0 || vocab >= 0x7fffffff) return ib::fail(IB_ERR_ARG, "ib_sample_filtered: vocabulary %lld out of range", (long long)vocab);
-    IB_LAUNCH(sample_filtered_kernel, unsigned(n_rows), 1024, 0, logits, vocab, temperature, seed, step, top_k, top_p, out);
+    IB_LAUNCH(sample_filtered_kernel, unsigned(n_rows), 1024, 0, logits, vocab, temperature, seed, step, top_k, top_p, out, feedback, slots);
     return ib::check_launch("ib_sample_filtered");
 }

@@ -56,6 +56,7 @@ class StepContext:
     want_rows: torch.Tensor          # [n_want]
     block_tables: List[torch.Tensor]  # per cache group: [S, max_blocks]
     status: torch.Tensor             # [1] kernels raise it on a page index or token id out of range
+    feedback: Optional[torch.Tensor] = None   # [slots] the sampler's last token per request (for token id -1)
     # host copies, for planning kernel launches without a device round trip
     seg_lens: List[int] = field(default_factory=list)
     seg_pos0_host: List[int] = field(default_factory=list)
@@ -69,14 +70,16 @@ def _round_up(x: int, m: int) -> int:
     return (x + m - 1) // m * m
 
 
+FEEDBACK_TOKEN = -1           # as a decode entry's token: "what the sampler produced last for this request"
 GRAPH_WIDTH_PAGES = 32        # decode-only block tables are padded to a multiple of this many pages (512 positions)
 GRAPH_WARMUP_STEPS = 2        # eager steps of a shape before its graph is captured
 MAX_GRAPHS = 48
+GRAPH_COPIES = 2              # executable copies per shape, launched in turn
 
 
 class _GraphEntry:
     def __init__(self, static: torch.Tensor):
-        self.static, self.graph, self.logits, self.warm, self.n_launches = static, None, None, 0, 0
+        self.static, self.graphs, self.turn, self.warm, self.n_launches = static, [], 0, 0, 0
         self.pinned, self.flip = None, 0
 
 
@@ -111,6 +114,9 @@ class Engine:
         from ..fast_ops import device_state
         self.status = device_state(self.rt.device).status     # shared with the fast kernels of this device
         self.steps_run = 0
+        # The sampler leaves every request's last token here (indexed by state slot); a decode entry whose token is
+        # FEEDBACK_TOKEN reads it, so that the host need not see a token before the next step is launched.
+        self.next_tokens = torch.zeros(max(1, max_requests), dtype=torch.int32, device=self.rt.device)
         # Decode-only steps of the bfloat16 path are captured into CUDA graphs, one per (batch, wanted rows, table widths).
         self.use_graphs = bool(cuda_graphs) and dtype == torch.bfloat16
         self._graphs: Dict[tuple, _GraphEntry] = {}
@@ -169,7 +175,9 @@ class Engine:
             if n == 1:
                 # a decoded token: the common case, kept free of array work
                 tok = int(e.tokens[0])
-                if not 0 <= tok < V:
+                if tok == FEEDBACK_TOKEN and pos0[s] > 0:
+                    pass                                # the request's last sampled token, still on the device
+                elif not 0 <= tok < V:
                     raise ValueError(f"request {e.rid!r}: token id {tok} is outside the vocabulary [0, {V})")
                 if pos0[s] + 1 > self.max_seq_len:
                     raise ValueError(f"request {e.rid!r}: {pos0[s] + 1} positions exceed the limit of {self.max_seq_len}")
@@ -239,7 +247,7 @@ class Engine:
             token_ids=cut(0, T), positions=cut(1, T), token_seg=cut(2, T), seg_start=cut(3, S + 1),
             seg_pos0=cut(4, S), seg_slot=cut(5, S), want_rows=cut(6, n_want),
             block_tables=[cut(7 + gi, S * widths[gi]).view(S, widths[gi]) for gi in range(n_groups)],
-            status=self.status, seg_lens=seg_lens, seg_pos0_host=pos0, max_q_len=max(seg_lens),
+            feedback=self.next_tokens, status=self.status, seg_lens=seg_lens, seg_pos0_host=pos0, max_q_len=max(seg_lens),
             max_ctx_len=max(p + n for p, n in zip(pos0, seg_lens)), decode_only=all(n == 1 for n in seg_lens))
         if entry is not None:
             # a graph's launch shapes must not depend on the step: bound the context by the table width
@@ -273,10 +281,13 @@ class Engine:
         with torch.cuda.device(self.rt.device):
             if entry is None:
                 logits = self.model.forward(ctx, self.cache_views)
-            elif entry.graph is not None:
-                entry.graph.replay()
+            elif len(entry.graphs) == GRAPH_COPIES:
+                # Copies of the graph take turns: launching an executable graph again while its previous launch is
+                # still running is serialised by the driver, which would put the launch cost between two steps.
+                entry.turn = (entry.turn + 1) % GRAPH_COPIES
+                graph, logits = entry.graphs[entry.turn]
+                graph.replay()
                 ops._LAUNCHES[0] += entry.n_launches
-                logits = entry.logits
             elif entry.warm < GRAPH_WARMUP_STEPS:
                 # The first steps of a shape run eagerly: they build libraries, size workspaces, set attributes.
                 entry.warm += 1
@@ -285,13 +296,12 @@ class Engine:
                 graph = torch.cuda.CUDAGraph()
                 n0 = ops.kernel_launches()
                 with torch.cuda.graph(graph, pool=self._graph_pool):
-                    entry.logits = self.model.forward(ctx, self.cache_views)
+                    logits = self.model.forward(ctx, self.cache_views)
                 entry.n_launches = ops.kernel_launches() - n0        # kernels of this package inside the graph
                 ops._LAUNCHES[0] = n0
-                entry.graph = graph
+                entry.graphs.append((graph, logits))
                 graph.replay()
                 ops._LAUNCHES[0] += entry.n_launches
-                logits = entry.logits
         for rid, n in wanted:
             self.cache.advance(rid, n)
         self.steps_run += 1

@@ -16,6 +16,19 @@ from .engine import Engine, StepEntry
 from .scheduler import (BatchEngine, BatchItem, Completed, Request, SampleParams, Scheduler, SchedulerConfig)
 
 
+class PendingTokens:
+    """Sampled token ids on their way to the host."""
+
+    def __init__(self, rids, host, event):
+        self.rids, self._host, self._event = rids, host, event
+
+    def result(self) -> Dict[Hashable, int]:
+        if self._event is None:
+            return {}
+        self._event.synchronize()
+        return {rid: int(t) for rid, t in zip(self.rids, self._host.tolist())}
+
+
 class GenerationEngine(BatchEngine):
     """Runs a planned batch as ONE step and samples on the device; only token ids cross to the host."""
 
@@ -24,6 +37,7 @@ class GenerationEngine(BatchEngine):
         self.sampler = Sampler(engine.rt.device)
         self.max_seq_len = engine.max_seq_len
         self.max_requests = engine.cache.n_slots
+        self._pinned, self._flip = {}, 0
 
     def capacity_tokens(self) -> int:
         return min(self.engine.cache.pages_total()) * self.engine.cache.page_size if self.engine.cache.groups else 1 << 60
@@ -52,15 +66,30 @@ class GenerationEngine(BatchEngine):
                 hi = mid - 1
         return lo
 
-    def run(self, batch: Sequence[BatchItem]) -> Dict[Hashable, int]:
+    def run_async(self, batch: Sequence[BatchItem]) -> "PendingTokens":
+        """Enqueues the step, the sampling and the copy of the sampled ids to pinned host memory, and returns at
+        once. Every sampled token also stays on the device (engine.next_tokens[slot]); a later decode item may pass
+        FEEDBACK_TOKEN instead of the id."""
         entries = [StepEntry(b.rid, b.tokens, [len(b.tokens) - 1] if b.sample is not None else []) for b in batch]
+        slots = {b.rid: self.engine.cache.slot(b.rid) for b in batch if b.sample is not None}
         logits = self.engine.step(entries)
         rows = [b for b in batch if b.sample is not None]
         if not rows:
-            return {}
-        ids = self.sampler.sample(logits, [b.sample for b in rows], [b.position for b in rows])
-        host = ids.cpu().numpy()
-        return {b.rid: int(t) for b, t in zip(rows, host)}
+            return PendingTokens([], None, None)
+        ids = self.sampler.sample(logits, [b.sample for b in rows], [b.position for b in rows],
+                                  self.engine.next_tokens, [slots[b.rid] for b in rows])
+        self._flip ^= 1
+        key = (len(rows), self._flip)
+        host = self._pinned.get(key)
+        if host is None:
+            host = self._pinned[key] = torch.empty(len(rows), dtype=torch.int32).pin_memory()
+        host.copy_(ids, non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        return PendingTokens([b.rid for b in rows], host, event)
+
+    def run(self, batch: Sequence[BatchItem]) -> Dict[Hashable, int]:
+        return self.run_async(batch).result()
 
     def pages_in_use(self) -> int:
         return max(self.engine.cache.pages_in_use(), default=0)
@@ -79,7 +108,7 @@ class LLM:
 
     def __init__(self, model: str, dtype="bfloat16", device: str = "cuda:0", slots: int = 8, max_seq: int = 4096,
                  budget_mb: int = 0, max_batch_tokens: int = 512, page_size: int = 16, eos_id: Optional[int] = None,
-                 kernels: Optional[Dict[str, str]] = None, weights=None, spec=None):
+                 kernels: Optional[Dict[str, str]] = None, weights=None, spec=None, overlap: bool = True):
         """slots: live requests; max_seq: per-sequence cap; budget_mb: size of the page pool (0 = reserve
         slots x max_seq, as the reference does). ``spec`` + ``weights`` may replace the folder."""
         from ..config.registry import load_config
@@ -93,7 +122,7 @@ class LLM:
                              cache_budget_bytes=int(budget_mb) << 20)
         self.batch_engine = GenerationEngine(self.engine)
         default_eos = eos_id if eos_id is not None else (spec.eos_token_id if spec.eos_token_id is not None else -1)
-        self.scheduler_config = SchedulerConfig(eos_id=default_eos, max_batch_tokens=max_batch_tokens)
+        self.scheduler_config = SchedulerConfig(eos_id=default_eos, max_batch_tokens=max_batch_tokens, overlap=overlap)
         self._next_id = 0
 
     def new_scheduler(self, **overrides) -> Scheduler:

@@ -61,7 +61,8 @@ class Model:
         return needs
 
     def forward(self, step, cache_views: Mapping[int, object]) -> torch.Tensor:
-        h = ops.embedding(self.embedding, step.token_ids, step.status)            # float32 [T, hidden]
+        h = ops.embedding(self.embedding, step.token_ids, step.status, getattr(step, "feedback", None),
+                          step.token_seg, step.seg_slot)                          # float32 [T, hidden]
         for call in self.spec.schedule:
             h = self.blocks[call.layer].forward(h, step, cache_views[call.cache], call.write_cache)
         if step.n_want == 0:

@@ -20,6 +20,13 @@ When pages run out (decided here, tested in tests/test_scheduler.py):
      through its prompt simply starts again;
   3. a request that could not fit even alone is refused at ``submit`` (prompt + max_new must fit
      both the sequence limit and the page pool), so step 2 always ends.
+
+Overlap (``SchedulerConfig.overlap``): a step is launched before the tokens of the step before it have reached
+the host. The engine keeps every request's last sampled token on the device, and a decode item then carries
+FEEDBACK_TOKEN instead of an id; the host reads a step's tokens while the next step runs, so callbacks, eos and
+retirement come one step late (a request that hit eos has then run one token too many, which is dropped).
+max_new and the sequence limit are counted, not read, so they stop a request on time. Before anything is
+preempted the tokens in flight are read, so a victim's new prompt holds everything it generated.
 """
 from __future__ import annotations
 
@@ -31,6 +38,7 @@ from enum import IntEnum
 from typing import Callable, Deque, Dict, Hashable, List, Optional, Sequence, Tuple
 
 USE_DEFAULT_EOS = None
+FEEDBACK_TOKEN = -1        # a decode item's token when the previous step's result has not reached the host yet
 
 
 @dataclass
@@ -123,6 +131,7 @@ class SchedulerConfig:
     continuous: bool = True             # False = static batching baseline
     eos_id: int = -1                    # -1 = never stop on eos
     max_batch_tokens: int = 512         # token budget of one step
+    overlap: bool = False               # launch step n+1 before the tokens of step n have reached the host
     event_capacity: int = 1 << 16
     on_token: Optional[Callable[[Hashable, int], None]] = None
     on_done: Optional[Callable[[Completed], None]] = None
@@ -156,6 +165,15 @@ class BatchEngine:
     def run(self, batch: Sequence[BatchItem]) -> Dict[Hashable, int]:
         """Runs the batch as one step; returns the sampled token of every item that has ``sample``."""
         raise NotImplementedError
+    def run_async(self, batch: Sequence[BatchItem]):
+        """Starts the step and returns an object whose ``result()`` gives what ``run`` returns. An item's token may
+        be FEEDBACK_TOKEN: the token sampled last for that request, which the engine kept. The default runs at once."""
+        done = self.run(batch)
+
+        class _Done:
+            def result(self_inner):
+                return done
+        return _Done()
     def pages_in_use(self) -> int: raise NotImplementedError
     def pages_total(self) -> int: raise NotImplementedError
 
@@ -172,6 +190,7 @@ class _Active:
     admitted_ms: float = 0.0
     first_token_ms: float = 0.0
     preemptions: int = 0
+    pending: int = 0                # tokens sampled on the device that the host has not read yet (overlap mode)
 
     @property
     def decoding(self) -> bool:
@@ -193,6 +212,7 @@ class Scheduler:
         self.preemptions = 0
         self._t0 = time.perf_counter()
         self._preempt_counts: Dict[Hashable, int] = {}
+        self._pending = None            # (PendingTokens, batch) of the step in flight (overlap mode)
 
     # ------------------------------------------------------------------ public
 
@@ -209,7 +229,7 @@ class Scheduler:
         self._cancelled.add(request_id)
 
     def idle(self) -> bool:
-        return not self.queue and not self.active
+        return not self.queue and not self.active and self._pending is None
 
     @property
     def steps(self) -> int:
@@ -300,8 +320,11 @@ class Scheduler:
         for a in decode:
             if budget <= 0:
                 break
-            pos = len(a.req.prompt) + len(a.out) - len(a.req.generated_so_far) - 1
-            batch.append(BatchItem(a.req.id, [a.last_token], a.req.sample, pos))
+            n_out = len(a.out) + a.pending
+            if n_out >= a.req.max_new or a.prompt_len + n_out >= self.eng.max_seq_len:
+                continue                                # it ends as soon as its pending token has been read
+            pos = len(a.req.prompt) + n_out - len(a.req.generated_so_far) - 1
+            batch.append(BatchItem(a.req.id, [FEEDBACK_TOKEN if a.pending else a.last_token], a.req.sample, pos))
             wanted.append((a.req.id, 1))
             budget -= 1
         if wanted and not self.eng.can_run(wanted):
@@ -320,6 +343,42 @@ class Scheduler:
             budget -= n
         return batch
 
+    def _take_tokens(self, batch, sampled) -> int:
+        """Appends the sampled tokens to their requests, calls back, and retires what has finished."""
+        decoded = 0
+        for b in batch:
+            if b.sample is None:
+                continue
+            a = self.active.get(b.rid)
+            if a is None or b.rid not in sampled:
+                continue                                # retired, cancelled or preempted meanwhile: the token is dropped
+            if a.pending:
+                a.pending -= 1
+            tok = int(sampled[b.rid])
+            if a.first_token_ms == 0.0:
+                a.first_token_ms = self._now()
+            a.last_token = tok
+            a.out.append(tok)
+            decoded += 1
+            if self.cfg.on_token:
+                self.cfg.on_token(b.rid, tok)
+            if tok == self._eos(a.req):
+                self._retire(b.rid, StopReason.EOS)
+            elif len(a.out) >= a.req.max_new:
+                self._retire(b.rid, StopReason.MAX_NEW)
+            elif a.prompt_len + len(a.out) >= self.eng.max_seq_len:
+                self._retire(b.rid, StopReason.CACHE_FULL)
+        return decoded
+
+    def _apply_pending(self) -> int:
+        if self._pending is None:
+            return 0
+        handle, batch, seqs = self._pending
+        self._pending = None
+        # a request admitted again after a preemption must not take a token of its earlier life
+        live = [b for b in batch if b.rid in self.active and self.active[b.rid].admitted_seq == seqs[b.rid]]
+        return self._take_tokens(live, handle.result())
+
     def step(self) -> int:
         """Cancel -> admit -> plan (preempting while nothing can move) -> run -> retire. Returns tokens decoded."""
         t_start = self._now()
@@ -329,6 +388,10 @@ class Scheduler:
         self._admit()
         batch = self._plan()
         while not batch and self.active:
+            if self._pending is not None:
+                self._apply_pending()                   # a victim's prompt must hold every token it has generated
+                batch = self._plan()
+                continue
             if len(self.active) == 1:
                 only = next(iter(self.active.values()))
                 raise RuntimeError(f"scheduler: out of cache pages with nothing to preempt (request {only.req.id!r})")
@@ -336,28 +399,26 @@ class Scheduler:
             batch = self._plan()
         decoded = 0
         n_tokens = sum(len(b.tokens) for b in batch)
-        if batch:
+        if self.cfg.overlap:
+            launched = None
+            if batch:
+                for b in batch:
+                    a = self.active[b.rid]
+                    if not a.decoding:
+                        a.fed += len(b.tokens)
+                    if b.sample is not None:
+                        a.pending += 1
+                seqs = {b.rid: self.active[b.rid].admitted_seq for b in batch}
+                launched = (self.eng.run_async(batch), batch, seqs)
+            decoded = self._apply_pending()             # the previous step's tokens, while this step runs
+            self._pending = launched
+        elif batch:
             sampled = self.eng.run(batch)
             for b in batch:
                 a = self.active[b.rid]
                 if not a.decoding:
                     a.fed += len(b.tokens)
-                if b.sample is None:
-                    continue
-                tok = int(sampled[b.rid])
-                if a.first_token_ms == 0.0:
-                    a.first_token_ms = self._now()
-                a.last_token = tok
-                a.out.append(tok)
-                decoded += 1
-                if self.cfg.on_token:
-                    self.cfg.on_token(b.rid, tok)
-                if tok == self._eos(a.req):
-                    self._retire(b.rid, StopReason.EOS)
-                elif len(a.out) >= a.req.max_new:
-                    self._retire(b.rid, StopReason.MAX_NEW)
-                elif a.prompt_len + len(a.out) >= self.eng.max_seq_len:
-                    self._retire(b.rid, StopReason.CACHE_FULL)
+            decoded = self._take_tokens(batch, sampled)
         self._event("step", tokens=n_tokens, decoded=decoded, t=t_start, dur=self._now() - t_start)
         self._step += 1
         return decoded

@@ -82,14 +82,22 @@ def _call(f, *args) -> None:
 
 # ----------------------------------------------------------------------------- plain kernels
 
-def embedding(table: torch.Tensor, ids: torch.Tensor, status: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """float32 rows of ``table`` ([vocab, hidden], float32 or bfloat16) for int32 ``ids``."""
+def embedding(table: torch.Tensor, ids: torch.Tensor, status: Optional[torch.Tensor] = None,
+              feedback: Optional[torch.Tensor] = None, token_seg: Optional[torch.Tensor] = None,
+              seg_slot: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """float32 rows of ``table`` ([vocab, hidden], float32 or bfloat16) for int32 ``ids``. An id of -1 is replaced by
+    ``feedback[seg_slot[token_seg[t]]]``: the token the sampler left on the device for that request."""
     _check(table, "table")
     _check(ids, "ids", torch.int32)
     T, (V, H) = ids.numel(), table.shape
     out = torch.empty((T, H), dtype=torch.float32, device=table.device)
-    f = _fn("plain", "ib_embedding", [c_void_p, c_int, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p])
-    _call(f, table.data_ptr(), dtype_code(table.dtype), ids.data_ptr(), T, H, V, out.data_ptr(), _ptr(status), _stream())
+    if feedback is not None:
+        _check(feedback, "feedback", torch.int32)
+        _check(token_seg, "token_seg", torch.int32, (T,))
+        _check(seg_slot, "seg_slot", torch.int32)
+    f = _fn("plain", "ib_embedding", [c_void_p, c_int, c_void_p, c_int64, c_int64, c_int64] + [c_void_p] * 6)
+    _call(f, table.data_ptr(), dtype_code(table.dtype), ids.data_ptr(), T, H, V, out.data_ptr(), _ptr(status),
+          _ptr(feedback), _ptr(token_seg), _ptr(seg_slot), _stream())
     return out
 
 
@@ -201,22 +209,26 @@ def swiglu(gate_up: torch.Tensor, interleave8: bool = False) -> torch.Tensor:
     return out
 
 
-def sample(logits: torch.Tensor, temperature: torch.Tensor, seed: torch.Tensor, step: torch.Tensor) -> torch.Tensor:
+def sample(logits: torch.Tensor, temperature: torch.Tensor, seed: torch.Tensor, step: torch.Tensor,
+           feedback: Optional[torch.Tensor] = None, slots: Optional[torch.Tensor] = None) -> torch.Tensor:
     """One token id per row of float32 logits: argmax at temperature 0, else Gumbel-max with a
-    hash of (seed, step, index). temperature float32 [B]; seed, step int64 [B]. Returns int32 [B]."""
+    hash of (seed, step, index). temperature float32 [B]; seed, step int64 [B]. Returns int32 [B].
+    With ``feedback`` (int32 [slots]) and ``slots`` (int64 [B]) each token is also left at feedback[slots[b]]."""
     _check(logits, "logits", torch.float32)
     B, V = logits.shape
     _check(temperature, "temperature", torch.float32, (B,))
     _check(seed, "seed", torch.int64, (B,))
     _check(step, "step", torch.int64, (B,))
     out = torch.empty((B,), dtype=torch.int32, device=logits.device)
-    f = _fn("plain", "ib_sample", [c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
-    _call(f, logits.data_ptr(), B, V, temperature.data_ptr(), seed.data_ptr(), step.data_ptr(), out.data_ptr(), _stream())
+    f = _fn("plain", "ib_sample", [c_void_p, c_int64, c_int64] + [c_void_p] * 7)
+    _call(f, logits.data_ptr(), B, V, temperature.data_ptr(), seed.data_ptr(), step.data_ptr(), out.data_ptr(),
+          _ptr(feedback), _ptr(slots), _stream())
     return out
 
 
 def sample_filtered(logits: torch.Tensor, temperature: torch.Tensor, seed: torch.Tensor, step: torch.Tensor,
-                    top_k: torch.Tensor, top_p: torch.Tensor) -> torch.Tensor:
+                    top_k: torch.Tensor, top_p: torch.Tensor, feedback: Optional[torch.Tensor] = None,
+                    slots: Optional[torch.Tensor] = None) -> torch.Tensor:
     """As ``sample``, after keeping the top_k (int64 [B], 0 = all) largest logits and then the smallest set of
     largest probabilities whose mass reaches top_p (float32 [B], 1 = all)."""
     _check(logits, "logits", torch.float32)
@@ -227,7 +239,7 @@ def sample_filtered(logits: torch.Tensor, temperature: torch.Tensor, seed: torch
     _check(top_k, "top_k", torch.int64, (B,))
     _check(top_p, "top_p", torch.float32, (B,))
     out = torch.empty((B,), dtype=torch.int32, device=logits.device)
-    f = _fn("plain", "ib_sample_filtered", [c_void_p, c_int64, c_int64] + [c_void_p] * 7)
+    f = _fn("plain", "ib_sample_filtered", [c_void_p, c_int64, c_int64] + [c_void_p] * 9)
     _call(f, logits.data_ptr(), B, V, temperature.data_ptr(), seed.data_ptr(), step.data_ptr(), top_k.data_ptr(),
-          top_p.data_ptr(), out.data_ptr(), _stream())
+          top_p.data_ptr(), out.data_ptr(), _ptr(feedback), _ptr(slots), _stream())
     return out

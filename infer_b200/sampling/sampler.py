@@ -22,9 +22,11 @@ class Sampler:
         self.device = torch.device(device)
         self._pinned, self._flip = {}, 0
 
-    def sample(self, logits: torch.Tensor, params: Sequence, positions: Sequence[int]) -> torch.Tensor:
+    def sample(self, logits: torch.Tensor, params: Sequence, positions: Sequence[int],
+               feedback: torch.Tensor = None, slots: Sequence[int] = None) -> torch.Tensor:
         """logits float32 [B, vocab] on the device; params: objects with temperature, seed, top_k, top_p;
-        positions: the sampler's step key per row. Returns int32 [B] on the device."""
+        positions: the sampler's step key per row. Returns int32 [B] on the device. With ``feedback`` (int32 per
+        request slot) and ``slots`` (one per row) each token is also left at feedback[slot] for the next step."""
         B = logits.shape[0]
         if B != len(params) or B != len(positions):
             raise ValueError("one SampleParams and one position per row of logits")
@@ -37,6 +39,7 @@ class Sampler:
             host[i, 0] = int(p.seed) & 0x7FFFFFFFFFFFFFFF
             host[i, 1] = int(pos)
             host[i, 2] = int(getattr(p, "top_k", 0) or 0)
+            host[i, 3] = int(slots[i]) if slots is not None else 0
             top_p[i] = float(getattr(p, "top_p", 1.0))
             if temp[i] > 0 and (host[i, 2] > 0 or top_p[i] < 1.0):
                 filtered = True
@@ -53,7 +56,9 @@ class Sampler:
         t = stage[1].to(self.device, non_blocking=True)
         self.last_h2d_bytes = host.nbytes + temp.nbytes
         seed, step = ints[:, 0].contiguous(), ints[:, 1].contiguous()
+        fb = feedback if slots is not None else None
+        sl = ints[:, 3].contiguous() if fb is not None else None
         if not filtered:
-            return ops.sample(logits, t, seed, step)
+            return ops.sample(logits, t, seed, step, fb, sl)
         tp = torch.from_numpy(top_p).pin_memory().to(self.device, non_blocking=True)
-        return ops.sample_filtered(logits, t, seed, step, ints[:, 2].contiguous(), tp)
+        return ops.sample_filtered(logits, t, seed, step, ints[:, 2].contiguous(), tp, fb, sl)

@@ -95,3 +95,20 @@ def test_eos_stops_and_is_included():
     stop = full[4]
     cut = llm.generate([p], max_new=12, eos_id=stop)[0]
     assert cut == full[:full.index(stop) + 1]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+def test_overlap_and_plain_scheduling_generate_the_same(dtype):
+    """Launching a step before the last step's tokens reached the host (they stay on the device for the model) gives
+    the streams of the one-step-at-a-time scheduler: greedy, seeded sampling, eos, and with few pages."""
+    name = "b"
+    cfg = H.TINY[name]
+    prompts = [H.random_ids(cfg, n, 800 + n) for n in (3, 21, 40, 9, 64)]
+    a = _llm(name, dtype, slots=3, max_seq=128, overlap=False)
+    b = _llm(name, dtype, slots=3, max_seq=128, overlap=True)
+    for kw in (dict(max_new=20), dict(max_new=20, temperature=0.9, seed=3), dict(max_new=12, top_k=5, temperature=1.0, seed=1)):
+        assert a.generate(prompts, **kw) == b.generate(prompts, **kw), kw
+    full = a.generate(prompts[:2], max_new=16)
+    stop = full[1][5]
+    assert a.generate(prompts[:2], max_new=16, eos_id=stop) == b.generate(prompts[:2], max_new=16, eos_id=stop)
+    assert b.engine.cache.pages_in_use() == [0]

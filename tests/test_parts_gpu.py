@@ -27,6 +27,7 @@ def _step(cache, entries):
     eng.spec = type("S", (), {"vocab_size": 10 ** 6})()
     eng.rt = _rt(torch.float32)
     eng.status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    eng.next_tokens = torch.zeros(8, dtype=torch.int32, device=DEV)
     for rid, n in entries:
         if rid not in cache.requests:
             cache.admit(rid)

@@ -166,3 +166,42 @@ def test_event_ring_wraps():
     sch.run_until_idle()
     assert len(sch.events) == 4 and sch.events.dropped > 0
     assert sch.events[3].kind == "step" and sch.events[2].kind == "retire"
+
+
+@pytest.mark.parametrize("pages", [1000, 9])
+def test_overlap_mode_gives_the_same_streams(pages):
+    """Launching a step before the previous step's tokens are read changes when tokens are seen, not what they are;
+    with few pages the tokens in flight are read before a victim is chosen."""
+    def run(overlap):
+        eng = FakeEngine(slots=3, max_seq=64, pages=pages, page=4)
+        seen = []
+        sch = Scheduler(eng, SchedulerConfig(max_batch_tokens=16, overlap=overlap, eos_id=2012 if pages == 1000 else -1,
+                                             on_token=lambda r, t: seen.append((r, t))))
+        for rid, plen, mn in ((1, 8, 12), (2, 8, 12), (3, 5, 9), (4, 20, 3)):
+            sch.submit(Request(rid, [0] * plen, mn))
+        sch.run_until_idle()
+        assert eng.len == {} and eng.pages_in_use() == 0 and sch.idle()
+        return {c.id: (c.reason, c.tokens) for c in sch.completed}, seen, sch
+    plain, seen_p, _ = run(False)
+    over, seen_o, sch = run(True)
+    assert plain == over
+    if pages == 1000:
+        assert plain[2] == (StopReason.EOS, [2008, 2009, 2010, 2011, 2012])      # eos is honoured although it is seen late
+    assert sorted(seen_p) == sorted(seen_o)
+    for rid in (1, 2, 3, 4):
+        assert [t for r, t in seen_o if r == rid] == over[rid][1]          # per request, tokens are reported in order
+    if pages == 9:
+        assert sch.preemptions > 0
+
+
+def test_overlap_decode_items_carry_the_feedback_token():
+    from infer_b200.engine.scheduler import FEEDBACK_TOKEN
+    eng = FakeEngine(slots=1)
+    fed = []
+    orig = eng.run
+    eng.run = lambda batch: (fed.append([b.tokens for b in batch]), orig(batch))[1]
+    sch = Scheduler(eng, SchedulerConfig(overlap=True))
+    sch.submit(Request(1, [5, 6, 7], 4))
+    sch.run_until_idle()
+    assert fed[0] == [[5, 6, 7]] and all(step == [[FEEDBACK_TOKEN]] for step in fed[1:4])
+    assert sch.completed[0].tokens == _expected(1, 3, 4)
