@@ -55,6 +55,7 @@ constexpr int PF_SMEM = PF_BM * ROW_BYTES + 2 * 2 * PF_TILE_BYTES;          // Q
 struct AttnParams {
     const bf16* q; const bf16* k_cache; const bf16* v_cache; bf16* out;
     const bf16* qkv; const float* cos; const float* sin; bf16* k_cache_w; bf16* v_cache_w; int write_cache;   // fused decode
+    const void* prefetch; int64_t prefetch_bytes;      // weights of a later kernel to pull into L2 meanwhile
     const int* block_table; int max_blocks;
     const int* seg_start; const int* seg_pos0;
     int n_heads, n_kv, group, window;
@@ -190,6 +191,9 @@ __global__ void __launch_bounds__(DEC_WARPS * 32)
 attn_decode_kernel(const AttnParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ float wgt[MAX_SPLITS][16];                // weight of every rank's partial, per head of the group
+    // This kernel is a chain of latencies and leaves HBM nearly idle: a good time to fetch a later product's weights.
+    ib::l2_prefetch_share(p.prefetch, p.prefetch_bytes, (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x,
+                          gridDim.x * gridDim.y * gridDim.z);
     ib::pdl_wait();
     const int split = blockIdx.x, kvh = blockIdx.y, seg = blockIdx.z;
     const int n_splits = gridDim.x;
@@ -590,7 +594,8 @@ IB_EXPORT int ib_attention_decode_fused(const void* qkv, const float* cos_t, con
                                         void* out, const int* block_table, int max_blocks, const int* seg_start,
                                         const int* seg_pos0, int n_segments, int n_heads, int n_kv, int head_dim,
                                         int page_size, int window, float scale, int64_t n_pages, int write_cache,
-                                        int n_splits, int* status, cudaStream_t stream) {
+                                        int n_splits, int* status, const void* prefetch, int64_t prefetch_bytes,
+                                        cudaStream_t stream) {
     if (n_segments <= 0) return IB_OK;
     int rc = check_common(n_segments, n_heads, n_kv, head_dim, page_size, n_splits, status);
     if (rc) return rc;
@@ -598,6 +603,7 @@ IB_EXPORT int ib_attention_decode_fused(const void* qkv, const float* cos_t, con
     if (!cos_t || !sin_t) return ib::fail(IB_ERR_ARG, "attention_decode_fused: rotation tables are required");
     AttnParams p = {};
     p.qkv = (const bf16*)qkv; p.cos = cos_t; p.sin = sin_t; p.write_cache = write_cache ? 1 : 0;
+    p.prefetch = prefetch; p.prefetch_bytes = prefetch_bytes & ~int64_t(15);
     p.k_cache = (const bf16*)k_cache; p.v_cache = (const bf16*)v_cache; p.k_cache_w = (bf16*)k_cache; p.v_cache_w = (bf16*)v_cache;
     p.out = (bf16*)out;
     p.block_table = block_table; p.max_blocks = max_blocks; p.seg_start = seg_start; p.seg_pos0 = seg_pos0;

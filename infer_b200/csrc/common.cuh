@@ -86,6 +86,21 @@ inline int launch(const char* what, void (*kernel)(KArgs...), dim3 grid, dim3 bl
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// Asks the memory system to bring `bytes` (a multiple of 16) at `base` into L2, this CTA taking its share of the
+// range. Used by decode kernels to fetch the weights of a kernel that runs later, while they themselves are bound by
+// latency and leave HBM idle. A hint: nothing waits for it and nothing breaks if the lines are evicted again.
+__device__ __forceinline__ void l2_prefetch_share(const void* base, int64_t bytes, int cta, int n_cta) {
+    if (!base || bytes <= 0) return;
+    constexpr int64_t PIECE = 4096;
+    const int64_t per = (((bytes + n_cta - 1) / n_cta) + PIECE - 1) / PIECE * PIECE;
+    const int64_t lo = int64_t(cta) * per, hi = lo + per < bytes ? lo + per : bytes;
+    const char* b = static_cast<const char*>(base);
+    for (int64_t off = lo + int64_t(threadIdx.x) * PIECE; off < hi; off += int64_t(blockDim.x) * PIECE) {
+        const uint32_t n = uint32_t(hi - off < PIECE ? hi - off : PIECE) & ~15u;
+        if (n) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(b + off), "r"(n) : "memory");
+    }
+}
+
 template <typename T> __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }

@@ -65,6 +65,8 @@ struct GemvParams {
     int64_t N, K, tiles;
     int cluster, groups;      // CTAs per tile; tile groups in the grid (grid = groups * cluster)
     int stage_x;              // activations staged in shared memory
+    const void* prefetch;     // weights of a later kernel to pull into L2 meanwhile (or null)
+    int64_t prefetch_bytes;
 };
 
 // Occupancy matters more than anything else here (resident warps = bytes in flight): 64 registers for up to 8
@@ -103,6 +105,7 @@ stream_gemv_kernel(const GemvParams p) {
     };
     uint4 a0[UNROLL], a1[UNROLL];
     load_w(c_begin, a0, a1);                             // before the wait: weights have no producer kernel
+    ib::l2_prefetch_share(p.prefetch, p.prefetch_bytes, blockIdx.x, gridDim.x);
     ib::pdl_launch_dependents();                         // the successor may start its own weight loads as SMs free up
     ib::pdl_wait();
 
@@ -245,7 +248,8 @@ int launch(const GemvParams& p, int out_dtype, int epi, int grid_ctas, size_t sm
 // 8); 0 lets the kernel choose from N, K and sm_count.
 IB_EXPORT int ib_linear_skinny(const void* x, const float* norm_w, float eps, const void* w, const float* bias,
                                const float* residual, void* out, int64_t M, int64_t N, int64_t K, int out_dtype, int epi,
-                               int cluster, int sm_count, cudaStream_t stream) {
+                               int cluster, int sm_count, const void* prefetch, int64_t prefetch_bytes,
+                               cudaStream_t stream) {
     if (M <= 0 || N <= 0) return IB_OK;
     if (M > 16) return ib::fail(IB_ERR_ARG, "linear_skinny: at most 16 rows, got %lld", (long long)M);
     if (K <= 0 || K % 8) return ib::fail(IB_ERR_ARG, "linear_skinny: K = %lld must be a positive multiple of 8", (long long)K);
@@ -270,6 +274,7 @@ IB_EXPORT int ib_linear_skinny(const void* x, const float* norm_w, float eps, co
     p.w = (const bf16*)w; p.bias = bias; p.residual = residual; p.out = out;
     p.M = int(M); p.N = N; p.K = K; p.tiles = tiles; p.cluster = cluster;
     p.groups = int(tiles);
+    p.prefetch = prefetch; p.prefetch_bytes = prefetch_bytes & ~int64_t(15);
     p.stage_x = norm_w ? 1 : 0;
     const int rows_pad = M <= 8 ? 8 : 16;
     const size_t smem = norm_w ? size_t(rows_pad) * size_t(K * 2 + XS_PAD) : 0;

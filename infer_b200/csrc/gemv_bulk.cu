@@ -96,6 +96,8 @@ struct GemvParams {
     int64_t tiles;
     int groups;               // tile walkers in the grid (grid = groups * cluster); a walker takes every groups-th tile
     int* status;
+    const void* prefetch;     // weights of a later kernel to pull into L2 meanwhile (or null)
+    int64_t prefetch_bytes;
 };
 
 template <int NT, int EPI, typename TOut>
@@ -156,6 +158,7 @@ bulk_gemv_kernel(const GemvParams p) {
             if (i == NS - 1 || i == n_iter - 1) ib::pdl_launch_dependents();     // the first ring is on its way
         }
         if (n_iter == 0) ib::pdl_launch_dependents();
+        ib::l2_prefetch_share(p.prefetch, p.prefetch_bytes, blockIdx.x, gridDim.x);
         if (cluster > 1) {                               // the cluster barriers below count every thread
             cg::cluster_group cl = cg::this_cluster();
             cl.sync();
@@ -305,7 +308,7 @@ int launch(const GemvParams& p, int out_dtype, int epi, int grid_ctas, cudaStrea
 // sm_count. status: one int in device memory, raised if a bounded wait runs out.
 IB_EXPORT int ib_linear_skinny_bulk(const void* x, const void* w, const float* bias, const float* residual, void* out,
                                     int64_t M, int64_t N, int64_t K, int out_dtype, int epi, int cluster, int sm_count,
-                                    int* status, cudaStream_t stream) {
+                                    int* status, const void* prefetch, int64_t prefetch_bytes, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return IB_OK;
     if (M > 16) return ib::fail(IB_ERR_ARG, "linear_skinny_bulk: at most 16 rows, got %lld", (long long)M);
     if (K <= 0 || K % 8) return ib::fail(IB_ERR_ARG, "linear_skinny_bulk: K = %lld must be a positive multiple of 8", (long long)K);
@@ -325,6 +328,7 @@ IB_EXPORT int ib_linear_skinny_bulk(const void* x, const void* w, const float* b
     GemvParams p;
     p.x = (const bf16*)x; p.w = (const bf16*)w; p.bias = bias; p.residual = residual; p.out = out;
     p.M = int(M); p.N = N; p.K = K; p.cluster = cluster; p.status = status; p.tiles = tiles;
+    p.prefetch = prefetch; p.prefetch_bytes = prefetch_bytes & ~int64_t(15);
     // Three CTAs fit an SM; with more tiles than that, a CTA walks over several and its ring never drains between them.
     int64_t groups = cluster > 1 ? tiles : (tiles < 3LL * sms ? tiles : 3LL * sms);
     p.groups = int(groups);

@@ -35,6 +35,21 @@ class Model:
             self.head.out_features, self.head.in_features = self.embedding.shape
         else:
             self.head = Linear(runtime, weights[spec.head_name])
+        self.head.prefetch_next = None
+        self.plan_prefetch()
+
+    def plan_prefetch(self, distance: int = 2) -> None:
+        """Walks the kernels of a step in run order and tells each to fetch, while it runs, the weights of the kernel
+        `distance` places later (a decode step's kernels are bound by latency and leave HBM idle most of the time;
+        with the hint the next products find their weights in L2)."""
+        line = []
+        for call in self.spec.schedule:
+            b = self.blocks[call.layer]
+            line += list(b.mixer.stations()) + list(b.feed_forward.stations())
+        line.append((self.head, self.head.weight))
+        for i, (holder, _) in enumerate(line):
+            ahead = [w for _, w in line[i + distance:i + distance + 1] if w is not None]
+            holder.prefetch_next = ahead[0] if ahead else None
 
     def _load_part(self, part, family, pspec, weights):
         names = part_class(family, pspec.kind).param_shapes(pspec)

@@ -44,6 +44,7 @@ class Attention(Mixer):
         self.position = build_part("position", pos, runtime) if pos is not None else None
         self.qkv: Optional[Linear] = None
         self.o: Optional[Linear] = None
+        self.prefetch_next = None      # hint for the attention kernel itself (see Part.stations)
 
     @classmethod
     def param_shapes(cls, spec):
@@ -65,6 +66,9 @@ class Attention(Mixer):
     def cache_need(self):
         return PagedKVNeed(self.n_kv, self.head_dim, self.window)
 
+    def stations(self):
+        return [(self.qkv, self.qkv.weight), (self, None), (self.o, self.o.weight)]
+
     def forward(self, x, step, cache, residual, write_cache=True):
         qkv = self.qkv(x)                                              # [T, (heads + 2 kv) * head_dim]
         table = step.block_tables[cache.group]
@@ -80,7 +84,7 @@ class Attention(Mixer):
             from .. import fast_ops
             ctx = fast_ops.attention_decode_fused(qkv, cos, sin, cache.k, cache.v, table, step.seg_start, step.seg_pos0,
                                                   self.n_heads, self.n_kv, self.head_dim, self.window, self.scale,
-                                                  step.max_ctx_len, write_cache)
+                                                  step.max_ctx_len, write_cache, prefetch=self.prefetch_next)
             if ctx is not None:
                 return self.o(ctx, residual=residual)
         if self.rt.fast("rope"):

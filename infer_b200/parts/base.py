@@ -60,6 +60,12 @@ class Part:
         """Receives the part's parameters (CPU tensors in their stored dtype) and moves what it
         needs to the device, in the layout its kernels want."""
 
+    def stations(self):
+        """The part's kernels in run order, for prefetch hints: a list of (holder, weight) where ``weight`` is the big
+        tensor the kernel streams (or None) and ``holder.prefetch_next`` may be set to a tensor that the kernel
+        should pull into L2 while it runs. Parts that do not care return nothing."""
+        return []
+
 
 class DeferredNorm:
     """The float32 rows ``h`` with a norm that has not been applied yet. A part that declares

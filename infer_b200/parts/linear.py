@@ -20,6 +20,7 @@ class Linear:
         self.weight = weight.to(device=rt.device, dtype=rt.dtype).contiguous()
         self.bias = None if bias is None else bias.to(device=rt.device, dtype=torch.float32).contiguous()
         self.out_features, self.in_features = self.weight.shape
+        self.prefetch_next = None      # weights of a product that runs later; decode kernels fetch them into L2
 
     def __call__(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None,
                  out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
@@ -32,7 +33,8 @@ class Linear:
             out_dtype = torch.float32
         if self.rt.fast("linear"):
             from .. import fast_ops
-            y = fast_ops.linear(x, self.weight, self.bias, residual, out_dtype or self.rt.dtype, out)
+            y = fast_ops.linear(x, self.weight, self.bias, residual, out_dtype or self.rt.dtype, out,
+                                prefetch=self.prefetch_next)
             if y is not None:
                 return y
         if isinstance(x, DeferredNorm):
