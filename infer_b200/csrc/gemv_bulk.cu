@@ -39,11 +39,13 @@ using bf16 = __nv_bfloat16;
 constexpr int WARPS = 8;                  // consumer warps; warp 8 is the producer
 constexpr int THREADS = (WARPS + 1) * 32;
 constexpr int ROWS = 16;
-constexpr int KC = 512;                   // elements of K per stage and row (1 KB)
-constexpr int PITCH = KC * 2 + 64;        // bytes between rows of a stage: consecutive rows start 16 banks apart
-constexpr int STAGE_BYTES = ROWS * PITCH;
-constexpr int NS = 4;                     // stages in the ring
-constexpr int SMEM_BYTES = NS * STAGE_BYTES;
+#ifndef IB_GEMV_CTAS_PER_SM
+#define IB_GEMV_CTAS_PER_SM 2
+#endif
+constexpr int KC_MAX = 1536;              // most elements of K per stage and row (3 KB)
+constexpr int CPW_MAX = KC_MAX / 32 / WARPS;   // most 32-element chunks per warp and stage
+constexpr int NS_MAX = 8;                 // most stages in the ring
+constexpr int RING_BYTES = 2 * ROWS * (KC_MAX * 2 + 64);
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
 constexpr int STATUS_TIMEOUT = 104;
 
@@ -93,6 +95,8 @@ struct GemvParams {
     int M;
     int64_t N, K;
     int cluster;              // CTAs per tile
+    int kc;                   // elements of K per stage and row: a multiple of 64, at most KC_MAX
+    int ns;                   // stages in the ring: 2 .. NS_MAX, ns * ROWS * (kc * 2 + 64) <= RING_BYTES
     int64_t tiles;
     int groups;               // tile walkers in the grid (grid = groups * cluster); a walker takes every groups-th tile
     int* status;
@@ -101,10 +105,10 @@ struct GemvParams {
 };
 
 template <int NT, int EPI, typename TOut>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, 2)
 bulk_gemv_kernel(const GemvParams p) {
-    extern __shared__ __align__(128) uint8_t stages[];   // [NS][ROWS][PITCH]
-    __shared__ __align__(8) uint64_t bars[2 * NS];       // full[NS], empty[NS]
+    extern __shared__ __align__(128) uint8_t stages[];   // [ns][ROWS][pitch]
+    __shared__ __align__(8) uint64_t bars[2 * NS_MAX];   // full[ns], empty[ns]
     __shared__ float red[WARPS][NT][8][ROWS];
     __shared__ float part[NT][8][ROWS];                  // this CTA's sum; read by the cluster's first CTA
     __shared__ int failed;
@@ -114,6 +118,9 @@ bulk_gemv_kernel(const GemvParams p) {
     const int rank = cluster > 1 ? int(blockIdx.x % cluster) : 0;
     const int group = blockIdx.x / cluster;              // this CTA walks tiles group, group + groups, ...
     const int64_t K = p.K, N = p.N;
+    const int KC = p.kc, NS = p.ns;
+    const int PITCH = KC * 2 + 64;                       // bytes between rows of a stage: consecutive rows start 16 banks apart
+    const int STAGE_BYTES = ROWS * PITCH;
     // This CTA's slice of K, in stages of KC elements.
     const int64_t total_stages = (K + KC - 1) / KC;
     const int64_t per_cta = (total_stages + cluster - 1) / cluster;
@@ -123,7 +130,7 @@ bulk_gemv_kernel(const GemvParams p) {
     const int64_t n_iter = my_tiles * spt;
     const uint32_t stage0 = smem_u32(stages), bar0 = smem_u32(bars);
     auto full_bar = [&](int s) { return bar0 + 8u * s; };
-    auto empty_bar = [&](int s) { return bar0 + 8u * (NS + s); };
+    auto empty_bar = [&](int s) { return bar0 + 8u * (NS_MAX + s); };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < NS; s++) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), WARPS); }
@@ -133,7 +140,7 @@ bulk_gemv_kernel(const GemvParams p) {
     // Rows beyond N (last tile only) are never copied: start from zeros. A stage that held an earlier tile's rows is
     // harmless there, because those rows' results are not stored.
     if (N % ROWS != 0 && (p.tiles - 1 - group) % p.groups == 0) {     // this CTA takes the last, partial tile
-        for (int i = threadIdx.x; i < SMEM_BYTES / 16; i += THREADS) reinterpret_cast<uint4*>(stages)[i] = make_uint4(0u, 0u, 0u, 0u);
+        for (int i = threadIdx.x; i < RING_BYTES / 16; i += THREADS) reinterpret_cast<uint4*>(stages)[i] = make_uint4(0u, 0u, 0u, 0u);
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     __syncthreads();
@@ -176,7 +183,7 @@ bulk_gemv_kernel(const GemvParams p) {
         xr[nt] = p.x + int64_t(nt * 8 + g) * K + t * 8;
     }
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-    constexpr int CPW = KC / 32 / WARPS;                 // 32-element chunks per warp and stage
+    constexpr int CPW = CPW_MAX;                         // warp w takes the 32-element chunks w, w + 8, ... of a stage
     float acc[NT][4];
 #pragma unroll
     for (int nt = 0; nt < NT; nt++) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.0f;
@@ -192,8 +199,8 @@ bulk_gemv_kernel(const GemvParams p) {
         bool k_ok[CPW];
 #pragma unroll
         for (int u = 0; u < CPW; u++) {
-            const int64_t k = k0 + (warp * CPW + u) * 32;
-            k_ok[u] = k + t * 8 < K;
+            const int64_t k = k0 + (warp + u * WARPS) * 32;
+            k_ok[u] = (warp + u * WARPS) * 32 < KC && k + t * 8 < K;
 #pragma unroll
             for (int nt = 0; nt < NT; nt++)
                 b[u][nt] = (k_ok[u] && x_ok[nt]) ? __ldg(reinterpret_cast<const uint4*>(xr[nt] + k)) : zero;
@@ -205,7 +212,7 @@ bulk_gemv_kernel(const GemvParams p) {
         const uint8_t* st = stages + s * STAGE_BYTES;
 #pragma unroll
         for (int u = 0; u < CPW; u++) {
-            const int cb = ((warp * CPW + u) * 32 + t * 8) * 2;
+            const int cb = ((warp + u * WARPS) * 32 + t * 8) * 2;
             const uint4 a0 = k_ok[u] ? *reinterpret_cast<const uint4*>(st + g * PITCH + cb) : zero;
             const uint4 a1 = k_ok[u] ? *reinterpret_cast<const uint4*>(st + (g + 8) * PITCH + cb) : zero;
 #pragma unroll
@@ -281,11 +288,11 @@ int launch(const GemvParams& p, int out_dtype, int epi, int grid_ctas, cudaStrea
         static bool configured = false;                                                                            \
         if (!configured) {                                                                                         \
             cudaError_t e = cudaFuncSetAttribute(bulk_gemv_kernel<NT, EPI_, T_>,                                   \
-                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);         \
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, RING_BYTES);         \
             if (e != cudaSuccess) return ib::fail(IB_ERR_CUDA, "linear_skinny_bulk: cannot set shared memory size: %s", cudaGetErrorString(e)); \
             configured = true;                                                                                     \
         }                                                                                                          \
-        return ib::launch("linear_skinny_bulk", bulk_gemv_kernel<NT, EPI_, T_>, grid, block, size_t(SMEM_BYTES), stream, cl, p); \
+        return ib::launch("linear_skinny_bulk", bulk_gemv_kernel<NT, EPI_, T_>, grid, block, size_t(RING_BYTES), stream, cl, p); \
     } while (0)
     if (epi == 2) {
         if (out_dtype != IB_BF16) return ib::fail(IB_ERR_ARG, "linear_skinny_bulk: the SwiGLU epilogue writes bfloat16");
@@ -318,19 +325,25 @@ IB_EXPORT int ib_linear_skinny_bulk(const void* x, const void* w, const float* b
     const int64_t tiles = (N + ROWS - 1) / ROWS;
     if (tiles > 0x7fffffffLL / 8) return ib::fail(IB_ERR_ARG, "linear_skinny_bulk: N too large");
     const int sms = sm_count > 0 ? sm_count : 148;
+    // A stage holds ROWS rows of kc elements: K in as few equal stages as the ring allows (a whole row for K up to
+    // KC_MAX), since the cost of a stage (its copies, the barrier round trip) does not depend on its size.
+    const int64_t n_stages = (K + KC_MAX - 1) / KC_MAX;
+    const int kc = int(((K + n_stages - 1) / n_stages + 63) / 64 * 64);
+    int ns = RING_BYTES / (ROWS * (kc * 2 + 64));
+    if (ns > NS_MAX) ns = NS_MAX;
     if (cluster == 0) {
-        // Share a tile among CTAs while the tiles alone leave SMs idle and every CTA keeps at least two stages of K.
+        // Share a tile among CTAs while the tiles alone leave SMs idle and every CTA keeps at least three stages of K.
         cluster = 1;
-        const int64_t n_stages = (K + KC - 1) / KC;
-        while (cluster < 8 && tiles * cluster < 2LL * sms && n_stages / (cluster * 2) >= 2) cluster *= 2;
+        while (cluster < 8 && tiles * cluster < 2LL * sms && n_stages >= 6 * cluster) cluster *= 2;
     }
     if (cluster != 1 && cluster != 2 && cluster != 4 && cluster != 8) return ib::fail(IB_ERR_ARG, "linear_skinny_bulk: cluster must be 1, 2, 4 or 8");
     GemvParams p;
     p.x = (const bf16*)x; p.w = (const bf16*)w; p.bias = bias; p.residual = residual; p.out = out;
-    p.M = int(M); p.N = N; p.K = K; p.cluster = cluster; p.status = status; p.tiles = tiles;
+    p.M = int(M); p.N = N; p.K = K; p.cluster = cluster; p.status = status; p.tiles = tiles; p.kc = kc; p.ns = ns;
     p.prefetch = prefetch; p.prefetch_bytes = prefetch_bytes & ~int64_t(15);
-    // Three CTAs fit an SM; with more tiles than that, a CTA walks over several and its ring never drains between them.
-    int64_t groups = cluster > 1 ? tiles : (tiles < 3LL * sms ? tiles : 3LL * sms);
+    // Two CTAs fit an SM; with more tiles than that, a CTA walks over several and its ring never drains between them.
+    constexpr int64_t PER_SM = IB_GEMV_CTAS_PER_SM;
+    int64_t groups = cluster > 1 ? tiles : (tiles < PER_SM * sms ? tiles : PER_SM * sms);
     p.groups = int(groups);
     const int grid_ctas = int(groups) * cluster;
     if (M <= 8) return launch<1>(p, out_dtype, epi, grid_ctas, stream);
