@@ -31,6 +31,7 @@ MODULES: Dict[str, str] = {
     "plain": "plain_ops.cu",
     "gemv": "gemv.cu",
     "gemvb": "gemv_bulk.cu",
+    "chain": "linear_chain.cu",
     "gemm": "gemm_tcgen05.cu",
     "attn": "attention_fast.cu",
 }

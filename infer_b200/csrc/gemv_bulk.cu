@@ -22,6 +22,10 @@
 // pair those elements in an order that differs from the natural k order, identically for weights and activations,
 // which leaves every dot product unchanged.
 //
+// For K <= 1536 a tile is one stage and a lane's fragments of the activations are the same in every tile: they are
+// read once per CTA, and the RMSNorm that precedes the product in a decoder layer can be applied to them in
+// registers (one pass over the float rows, the sum of squares put together from the warps' shares in warp order).
+//
 // Epilogues: (0) + bias -> bfloat16 or float; (1) + residual (float, may alias out) -> float; (2) SwiGLU for a
 // gate/up matrix whose rows are interleaved in blocks of 8 (rows 16b..16b+7 = gate features 8b..8b+7, rows
 // 16b+8..16b+15 = the matching up features): out[m, 8b + r] = silu(gate) * up, bfloat16 [M, N/2].
@@ -87,7 +91,9 @@ __device__ __forceinline__ void mma_bf16(float* c, uint32_t a0, uint32_t a1, uin
 }
 
 struct GemvParams {
-    const bf16* x;            // [M, K]
+    const bf16* x;            // [M, K]; or, with norm_w, float rows that are RMS-normalised first (K <= KC_MAX)
+    const float* norm_w;      // [K] or null
+    float eps;
     const bf16* w;            // [N, K]
     const float* bias;        // [N] or null
     const float* residual;    // [M, N] or null
@@ -111,6 +117,7 @@ bulk_gemv_kernel(const GemvParams p) {
     __shared__ __align__(8) uint64_t bars[2 * NS_MAX];   // full[ns], empty[ns]
     __shared__ float red[WARPS][NT][8][ROWS];
     __shared__ float part[NT][8][ROWS];                  // this CTA's sum; read by the cluster's first CTA
+    __shared__ float sumsq[WARPS][NT * 8];               // the warps' shares of a row's sum of squares (fused norm)
     __shared__ int failed;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -174,6 +181,13 @@ bulk_gemv_kernel(const GemvParams p) {
         return;
     }
     // -------------------------------------------------------------------- consumers (warps 0..7)
+    if (p.norm_w) {                                      // the norm's weight does not come from the predecessor: into L1 now
+#pragma unroll
+        for (int u = 0; u < CPW_MAX; u++) {
+            const int64_t k = (warp + u * WARPS) * 32 + t * 8;
+            if (k < K) asm volatile("prefetch.global.L1 [%0];" ::"l"(p.norm_w + k));
+        }
+    }
     ib::pdl_wait();                                      // activations come from the predecessor
     bool x_ok[NT];
     const bf16* xr[NT];
@@ -191,19 +205,101 @@ bulk_gemv_kernel(const GemvParams p) {
     const int r = threadIdx.x & 15, col = (threadIdx.x >> 4) & 7, ant = active ? threadIdx.x >> 7 : 0;
     TOut* out = reinterpret_cast<TOut*>(p.out);
 
+    // With one stage per tile a lane multiplies the same fragments of the activations in every tile: they are
+    // fetched, and normalised if the kernel is given the float residual stream, once.
+    const bool hoist = total_stages == 1;
+    uint4 b[CPW][NT];
+    bool k_ok[CPW];
+    if (hoist && n_iter > 0) {
+#pragma unroll
+        for (int u = 0; u < CPW; u++) k_ok[u] = (warp + u * WARPS) * 32 < KC && (warp + u * WARPS) * 32 + t * 8 < K;
+        if (p.norm_w) {
+            const float* h = reinterpret_cast<const float*>(p.x);
+            uint4 hi[CPW][NT];                           // b holds the first four floats of a fragment meanwhile, hi the rest
+            float ss[NT];
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) ss[nt] = 0.0f;
+#pragma unroll
+            for (int u = 0; u < CPW; u++) {
+                const int64_t k = (warp + u * WARPS) * 32 + t * 8;
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++) {
+                    const uint4* src = reinterpret_cast<const uint4*>(h + int64_t(nt * 8 + g) * K + k);
+                    b[u][nt] = (k_ok[u] && x_ok[nt]) ? src[0] : zero;
+                    hi[u][nt] = (k_ok[u] && x_ok[nt]) ? src[1] : zero;
+                }
+            }
+            auto sq = [](float a, uint4 q) {
+                a = fmaf(__uint_as_float(q.x), __uint_as_float(q.x), a);
+                a = fmaf(__uint_as_float(q.y), __uint_as_float(q.y), a);
+                a = fmaf(__uint_as_float(q.z), __uint_as_float(q.z), a);
+                return fmaf(__uint_as_float(q.w), __uint_as_float(q.w), a);
+            };
+#pragma unroll
+            for (int u = 0; u < CPW; u++) {
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++) ss[nt] = sq(sq(ss[nt], b[u][nt]), hi[u][nt]);
+            }
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) {
+                ss[nt] += __shfl_xor_sync(0xffffffffu, ss[nt], 1);
+                ss[nt] += __shfl_xor_sync(0xffffffffu, ss[nt], 2);
+                if (t == 0) sumsq[warp][nt * 8 + g] = ss[nt];
+            }
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            float scale[NT];
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) {
+                float total = 0.0f;
+#pragma unroll
+                for (int wi = 0; wi < WARPS; wi++) total += sumsq[wi][nt * 8 + g];   // warp order: the same for every batch
+                scale[nt] = rsqrtf(total / float(K) + p.eps);
+            }
+            auto pack = [](float lo, float hi2) {
+                __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi2);
+                return *reinterpret_cast<uint32_t*>(&v);
+            };
+#pragma unroll
+            for (int u = 0; u < CPW; u++) {
+                const int64_t k = (warp + u * WARPS) * 32 + t * 8;
+                float4 w0 = make_float4(0.f, 0.f, 0.f, 0.f), w1 = w0;
+                if (k_ok[u]) {
+                    w0 = __ldg(reinterpret_cast<const float4*>(p.norm_w + k));
+                    w1 = __ldg(reinterpret_cast<const float4*>(p.norm_w + k) + 1);
+                }
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++) {
+                    const uint4 lo = b[u][nt], up = hi[u][nt];
+                    const float sc = scale[nt];
+                    b[u][nt] = make_uint4(pack(__uint_as_float(lo.x) * sc * w0.x, __uint_as_float(lo.y) * sc * w0.y),
+                                          pack(__uint_as_float(lo.z) * sc * w0.z, __uint_as_float(lo.w) * sc * w0.w),
+                                          pack(__uint_as_float(up.x) * sc * w1.x, __uint_as_float(up.y) * sc * w1.y),
+                                          pack(__uint_as_float(up.z) * sc * w1.z, __uint_as_float(up.w) * sc * w1.w));
+                }
+            }
+        } else {
+#pragma unroll
+            for (int u = 0; u < CPW; u++) {
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++)
+                    b[u][nt] = (k_ok[u] && x_ok[nt]) ? __ldg(reinterpret_cast<const uint4*>(xr[nt] + (warp + u * WARPS) * 32)) : zero;
+            }
+        }
+    }
+
     for (int64_t i = 0; i < n_iter; i++) {
         const int s = int(i % NS);
         const int64_t k0 = (s_begin + i % spt) * KC;
-        // activations of this warp's chunks: independent of the weights, so they are loaded before the wait
-        uint4 b[CPW][NT];
-        bool k_ok[CPW];
+        if (!hoist) {
+            // activations of this warp's chunks: independent of the weights, so they are loaded before the wait
 #pragma unroll
-        for (int u = 0; u < CPW; u++) {
-            const int64_t k = k0 + (warp + u * WARPS) * 32;
-            k_ok[u] = (warp + u * WARPS) * 32 < KC && k + t * 8 < K;
+            for (int u = 0; u < CPW; u++) {
+                const int64_t k = k0 + (warp + u * WARPS) * 32;
+                k_ok[u] = (warp + u * WARPS) * 32 < KC && k + t * 8 < K;
 #pragma unroll
-            for (int nt = 0; nt < NT; nt++)
-                b[u][nt] = (k_ok[u] && x_ok[nt]) ? __ldg(reinterpret_cast<const uint4*>(xr[nt] + k)) : zero;
+                for (int nt = 0; nt < NT; nt++)
+                    b[u][nt] = (k_ok[u] && x_ok[nt]) ? __ldg(reinterpret_cast<const uint4*>(xr[nt] + k)) : zero;
+            }
         }
         if (!mbar_wait(full_bar(s), uint32_t(i / NS) & 1u)) {
             if (lane == 0) { atomicExch(p.status, STATUS_TIMEOUT); failed = 1; }
@@ -310,10 +406,11 @@ int launch(const GemvParams& p, int out_dtype, int epi, int grid_ctas, cudaStrea
 
 }  // namespace
 
-// x: bfloat16 [M, K]. epi: 0 = (+ bias), 1 = (+ bias) + residual -> float, 2 = SwiGLU over rows interleaved by 8 ->
+// x: bfloat16 [M, K]; with norm_w (float [K]) x is float [M, K] and is RMS-normalised (eps norm_eps) on the way in,
+// each CTA once for all its tiles (K <= 1536). epi: 0 = (+ bias), 1 = (+ bias) + residual -> float, 2 = SwiGLU over rows interleaved by 8 ->
 // bfloat16 [M, N/2]. cluster: CTAs that share a tile's K range (1, 2, 4 or 8); 0 lets the kernel choose from N, K and
 // sm_count. status: one int in device memory, raised if a bounded wait runs out.
-IB_EXPORT int ib_linear_skinny_bulk(const void* x, const void* w, const float* bias, const float* residual, void* out,
+IB_EXPORT int ib_linear_skinny_bulk(const void* x, const float* norm_w, float norm_eps, const void* w, const float* bias, const float* residual, void* out,
                                     int64_t M, int64_t N, int64_t K, int out_dtype, int epi, int cluster, int sm_count,
                                     int* status, const void* prefetch, int64_t prefetch_bytes, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return IB_OK;
@@ -322,6 +419,9 @@ IB_EXPORT int ib_linear_skinny_bulk(const void* x, const void* w, const float* b
     if ((uintptr_t(x) & 15) || (uintptr_t(w) & 15)) return ib::fail(IB_ERR_ARG, "linear_skinny_bulk: operands must be 16-byte aligned");
     if (epi == 2 && N % 16) return ib::fail(IB_ERR_ARG, "linear_skinny_bulk: the SwiGLU epilogue needs N to be a multiple of 16");
     if (!status) return ib::fail(IB_ERR_ARG, "linear_skinny_bulk: a status word is required");
+    if (norm_w && (K > KC_MAX || (uintptr_t(norm_w) & 15)))
+        return ib::fail(IB_ERR_ARG, "linear_skinny_bulk: the fused norm takes K <= %d and a 16-byte aligned weight", KC_MAX);
+    if (norm_w && cluster > 1) return ib::fail(IB_ERR_ARG, "linear_skinny_bulk: the fused norm does not share a tile among CTAs");
     const int64_t tiles = (N + ROWS - 1) / ROWS;
     if (tiles > 0x7fffffffLL / 8) return ib::fail(IB_ERR_ARG, "linear_skinny_bulk: N too large");
     const int sms = sm_count > 0 ? sm_count : 148;
@@ -338,7 +438,7 @@ IB_EXPORT int ib_linear_skinny_bulk(const void* x, const void* w, const float* b
     }
     if (cluster != 1 && cluster != 2 && cluster != 4 && cluster != 8) return ib::fail(IB_ERR_ARG, "linear_skinny_bulk: cluster must be 1, 2, 4 or 8");
     GemvParams p;
-    p.x = (const bf16*)x; p.w = (const bf16*)w; p.bias = bias; p.residual = residual; p.out = out;
+    p.x = (const bf16*)x; p.norm_w = norm_w; p.eps = norm_eps; p.w = (const bf16*)w; p.bias = bias; p.residual = residual; p.out = out;
     p.M = int(M); p.N = N; p.K = K; p.cluster = cluster; p.status = status; p.tiles = tiles; p.kc = kc; p.ns = ns;
     p.prefetch = prefetch; p.prefetch_bytes = prefetch_bytes & ~int64_t(15);
     // Two CTAs fit an SM; with more tiles than that, a CTA walks over several and its ring never drains between them.
