@@ -194,7 +194,11 @@ attn_decode_kernel(const AttnParams p) {
     // This kernel is a chain of latencies and leaves HBM nearly idle: a good time to fetch a later product's weights.
     ib::l2_prefetch_share(p.prefetch, p.prefetch_bytes, (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x,
                           gridDim.x * gridDim.y * gridDim.z);
-    ib::pdl_wait();
+    // Everything this kernel reads before the wait below was written before the step began (segment and block
+    // tables, the cache rows of earlier positions): with the rotation and the cache write fused in, the pages of the
+    // old keys are requested while the kernel that makes q, k and v is still running.
+    const bool early = FUSED && p.write_cache;
+    if (!early) ib::pdl_wait();
     const int split = blockIdx.x, kvh = blockIdx.y, seg = blockIdx.z;
     const int n_splits = gridDim.x;
     const int t = p.seg_start[seg];
@@ -211,6 +215,39 @@ attn_decode_kernel(const AttnParams p) {
     const int* table = p.block_table + int64_t(seg) * p.max_blocks;
     const int G = p.group;
     const int64_t qkv_row = int64_t(t) * (p.n_heads + 2 * p.n_kv) * HD;
+
+    uint8_t* my_ptr = smem + warp * DEC_STAGES * DEC_STAGE_BYTES;
+    const uint32_t my_smem = smem_u32(my_ptr);
+    const int my_pages = pg_end > pg_begin + warp ? (pg_end - pg_begin - warp + DEC_WARPS - 1) / DEC_WARPS : 0;
+
+    auto issue = [&](int i) {
+        if (i < my_pages) {
+            const int pg = pg_begin + warp + i * DEC_WARPS;
+            int page = table[pg];
+            if (page < 0 || page >= p.n_pages) { atomicExch(p.status, 3); page = -1; }
+            const uint32_t dst = my_smem + (i % DEC_STAGES) * DEC_STAGE_BYTES;
+            const int64_t base = page < 0 ? 0 : ((int64_t(page) * p.n_kv + kvh) * PAGE) * HD;
+#pragma unroll
+            for (int c = lane; c < PAGE * CHUNKS; c += 32) {
+                const int row = c / CHUNKS, col = c % CHUNKS;
+                const int key = pg * PAGE + row;
+                // rows not written yet read as zeros (with FUSED the row of `pos` itself comes from the projections)
+                const int bytes = (page >= 0 && (FUSED && p.write_cache ? key < pos : key <= pos)) ? 16 : 0;
+                cp_async16(dst + row * ROW_BYTES + col * 16, p.k_cache + base + row * HD + col * 8, bytes);
+                cp_async16(dst + PAGE * ROW_BYTES + row * ROW_BYTES + col * 16, p.v_cache + base + row * HD + col * 8, bytes);
+            }
+        }
+        cp_commit();
+    };
+
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
+    float o[HD / 8][4];
+#pragma unroll
+    for (int n = 0; n < HD / 8; n++) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f;
+
+#pragma unroll
+    for (int i = 0; i < DEC_STAGES - 1; i++) issue(i);
+    if (early) ib::pdl_wait();                           // q, k and v of this step come from the predecessor
 
     // Query fragments straight from global memory: tile row = head within the group, zero beyond it.
     uint32_t qf[KS][4];
@@ -245,37 +282,6 @@ attn_decode_kernel(const AttnParams p) {
             qf[ks][3] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(qb + (g + 8) * HD + d + 8) : 0u;
         }
     }
-    uint8_t* my_ptr = smem + warp * DEC_STAGES * DEC_STAGE_BYTES;
-    const uint32_t my_smem = smem_u32(my_ptr);
-    const int my_pages = pg_end > pg_begin + warp ? (pg_end - pg_begin - warp + DEC_WARPS - 1) / DEC_WARPS : 0;
-
-    auto issue = [&](int i) {
-        if (i < my_pages) {
-            const int pg = pg_begin + warp + i * DEC_WARPS;
-            int page = table[pg];
-            if (page < 0 || page >= p.n_pages) { atomicExch(p.status, 3); page = -1; }
-            const uint32_t dst = my_smem + (i % DEC_STAGES) * DEC_STAGE_BYTES;
-            const int64_t base = page < 0 ? 0 : ((int64_t(page) * p.n_kv + kvh) * PAGE) * HD;
-#pragma unroll
-            for (int c = lane; c < PAGE * CHUNKS; c += 32) {
-                const int row = c / CHUNKS, col = c % CHUNKS;
-                const int key = pg * PAGE + row;
-                // rows not written yet read as zeros (with FUSED the row of `pos` itself comes from the projections)
-                const int bytes = (page >= 0 && (FUSED && p.write_cache ? key < pos : key <= pos)) ? 16 : 0;
-                cp_async16(dst + row * ROW_BYTES + col * 16, p.k_cache + base + row * HD + col * 8, bytes);
-                cp_async16(dst + PAGE * ROW_BYTES + row * ROW_BYTES + col * 16, p.v_cache + base + row * HD + col * 8, bytes);
-            }
-        }
-        cp_commit();
-    };
-
-    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
-    float o[HD / 8][4];
-#pragma unroll
-    for (int n = 0; n < HD / 8; n++) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f;
-
-#pragma unroll
-    for (int i = 0; i < DEC_STAGES - 1; i++) issue(i);
     for (int i = 0; i < my_pages; i++) {
         cp_wait<DEC_STAGES - 2>();
         __syncwarp();
