@@ -247,6 +247,12 @@ attn_decode_kernel(const AttnParams p) {
 
 #pragma unroll
     for (int i = 0; i < DEC_STAGES - 1; i++) issue(i);
+    if constexpr (FUSED) {                               // the rotation's table rows, on their way meanwhile
+        if (lane * 32 < HD / 2) {
+            asm volatile("prefetch.global.L1 [%0];" ::"l"(p.cos + int64_t(pos) * (HD / 2) + lane * 32));
+            asm volatile("prefetch.global.L1 [%0];" ::"l"(p.sin + int64_t(pos) * (HD / 2) + lane * 32));
+        }
+    }
     if (early) ib::pdl_wait();                           // q, k and v of this step come from the predecessor
 
     // Query fragments straight from global memory: tile row = head within the group, zero beyond it.

@@ -4,7 +4,7 @@
 // The kernel is bound by HBM bandwidth: the weights are read exactly once and everything is arranged so that as many
 // bytes as possible are in flight per SM without costing registers or issue slots.
 //
-// A tile is 16 output features. For small N a thread-block cluster of 2, 4 or 8 CTAs owns a tile and each CTA takes
+// A tile is 16 output features. For small N a thread-block cluster of up to 8 CTAs owns a tile and each CTA takes
 // a slice of K; for large N the grid is three CTAs per SM and a CTA walks over many tiles, its copy ring running ahead
 // into the next tile while the current one is reduced. A producer warp streams the tile's rows into a ring of shared-memory stages with bulk
 // asynchronous copies (cp.async.bulk, one per row and stage, completion counted on an mbarrier); eight consumer
@@ -427,16 +427,19 @@ IB_EXPORT int ib_linear_skinny_bulk(const void* x, const float* norm_w, float no
     const int sms = sm_count > 0 ? sm_count : 148;
     // A stage holds ROWS rows of kc elements: K in as few equal stages as the ring allows (a whole row for K up to
     // KC_MAX), since the cost of a stage (its copies, the barrier round trip) does not depend on its size.
-    const int64_t n_stages = (K + KC_MAX - 1) / KC_MAX;
-    const int kc = int(((K + n_stages - 1) / n_stages + 63) / 64 * 64);
-    int ns = RING_BYTES / (ROWS * (kc * 2 + 64));
-    if (ns > NS_MAX) ns = NS_MAX;
+    int64_t n_stages = (K + KC_MAX - 1) / KC_MAX;
     if (cluster == 0) {
-        // Share a tile among CTAs while the tiles alone leave SMs idle and every CTA keeps at least three stages of K.
+        // Share a tile among CTAs while the tiles alone leave SMs idle and every CTA keeps at least three stages of K
+        // (measured on B200 for K = 8960: 10.8 us alone, 8.9 us in pairs, 14.4 us in fours; clusters of three or six
+        // run slower still).
         cluster = 1;
         while (cluster < 8 && tiles * cluster < 2LL * sms && n_stages >= 6 * cluster) cluster *= 2;
     }
     if (cluster != 1 && cluster != 2 && cluster != 4 && cluster != 8) return ib::fail(IB_ERR_ARG, "linear_skinny_bulk: cluster must be 1, 2, 4 or 8");
+    n_stages = (n_stages + cluster - 1) / cluster * cluster;     // the same number of stages for every CTA of a cluster
+    const int kc = int(((K + n_stages - 1) / n_stages + 63) / 64 * 64);
+    int ns = RING_BYTES / (ROWS * (kc * 2 + 64));
+    if (ns > NS_MAX) ns = NS_MAX;
     GemvParams p;
     p.x = (const bf16*)x; p.norm_w = norm_w; p.eps = norm_eps; p.w = (const bf16*)w; p.bias = bias; p.residual = residual; p.out = out;
     p.M = int(M); p.N = N; p.K = K; p.cluster = cluster; p.status = status; p.tiles = tiles; p.kc = kc; p.ns = ns;
