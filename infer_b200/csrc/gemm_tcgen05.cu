@@ -14,9 +14,13 @@
 //   plain   A = x (tokens on the 128-row side), B = w;  for many tokens (prefill)
 //   swap    A = w (output features on the 128-row side), B = x, tokens on the BN side padded to 16/32/64;
 //           for few tokens (decode), where the weights are streamed once and the tensor core's M is not wasted.
-// With few tiles the K range is cut into `splits` slices (grid.z); each CTA writes a float partial tile to the
-// workspace, and the CTA that arrives last at the tile's counter adds the slices in ascending order (so the sum
-// does not depend on arrival order) and runs the epilogue.
+// With few tiles the K range is cut into `splits` slices. In the swapped mapping the slices of a tile are the CTAs
+// of one thread-block cluster: each leaves its float tile in its shared memory and every CTA adds a share of the
+// columns over all slices, in ascending order, through distributed shared memory. Otherwise (grid.z) each CTA writes
+// its float tile to a workspace and the CTA that arrives last at the tile's counter adds the slices in ascending
+// order. Either way the sum does not depend on arrival order.
+// In the swapped mapping the ring takes up to eight stages (the CTA has the SM to itself and all of its weights
+// should be in flight) and the weights' first stages are requested before the kernel waits for its predecessor.
 //
 // Sizes: any M, N >= 1; K a multiple of 8 (TMA needs 16-byte row pitch); rows beyond M, N and columns beyond K are
 // zero-filled by TMA and masked at the store. Everything else is refused with an error.
@@ -73,6 +77,20 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
 }
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t map_cluster(uint32_t local_smem, uint32_t rank) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_smem), "r"(rank));
+    return remote;
+}
+__device__ __forceinline__ float ld_cluster_f32(uint32_t addr) {
+    float v;
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+    return v;
+}
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
     asm volatile(
@@ -146,6 +164,9 @@ struct GemmParams {
     float* workspace;                    // [splits, tiles, 128, BN] partials (splits > 1)
     unsigned int* counters;              // [tiles], zero between calls
     int* status;
+    int stages;                          // stages of the operand ring in use (<= Cfg::MAX_STAGES)
+    int cluster_split;                   // 1: the K slices of a tile are the CTAs of one cluster (grid.x) and are added
+                                         //    through distributed shared memory; no workspace, no counters
 };
 
 template <int BN> struct Cfg {
@@ -153,8 +174,11 @@ template <int BN> struct Cfg {
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int STAGES = BN >= 128 ? 3 : (BN >= 64 ? 4 : 5);       // <= ~100 KB: two CTAs per SM
+    static constexpr int MAX_STAGES = BN >= 128 ? 6 : 8;                    // a CTA alone on its SM (decode: all of the ring in flight)
     static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static constexpr int SMEM_EXTRA = 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static constexpr int SMEM_BYTES = MAX_STAGES * STAGE_BYTES + SMEM_EXTRA;
+    static_assert(BM * BN * 4 <= STAGES * STAGE_BYTES, "a float partial tile must fit the smallest ring");
 };
 
 template <typename TOut> __device__ __forceinline__ void store_elem(TOut* p, float v);
@@ -163,7 +187,7 @@ template <> __device__ __forceinline__ void store_elem<bf16>(bf16* p, float v) {
 
 // Applies bias/residual and stores 16 accumulator values of tile row `r`, tile columns [c0, c0 + 16).
 template <typename TOut>
-__device__ __forceinline__ void epilogue_store(const GemmParams& p, const float* v, int64_t a_row, int64_t b_row0) {
+__device__ __forceinline__ void epilogue_store(const GemmParams& p, const float* v, int64_t a_row, int64_t b_row0, int ncols = 16) {
     TOut* out = reinterpret_cast<TOut*>(p.out);
     if (p.epi == 2) {
         // Feature rows come in blocks of 16: 8 gate rows, then the 8 matching up rows. out[m, 8 blk + r] = silu(g) * u.
@@ -176,7 +200,7 @@ __device__ __forceinline__ void epilogue_store(const GemmParams& p, const float*
             for (int j = 0; j < 16; j++) {
                 const float other = __shfl_xor_sync(0xffffffffu, v[j], 8);
                 const int64_t m = b_row0 + j;
-                if (is_gate && n < p.N && m < p.M) {
+                if (is_gate && n < p.N && m < p.M && j < ncols) {
                     const float gte = v[j];
                     store_elem<TOut>(out + m * half + (n >> 4) * 8 + (n & 7), gte / (1.0f + expf(-gte)) * other);
                 }
@@ -212,7 +236,7 @@ __device__ __forceinline__ void epilogue_store(const GemmParams& p, const float*
 #pragma unroll
         for (int j = 0; j < 16; j++) {
             const int64_t m = b_row0 + j;
-            if (m < p.M) {
+            if (m < p.M && j < ncols) {
                 float x = v[j] + b;
                 if (p.residual) x += p.residual[m * p.N + n];
                 store_elem<TOut>(out + m * p.N + n, x);
@@ -274,22 +298,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     // Operand stages need 1024-byte alignment for the 128-byte swizzle pattern.
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
-    const uint32_t bars = base + C::STAGES * C::STAGE_BYTES;                  // full[S], empty[S], tmem_full
-    volatile uint32_t* slots = reinterpret_cast<volatile uint32_t*>(base_ptr + C::STAGES * C::STAGE_BYTES + (2 * C::STAGES + 1) * 8);
+    const int S = p.stages;
+    const uint32_t bars = base + S * C::STAGE_BYTES;                          // full[S], empty[S], tmem_full
+    volatile uint32_t* slots = reinterpret_cast<volatile uint32_t*>(base_ptr + S * C::STAGE_BYTES + (2 * S + 1) * 8);
     // slots[0] = TMEM base address, slots[1] = abort flag, slots[2] = "this CTA reduces the split-K slices"
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tile_a = blockIdx.x, tile_b = blockIdx.y, split = blockIdx.z;
+    // grid (tiles a, tiles b, slices), or with the slices as one cluster: (slices, tiles a, tiles b)
+    const int tile_a = p.cluster_split ? blockIdx.y : blockIdx.x, tile_b = p.cluster_split ? blockIdx.z : blockIdx.y;
+    const int split = p.cluster_split ? blockIdx.x : blockIdx.z;
     const int kb0 = split * p.kb_per_split;
     const int kb1 = min(p.kb_total, kb0 + p.kb_per_split);
     const int n_kb = kb1 - kb0;
 
     auto full_bar = [&](int s) { return bars + 8u * s; };
-    auto empty_bar = [&](int s) { return bars + 8u * (C::STAGES + s); };
-    const uint32_t tmem_full_bar = bars + 8u * (2 * C::STAGES);
+    auto empty_bar = [&](int s) { return bars + 8u * (S + s); };
+    const uint32_t tmem_full_bar = bars + 8u * (2 * S);
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < C::STAGES; s++) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (int s = 0; s < S; s++) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
         mbar_init(tmem_full_bar, 1);
         slots[1] = 0; slots[2] = 0;
         fence_barrier_init();
@@ -304,17 +331,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = slots[0];
-    ib::pdl_wait();                       // set-up above overlapped the predecessor; operands are touched from here on
+    // The set-up above overlapped the predecessor. Each role waits for it where it first touches what the predecessor
+    // may have written: the producer before it loads activations, the epilogue before it reads or writes the output.
 
     if (warp == 0) {
         // ---------------------------------------------------------------- TMA producer
         if (lane != 0) ib::pdl_launch_dependents();
         if (lane == 0) {
             int issued = 0;
-            for (int i = 0; i < n_kb; i++) {
-                const int s = i % C::STAGES;
-                const uint32_t round = i / C::STAGES;
-                if (i >= C::STAGES && !mbar_wait(empty_bar(s), (round - 1) & 1)) {
+            // With the weights on the A side (decode) their first stages set out before the wait: no kernel writes them.
+            const int pre = p.swap ? min(S, n_kb) : 0;
+            for (int i = 0; i < pre; i++) {
+                mbar_expect_tx(full_bar(i), C::STAGE_BYTES);
+                tma_load_2d(base + i * C::STAGE_BYTES, &tm_a, full_bar(i), (kb0 + i) * BK, tile_a * BM);
+            }
+            ib::pdl_wait();
+            for (int i = 0; i < pre; i++)
+                tma_load_2d(base + i * C::STAGE_BYTES + C::A_BYTES, &tm_b, full_bar(i), (kb0 + i) * BK, tile_b * BN);
+            issued = pre;
+            for (int i = pre; i < n_kb; i++) {
+                const int s = i % S;
+                const uint32_t round = i / S;
+                if (i >= S && !mbar_wait(empty_bar(s), (round - 1) & 1)) {
                     atomicExch(p.status, STATUS_TIMEOUT_PRODUCER); slots[1] = 1; break;
                 }
                 if (slots[1]) break;
@@ -327,7 +365,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             if (slots[1]) {
                 // Drain: wait (bounded) until every copy this thread started has landed, so that none writes into
                 // shared memory after the CTA is gone.
-                for (int i = max(0, issued - C::STAGES); i < issued; i++) mbar_wait(full_bar(i % C::STAGES), (i / C::STAGES) & 1);
+                for (int i = max(0, issued - S); i < issued; i++) mbar_wait(full_bar(i % S), (i / S) & 1);
             }
         }
     } else if (warp == 1) {
@@ -335,8 +373,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         if (lane == 0) {
             constexpr uint32_t idesc = make_idesc(BN);
             for (int i = 0; i < n_kb; i++) {
-                const int s = i % C::STAGES;
-                if (!mbar_wait(full_bar(s), (i / C::STAGES) & 1)) {
+                const int s = i % S;
+                if (!mbar_wait(full_bar(s), (i / S) & 1)) {
                     atomicExch(p.status, STATUS_TIMEOUT_MMA); slots[1] = 1; break;
                 }
                 tc_fence_after();
@@ -357,6 +395,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         const int quad = warp & 3;                                  // this warp may touch TMEM lanes [32 quad, 32 quad + 32)
         const int r = quad * 32 + lane;                             // tile row
         const int64_t a_row = int64_t(tile_a) * BM + r;
+        ib::pdl_wait();
         bool ok = mbar_wait(tmem_full_bar, 0);
         if (!ok) { atomicExch(p.status, STATUS_TIMEOUT_EPILOGUE); slots[1] = 1; }
         ok = __all_sync(0xffffffffu, ok);
@@ -364,7 +403,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         if (ok) {
             const int n_tiles = gridDim.x * gridDim.y;
             const int tile = tile_b * gridDim.x + tile_a;
-            if (p.splits == 1) {
+            if (p.cluster_split) {
+                // This slice's tile goes to the start of the ring (every stage has been consumed), column-major like
+                // the workspace slices: the cluster adds the slices below.
+                float* mine = reinterpret_cast<float*>(base_ptr) + r;
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 16) {
+                    uint32_t raw[16];
+                    tmem_ld16(tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(c), raw);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 16; j++) mine[(c + j) * BM] = __uint_as_float(raw[j]);
+                }
+            } else if (p.splits == 1) {
 #pragma unroll 1
                 for (int c = 0; c < BN; c += 16) {
                     uint32_t raw[16];
@@ -422,6 +473,34 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 }
             }
         }
+    }
+    if (p.cluster_split) {
+        // Every CTA of the cluster adds its share of the tile's columns over all slices, in ascending order of the
+        // slice, reading the other CTAs' tiles through distributed shared memory, and runs the epilogue on them.
+        __syncwarp();
+        cluster_sync();
+        if (warp >= 2 && !slots[1]) {
+            const int r = (warp & 3) * 32 + lane;
+            const int64_t a_row = int64_t(tile_a) * BM + r;
+            const int per = (BN + p.splits - 1) / p.splits;
+            const int c_begin = min(BN, split * per), c_end = min(BN, c_begin + per);
+            const uint32_t local = base + uint32_t(r) * 4u;
+            for (int c0 = c_begin; c0 < c_end; c0 += 16) {
+                const int ncols = min(16, c_end - c0);
+                float v[16];
+#pragma unroll
+                for (int j = 0; j < 16; j++) v[j] = 0.0f;
+                for (int z = 0; z < p.splits; z++) {
+                    const uint32_t remote = map_cluster(local, uint32_t(z));
+#pragma unroll
+                    for (int j = 0; j < 16; j++)
+                        if (j < ncols) v[j] += ld_cluster_f32(remote + uint32_t(c0 + j) * (BM * 4u));
+                }
+                epilogue_store<TOut>(p, v, a_row, int64_t(tile_b) * BN + c0, ncols);
+            }
+        }
+        __syncwarp();
+        cluster_sync();                                  // no CTA leaves while its tile may still be read
     }
     tc_fence_before();
     __syncthreads();
@@ -497,7 +576,20 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, di
         if (e != cudaSuccess) return ib::fail(IB_ERR_CUDA, "gemm_tc: cannot set shared memory size: %s", cudaGetErrorString(e));
         configured = true;
     }
-    return ib::launch("gemm_tc", gemm_tc_kernel<BN, TOut>, grid, dim3(NUM_THREADS), size_t(C::SMEM_BYTES), stream, 1u, ma, mb, p);
+    if (p.stages < 1 || p.stages > C::MAX_STAGES) return ib::fail(IB_ERR_ARG, "gemm_tc: %d stages (at most %d)", p.stages, C::MAX_STAGES);
+    const size_t smem = size_t(p.stages) * C::STAGE_BYTES + C::SMEM_EXTRA;
+    return ib::launch("gemm_tc", gemm_tc_kernel<BN, TOut>, grid, dim3(NUM_THREADS), smem, stream,
+                      p.cluster_split ? unsigned(p.splits) : 1u, ma, mb, p);
+}
+
+// Stages of the ring: the default leaves room for a second CTA on the SM (prefill: one tile's epilogue overlaps the
+// other's main loop); with the weights on the A side a CTA streams them alone, so it takes as many stages as it has
+// k-blocks, up to the whole SM.
+template <int BN> int pick_stages(const GemmParams& p) {
+    using C = Cfg<BN>;
+    if (!p.swap) return C::STAGES;
+    const int want = p.kb_per_split < C::STAGES ? C::STAGES : p.kb_per_split;
+    return want > C::MAX_STAGES ? C::MAX_STAGES : want;
 }
 
 }  // namespace
@@ -515,18 +607,27 @@ IB_EXPORT int ib_gemm_tc_plan(int64_t M, int64_t N, int64_t K, int sm_count, int
     const int64_t rows_a = *swap ? N : M, rows_b = *swap ? M : N;
     const int64_t tiles = ((rows_a + BM - 1) / BM) * ((rows_b + *bn - 1) / *bn);
     if ((rows_b + *bn - 1) / *bn > 65535) return ib::fail(IB_ERR_ARG, "gemm_tc: too many tiles on the grid's second axis");
-    // Slices of K only when the tiles alone leave most of the GPU idle; each slice keeps at least four k-blocks.
+    // Slices of K only when the tiles alone leave most of the GPU idle.
     int s = 1;
     if (sm_count > 0 && tiles * 2 < sm_count) {
-        s = int((sm_count + tiles - 1) / tiles);
-        if (s > 16) s = 16;
-        if (s > kb_total / 4) s = kb_total / 4 > 0 ? kb_total / 4 : 1;
+        if (*swap) {
+            // decode: the slices of a tile form a cluster (at most 8 CTAs) and are added through distributed shared
+            // memory; each slice keeps at least two k-blocks
+            s = int(sm_count / tiles);
+            if (s > 8) s = 8;
+            if (s > kb_total / 2) s = kb_total / 2 > 0 ? kb_total / 2 : 1;
+        } else {
+            // each slice keeps at least four k-blocks
+            s = int((sm_count + tiles - 1) / tiles);
+            if (s > 16) s = 16;
+            if (s > kb_total / 4) s = kb_total / 4 > 0 ? kb_total / 4 : 1;
+        }
     }
     const int per = (kb_total + s - 1) / s;
     s = (kb_total + per - 1) / per;
     *splits = s;
-    *workspace_floats = s > 1 ? int64_t(s) * tiles * BM * (*bn) : 0;
-    *n_counters = s > 1 ? tiles : 0;
+    *workspace_floats = (s > 1 && !*swap) ? int64_t(s) * tiles * BM * (*bn) : 0;
+    *n_counters = (s > 1 && !*swap) ? tiles : 0;
     return IB_OK;
 }
 
@@ -556,11 +657,15 @@ IB_EXPORT int ib_gemm_tc(const void* x, const void* w, const float* bias, const 
     if (splits > p.kb_total) splits = p.kb_total;
     p.kb_per_split = (p.kb_total + splits - 1) / splits;
     p.splits = (p.kb_total + p.kb_per_split - 1) / p.kb_per_split;
-    if (p.splits > 1 && (!workspace || !counters)) return ib::fail(IB_ERR_ARG, "gemm_tc: split-K needs a workspace and counters");
+    p.cluster_split = (p.splits > 1 && !workspace) ? 1 : 0;
+    if (p.cluster_split && (!swap || p.splits > 8))
+        return ib::fail(IB_ERR_ARG, "gemm_tc: split-K without a workspace takes the swapped mapping and at most 8 slices");
+    if (p.splits > 1 && !p.cluster_split && !counters) return ib::fail(IB_ERR_ARG, "gemm_tc: split-K through the workspace needs counters");
     p.bias = bias; p.residual = residual; p.out = out;
     p.workspace = workspace; p.counters = counters; p.status = status;
-    const dim3 grid{unsigned((p.rows_a + BM - 1) / BM), unsigned((p.rows_b + bn - 1) / bn), unsigned(p.splits)};
-    if (grid.y > 65535) return ib::fail(IB_ERR_ARG, "gemm_tc: too many tiles on the grid's second axis");
+    const unsigned ta = unsigned((p.rows_a + BM - 1) / BM), tb = unsigned((p.rows_b + bn - 1) / bn);
+    if (tb > 65535 || (p.cluster_split && ta > 65535)) return ib::fail(IB_ERR_ARG, "gemm_tc: too many tiles on a grid axis");
+    const dim3 grid = p.cluster_split ? dim3{unsigned(p.splits), ta, tb} : dim3{ta, tb, unsigned(p.splits)};
     CUtensorMap ma, mb;
     int rc = get_map(swap ? w : x, p.rows_a, K, BM, &ma);
     if (rc) return rc;
@@ -568,6 +673,7 @@ IB_EXPORT int ib_gemm_tc(const void* x, const void* w, const float* bias, const 
     if (rc) return rc;
     const bool f32 = out_dtype == IB_F32;
     if (!f32 && out_dtype != IB_BF16) return ib::fail(IB_ERR_ARG, "gemm_tc: unknown output dtype %d", out_dtype);
+    p.stages = bn == 16 ? pick_stages<16>(p) : bn == 32 ? pick_stages<32>(p) : bn == 64 ? pick_stages<64>(p) : pick_stages<128>(p);
     switch (bn) {
         case 16: return f32 ? launch<16, float>(ma, mb, p, grid, stream) : launch<16, bf16>(ma, mb, p, grid, stream);
         case 32: return f32 ? launch<32, float>(ma, mb, p, grid, stream) : launch<32, bf16>(ma, mb, p, grid, stream);

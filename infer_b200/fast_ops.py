@@ -100,8 +100,9 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = Non
         out = torch.empty((M, n_out), dtype=out_dtype, device=x.device)
     else:
         _check(out, "out", out_dtype, (M, n_out))
-    ws = st.workspace(ws_floats) if splits > 1 else None
-    cnt = st.counters(n_counters) if splits > 1 else None
+    # split-K of the swapped mapping goes through the cluster's shared memory and needs neither
+    ws = st.workspace(ws_floats) if splits > 1 and ws_floats > 0 else None
+    cnt = st.counters(n_counters) if splits > 1 and ws_floats > 0 else None
     f = _fn("gemm", "ib_gemm_tc", [c_void_p] * 5 + [c_int64] * 3 + [c_int] * 5 + [c_void_p] * 4)
     _call(f, x.data_ptr(), w.data_ptr(), _ptr(bias), _ptr(residual), out.data_ptr(), M, N, K, dtype_code(out_dtype),
           2 if swiglu else 0, swap, bn, splits, _ptr(ws), _ptr(cnt), st.status.data_ptr(), _stream())
