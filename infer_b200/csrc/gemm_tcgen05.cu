@@ -30,6 +30,7 @@
 #include "common.cuh"
 
 #include <cuda.h>
+#include <cstdlib>
 #include <mutex>
 #include <unordered_map>
 
@@ -510,6 +511,156 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     }
 }
 
+
+// ------------------------------------------------------------------------------------------------ persistent kernel
+// For many tokens (prefill). The one-tile kernel above reads (128 + 128) rows of operands for a 128 x 128 tile; at
+// bfloat16 tensor speed that is more than the path from L2 delivers, so it cannot get far beyond half of the tensor
+// peak. Here a CTA owns an SM, walks over 256 x 128 tiles (two M=128 MMAs per k-step share one B tile: a quarter
+// less operand traffic per flop) and keeps two accumulators of 256 columns in tensor memory, so that the epilogue
+// warps drain one tile while the MMA warp already works on the next; the operand ring runs on across tiles.
+constexpr int PBM = 256, PBN = 128, PSTAGES = 4;
+constexpr int P_A_BYTES = PBM * BK * 2, P_B_BYTES = PBN * BK * 2, P_STAGE_BYTES = P_A_BYTES + P_B_BYTES;
+constexpr int P_SMEM_BYTES = PSTAGES * P_STAGE_BYTES + 1024 + 256;
+constexpr int P_TMEM_COLS = 512;
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+template <typename TOut>
+__global__ void __launch_bounds__(NUM_THREADS)
+gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const GemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+    constexpr int S = PSTAGES;
+    const uint32_t bars = base + S * P_STAGE_BYTES;               // full[S], empty[S], acc_full[2], acc_empty[2]
+    volatile uint32_t* slots = reinterpret_cast<volatile uint32_t*>(base_ptr + S * P_STAGE_BYTES + (2 * S + 4) * 8);
+    // slots[0] = TMEM base address, slots[1] = abort flag
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tiles_m = int((p.rows_a + PBM - 1) / PBM), tiles_n = int((p.rows_b + PBN - 1) / PBN);
+    const int n_tiles = tiles_m * tiles_n;
+    const int n_kb = p.kb_total;
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (S + s); };
+    auto acc_full_bar = [&](int b) { return bars + 8u * (2 * S + b); };
+    auto acc_empty_bar = [&](int b) { return bars + 8u * (2 * S + 2 + b); };
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; s++) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (int b = 0; b < 2; b++) { mbar_init(acc_full_bar(b), 1); mbar_init(acc_empty_bar(b), 4); }
+        slots[1] = 0;
+        fence_barrier_init();
+        prefetch_tensormap(&tm_a);
+        prefetch_tensormap(&tm_b);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(const_cast<uint32_t*>(&slots[0])), P_TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = slots[0];
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- TMA producer
+        if (lane == 0) {
+            ib::pdl_wait();
+            int it = 0, issued = 0;
+            for (int tile = blockIdx.x; tile < n_tiles && !slots[1]; tile += gridDim.x) {
+                const int tm = tile % tiles_m, tn = tile / tiles_m;    // neighbouring CTAs share the weight tile
+                for (int kb = 0; kb < n_kb; kb++, it++) {
+                    const int s = it % S;
+                    if (it >= S && !mbar_wait(empty_bar(s), ((it / S) - 1) & 1)) {
+                        atomicExch(p.status, STATUS_TIMEOUT_PRODUCER); slots[1] = 1; break;
+                    }
+                    if (slots[1]) break;
+                    const uint32_t a_dst = base + s * P_STAGE_BYTES, b_dst = a_dst + P_A_BYTES;
+                    mbar_expect_tx(full_bar(s), P_STAGE_BYTES);
+                    tma_load_2d(a_dst, &tm_a, full_bar(s), kb * BK, tm * PBM);
+                    tma_load_2d(b_dst, &tm_b, full_bar(s), kb * BK, tn * PBN);
+                    issued = it + 1;
+                }
+            }
+            if (slots[1]) {
+                // Drain: wait (bounded) until every copy this thread started has landed.
+                for (int i = max(0, issued - S); i < issued; i++) mbar_wait(full_bar(i % S), (i / S) & 1);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc(PBN);
+            int it = 0, lt = 0;
+            for (int tile = blockIdx.x; tile < n_tiles && !slots[1]; tile += gridDim.x, lt++) {
+                const int b = lt & 1;
+                if (lt >= 2 && !mbar_wait(acc_empty_bar(b), ((lt >> 1) - 1) & 1)) {      // the epilogue has drained it
+                    atomicExch(p.status, STATUS_TIMEOUT_MMA); slots[1] = 1; break;
+                }
+                tc_fence_after();
+                const uint32_t d0 = tmem_base + uint32_t(b * 256), d1 = d0 + 128u;
+                for (int kb = 0; kb < n_kb; kb++, it++) {
+                    const int s = it % S;
+                    if (!mbar_wait(full_bar(s), (it / S) & 1)) {
+                        atomicExch(p.status, STATUS_TIMEOUT_MMA); slots[1] = 1; break;
+                    }
+                    tc_fence_after();
+                    const uint32_t a_addr = base + s * P_STAGE_BYTES;
+                    const uint64_t a0 = make_desc(a_addr), a1 = make_desc(a_addr + P_A_BYTES / 2), bd = make_desc(a_addr + P_A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; k++) {
+                        const uint32_t acc = (kb > 0 || k > 0) ? 1u : 0u;
+                        umma_f16(d0, a0 + uint64_t(2 * k), bd + uint64_t(2 * k), idesc, acc);
+                        umma_f16(d1, a1 + uint64_t(2 * k), bd + uint64_t(2 * k), idesc, acc);
+                    }
+                    umma_commit(empty_bar(s));
+                }
+                if (slots[1]) break;
+                umma_commit(acc_full_bar(b));
+            }
+        }
+        ib::pdl_launch_dependents();
+    } else {
+        // ---------------------------------------------------------------- epilogue (warps 2..5)
+        const int quad = warp & 3;
+        ib::pdl_wait();
+        int lt = 0;
+        for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, lt++) {
+            const int tm = tile % tiles_m, tn = tile / tiles_m;
+            const int b = lt & 1;
+            bool ok = !slots[1] && mbar_wait(acc_full_bar(b), (lt >> 1) & 1);
+            if (!ok && !slots[1]) { atomicExch(p.status, STATUS_TIMEOUT_EPILOGUE); slots[1] = 1; }
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
+#pragma unroll 1
+            for (int m = 0; m < 2; m++) {
+                const int64_t a_row = int64_t(tm) * PBM + m * 128 + quad * 32 + lane;
+#pragma unroll 1
+                for (int c = 0; c < PBN; c += 16) {
+                    uint32_t raw[16];
+                    tmem_ld16(tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(b * 256 + m * 128 + c), raw);
+                    tmem_ld_wait();
+                    float v[16];
+#pragma unroll
+                    for (int j = 0; j < 16; j++) v[j] = __uint_as_float(raw[j]);
+                    epilogue_store<TOut>(p, v, a_row, int64_t(tn) * PBN + c);
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty_bar(b));
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, P_TMEM_COLS);
+    }
+}
+
 // ------------------------------------------------------------------------------------------------ host side
 
 using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -582,6 +733,19 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, di
                       p.cluster_split ? unsigned(p.splits) : 1u, ma, mb, p);
 }
 
+template <typename TOut>
+int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, int sm_count, cudaStream_t stream) {
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_persistent_kernel<TOut>, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES);
+        if (e != cudaSuccess) return ib::fail(IB_ERR_CUDA, "gemm_tc: cannot set shared memory size: %s", cudaGetErrorString(e));
+        configured = true;
+    }
+    const int64_t tiles = ((p.rows_a + PBM - 1) / PBM) * ((p.rows_b + PBN - 1) / PBN);
+    const unsigned ctas = unsigned(tiles < sm_count ? tiles : sm_count);
+    return ib::launch("gemm_tc", gemm_tc_persistent_kernel<TOut>, dim3(ctas), dim3(NUM_THREADS), size_t(P_SMEM_BYTES), stream, 1u, ma, mb, p);
+}
+
 // Stages of the ring: the default leaves room for a second CTA on the SM (prefill: one tile's epilogue overlaps the
 // other's main loop); with the weights on the A side a CTA streams them alone, so it takes as many stages as it has
 // k-blocks, up to the whole SM.
@@ -626,6 +790,11 @@ IB_EXPORT int ib_gemm_tc_plan(int64_t M, int64_t N, int64_t K, int sm_count, int
     const int per = (kb_total + s - 1) / s;
     s = (kb_total + per - 1) / per;
     *splits = s;
+    // Many tokens and enough 256 x 128 tiles to occupy the GPU: the persistent kernel (bn = 256 stands for it).
+    static const bool persistent_on = [] { const char* e = getenv("INFER_B200_GEMM_PERSISTENT"); return !(e && e[0] == '0'); }();
+    if (!*swap && s == 1 && persistent_on && sm_count > 0 &&
+        ((M + PBM - 1) / PBM) * ((N + PBN - 1) / PBN) * 2 >= sm_count)
+        *bn = 256;
     *workspace_floats = (s > 1 && !*swap) ? int64_t(s) * tiles * BM * (*bn) : 0;
     *n_counters = (s > 1 && !*swap) ? tiles : 0;
     return IB_OK;
@@ -642,7 +811,8 @@ IB_EXPORT int ib_gemm_tc(const void* x, const void* w, const float* bias, const 
     if (M <= 0 || N <= 0) return IB_OK;
     if (K <= 0 || K % 8) return ib::fail(IB_ERR_ARG, "gemm_tc: K = %lld must be a positive multiple of 8", (long long)K);
     if ((uintptr_t(x) & 15) || (uintptr_t(w) & 15)) return ib::fail(IB_ERR_ARG, "gemm_tc: operand bases must be 16-byte aligned");
-    if (bn != 16 && bn != 32 && bn != 64 && bn != 128) return ib::fail(IB_ERR_ARG, "gemm_tc: bn must be 16, 32, 64 or 128");
+    if (bn != 16 && bn != 32 && bn != 64 && bn != 128 && bn != 256) return ib::fail(IB_ERR_ARG, "gemm_tc: bn must be 16, 32, 64, 128 or 256 (the persistent kernel)");
+    if (bn == 256 && (swap || splits > 1)) return ib::fail(IB_ERR_ARG, "gemm_tc: the persistent kernel takes the plain mapping without K slices");
     if (!status) return ib::fail(IB_ERR_ARG, "gemm_tc: a status word is required");
     if (epi != 0 && epi != 2) return ib::fail(IB_ERR_ARG, "gemm_tc: unknown epilogue %d", epi);
     if (epi == 2 && (N % 16 || bias || residual)) return ib::fail(IB_ERR_ARG, "gemm_tc: the SwiGLU epilogue needs N %% 16 == 0 and no bias or residual");
@@ -666,13 +836,27 @@ IB_EXPORT int ib_gemm_tc(const void* x, const void* w, const float* bias, const 
     const unsigned ta = unsigned((p.rows_a + BM - 1) / BM), tb = unsigned((p.rows_b + bn - 1) / bn);
     if (tb > 65535 || (p.cluster_split && ta > 65535)) return ib::fail(IB_ERR_ARG, "gemm_tc: too many tiles on a grid axis");
     const dim3 grid = p.cluster_split ? dim3{unsigned(p.splits), ta, tb} : dim3{ta, tb, unsigned(p.splits)};
+    const bool f32 = out_dtype == IB_F32;
+    if (!f32 && out_dtype != IB_BF16) return ib::fail(IB_ERR_ARG, "gemm_tc: unknown output dtype %d", out_dtype);
     CUtensorMap ma, mb;
+    if (bn == 256) {
+        int rc = get_map(x, p.rows_a, K, PBM, &ma);
+        if (rc) return rc;
+        rc = get_map(w, p.rows_b, K, PBN, &mb);
+        if (rc) return rc;
+        static int sms = 0;
+        if (!sms) {
+            int dev = 0;
+            if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+                return ib::fail(IB_ERR_CUDA, "gemm_tc: cannot read the number of SMs");
+        }
+        p.splits = 1; p.cluster_split = 0; p.stages = PSTAGES;
+        return f32 ? launch_persistent<float>(ma, mb, p, sms, stream) : launch_persistent<bf16>(ma, mb, p, sms, stream);
+    }
     int rc = get_map(swap ? w : x, p.rows_a, K, BM, &ma);
     if (rc) return rc;
     rc = get_map(swap ? x : w, p.rows_b, K, bn, &mb);
     if (rc) return rc;
-    const bool f32 = out_dtype == IB_F32;
-    if (!f32 && out_dtype != IB_BF16) return ib::fail(IB_ERR_ARG, "gemm_tc: unknown output dtype %d", out_dtype);
     p.stages = bn == 16 ? pick_stages<16>(p) : bn == 32 ? pick_stages<32>(p) : bn == 64 ? pick_stages<64>(p) : pick_stages<128>(p);
     switch (bn) {
         case 16: return f32 ? launch<16, float>(ma, mb, p, grid, stream) : launch<16, bf16>(ma, mb, p, grid, stream);

@@ -20,6 +20,8 @@ SIZES = [
     (2048, 2048, 1536),    # plain, prefill-sized
     (130, 301, 96),        # plain, odd N
     (2, 320, 96),          # swap, K = 1.5 k-blocks
+    (1100, 3000, 520),     # persistent (256 x 128 tiles, two accumulators): ragged M and N, K tail, several tiles per CTA
+    (4000, 4100, 72),      # persistent, many tiles of two k-blocks: the accumulators alternate quickly
 ]
 
 
@@ -122,7 +124,7 @@ def test_skinny_matches_plain(M, N, K, bulk):
     assert torch.equal(one, fast_ops.linear_skinny(x, w, bias, None, torch.float32)[:1])
 
 
-@pytest.mark.parametrize("M", [1, 8, 13, 40, 64, 200])
+@pytest.mark.parametrize("M", [1, 8, 13, 40, 64, 200, 1500])
 @pytest.mark.parametrize("I,H", [(8960, 1536), (224, 96), (176, 80)])
 def test_fused_swiglu_matches_the_two_kernels(M, I, H):
     """gate/up product with the SwiGLU epilogue (rows interleaved in blocks of 8) against plain product + plain SwiGLU,
