@@ -11,7 +11,7 @@
 //          (max, sum, unnormalised output) to the workspace, and the CTA that arrives last at the (segment, kv head)
 //          counter adds the slices in ascending order and writes the result.
 //
-//  prefill (segments of 2 or more tokens)   grid (query tiles, heads, segments). 64 queries of one head per CTA,
+//  prefill (segments of 2 or more tokens)   grid (heads, query tiles from the last to the first, segments). 64 queries of one head per CTA,
 //          16 per warp; keys in tiles of 64 (4 pages) aligned to absolute multiples of 64, double-buffered with
 //          cp.async, causal and window masks applied in registers.
 //
@@ -437,7 +437,9 @@ __global__ void __launch_bounds__(PF_WARPS * 32)
 attn_prefill_kernel(const AttnParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     ib::pdl_wait();
-    const int qt = blockIdx.x, h = blockIdx.y, seg = blockIdx.z;
+    // The last query tiles have the most keys to go through: they start first, for every head (heads are the fast
+    // grid axis), and the short ones fill the gaps at the end.
+    const int qt = gridDim.y - 1 - blockIdx.y, h = blockIdx.x, seg = blockIdx.z;
     const int t0 = p.seg_start[seg];
     const int q_len = p.seg_start[seg + 1] - t0;
     if (q_len == 1 || qt * PF_BM >= q_len) return;
@@ -592,7 +594,8 @@ IB_EXPORT int ib_attention_fast(const void* q, const void* k_cache, const void* 
         if (rc) return rc;
     }
     if (max_q_len > 1) {
-        const dim3 grid{unsigned((max_q_len + PF_BM - 1) / PF_BM), unsigned(n_heads), unsigned(n_segments)};
+        if ((max_q_len + PF_BM - 1) / PF_BM > 65535) return ib::fail(IB_ERR_ARG, "attention_fast: a segment of %lld tokens has too many query tiles", (long long)max_q_len);
+        const dim3 grid{unsigned(n_heads), unsigned((max_q_len + PF_BM - 1) / PF_BM), unsigned(n_segments)};
         return ib::launch("attention_fast (prefill)", attn_prefill_kernel, grid, dim3(PF_WARPS * 32), size_t(PF_SMEM), stream, 1u, p);
     }
     return IB_OK;
