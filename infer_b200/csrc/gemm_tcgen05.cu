@@ -518,8 +518,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 // peak. Here a CTA owns an SM, walks over 256 x 128 tiles (two M=128 MMAs per k-step share one B tile: a quarter
 // less operand traffic per flop) and keeps two accumulators of 256 columns in tensor memory, so that the epilogue
 // warps drain one tile while the MMA warp already works on the next; the operand ring runs on across tiles.
-constexpr int PBM = 256, PBN = 128, PSTAGES = 4;
-constexpr int P_A_BYTES = PBM * BK * 2, P_B_BYTES = PBN * BK * 2, P_STAGE_BYTES = P_A_BYTES + P_B_BYTES;
+// The tile is 256 x 128, or 256 x 96 where that fills the SMs better (a matrix of 1536 features has 12 or 16 column
+// tiles; with 8 row tiles that is 96 or 128 CTAs' worth of work for 148 SMs).
+constexpr int PBM = 256, PSTAGES = 4;
+constexpr int P_A_BYTES = PBM * BK * 2;
+constexpr int P_STAGE_BYTES = P_A_BYTES + 128 * BK * 2;           // sized for the wider tile
 constexpr int P_SMEM_BYTES = PSTAGES * P_STAGE_BYTES + 1024 + 256;
 constexpr int P_TMEM_COLS = 512;
 
@@ -527,7 +530,7 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
-template <typename TOut>
+template <int PBN, typename TOut>
 __global__ void __launch_bounds__(NUM_THREADS)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -577,7 +580,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
                     }
                     if (slots[1]) break;
                     const uint32_t a_dst = base + s * P_STAGE_BYTES, b_dst = a_dst + P_A_BYTES;
-                    mbar_expect_tx(full_bar(s), P_STAGE_BYTES);
+                    mbar_expect_tx(full_bar(s), P_A_BYTES + PBN * BK * 2);
                     tma_load_2d(a_dst, &tm_a, full_bar(s), kb * BK, tm * PBM);
                     tma_load_2d(b_dst, &tm_b, full_bar(s), kb * BK, tn * PBN);
                     issued = it + 1;
@@ -733,17 +736,17 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, di
                       p.cluster_split ? unsigned(p.splits) : 1u, ma, mb, p);
 }
 
-template <typename TOut>
+template <int PBN, typename TOut>
 int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, int sm_count, cudaStream_t stream) {
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_persistent_kernel<TOut>, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_persistent_kernel<PBN, TOut>, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES);
         if (e != cudaSuccess) return ib::fail(IB_ERR_CUDA, "gemm_tc: cannot set shared memory size: %s", cudaGetErrorString(e));
         configured = true;
     }
     const int64_t tiles = ((p.rows_a + PBM - 1) / PBM) * ((p.rows_b + PBN - 1) / PBN);
     const unsigned ctas = unsigned(tiles < sm_count ? tiles : sm_count);
-    return ib::launch("gemm_tc", gemm_tc_persistent_kernel<TOut>, dim3(ctas), dim3(NUM_THREADS), size_t(P_SMEM_BYTES), stream, 1u, ma, mb, p);
+    return ib::launch("gemm_tc", gemm_tc_persistent_kernel<PBN, TOut>, dim3(ctas), dim3(NUM_THREADS), size_t(P_SMEM_BYTES), stream, 1u, ma, mb, p);
 }
 
 // Stages of the ring: the default leaves room for a second CTA on the SM (prefill: one tile's epilogue overlaps the
@@ -792,9 +795,14 @@ IB_EXPORT int ib_gemm_tc_plan(int64_t M, int64_t N, int64_t K, int sm_count, int
     *splits = s;
     // Many tokens and enough 256 x 128 tiles to occupy the GPU: the persistent kernel (bn = 256 stands for it).
     static const bool persistent_on = [] { const char* e = getenv("INFER_B200_GEMM_PERSISTENT"); return !(e && e[0] == '0'); }();
-    if (!*swap && s == 1 && persistent_on && sm_count > 0 &&
-        ((M + PBM - 1) / PBM) * ((N + PBN - 1) / PBN) * 2 >= sm_count)
-        *bn = 256;
+    if (!*swap && s == 1 && persistent_on && sm_count > 0) {
+        // share of the SMs at work over the rounds a tile width needs; the narrower tile moves a tenth more operand
+        // bytes per flop. bn = 256 stands for the 256 x 128 tile, 192 for 256 x 96.
+        const int64_t tm = (M + PBM - 1) / PBM;
+        const int64_t t128 = tm * ((N + 127) / 128), t96 = tm * ((N + 95) / 96);
+        auto fill = [&](int64_t t) { return double(t) / double(((t + sm_count - 1) / sm_count) * sm_count); };
+        if (t128 * 2 >= sm_count) *bn = fill(t96) * 0.9 > fill(t128) ? 192 : 256;
+    }
     *workspace_floats = (s > 1 && !*swap) ? int64_t(s) * tiles * BM * (*bn) : 0;
     *n_counters = (s > 1 && !*swap) ? tiles : 0;
     return IB_OK;
@@ -811,8 +819,9 @@ IB_EXPORT int ib_gemm_tc(const void* x, const void* w, const float* bias, const 
     if (M <= 0 || N <= 0) return IB_OK;
     if (K <= 0 || K % 8) return ib::fail(IB_ERR_ARG, "gemm_tc: K = %lld must be a positive multiple of 8", (long long)K);
     if ((uintptr_t(x) & 15) || (uintptr_t(w) & 15)) return ib::fail(IB_ERR_ARG, "gemm_tc: operand bases must be 16-byte aligned");
-    if (bn != 16 && bn != 32 && bn != 64 && bn != 128 && bn != 256) return ib::fail(IB_ERR_ARG, "gemm_tc: bn must be 16, 32, 64, 128 or 256 (the persistent kernel)");
-    if (bn == 256 && (swap || splits > 1)) return ib::fail(IB_ERR_ARG, "gemm_tc: the persistent kernel takes the plain mapping without K slices");
+    if (bn != 16 && bn != 32 && bn != 64 && bn != 128 && bn != 192 && bn != 256)
+        return ib::fail(IB_ERR_ARG, "gemm_tc: bn must be 16, 32, 64, 128, or 192 or 256 (the persistent kernel's 96 and 128 columns)");
+    if (bn >= 192 && (swap || splits > 1)) return ib::fail(IB_ERR_ARG, "gemm_tc: the persistent kernel takes the plain mapping without K slices");
     if (!status) return ib::fail(IB_ERR_ARG, "gemm_tc: a status word is required");
     if (epi != 0 && epi != 2) return ib::fail(IB_ERR_ARG, "gemm_tc: unknown epilogue %d", epi);
     if (epi == 2 && (N % 16 || bias || residual)) return ib::fail(IB_ERR_ARG, "gemm_tc: the SwiGLU epilogue needs N %% 16 == 0 and no bias or residual");
@@ -839,10 +848,11 @@ IB_EXPORT int ib_gemm_tc(const void* x, const void* w, const float* bias, const 
     const bool f32 = out_dtype == IB_F32;
     if (!f32 && out_dtype != IB_BF16) return ib::fail(IB_ERR_ARG, "gemm_tc: unknown output dtype %d", out_dtype);
     CUtensorMap ma, mb;
-    if (bn == 256) {
+    if (bn >= 192) {
+        const int pbn = bn == 256 ? 128 : 96;
         int rc = get_map(x, p.rows_a, K, PBM, &ma);
         if (rc) return rc;
-        rc = get_map(w, p.rows_b, K, PBN, &mb);
+        rc = get_map(w, p.rows_b, K, pbn, &mb);
         if (rc) return rc;
         static int sms = 0;
         if (!sms) {
@@ -851,7 +861,8 @@ IB_EXPORT int ib_gemm_tc(const void* x, const void* w, const float* bias, const 
                 return ib::fail(IB_ERR_CUDA, "gemm_tc: cannot read the number of SMs");
         }
         p.splits = 1; p.cluster_split = 0; p.stages = PSTAGES;
-        return f32 ? launch_persistent<float>(ma, mb, p, sms, stream) : launch_persistent<bf16>(ma, mb, p, sms, stream);
+        if (pbn == 128) return f32 ? launch_persistent<128, float>(ma, mb, p, sms, stream) : launch_persistent<128, bf16>(ma, mb, p, sms, stream);
+        return f32 ? launch_persistent<96, float>(ma, mb, p, sms, stream) : launch_persistent<96, bf16>(ma, mb, p, sms, stream);
     }
     int rc = get_map(swap ? w : x, p.rows_a, K, BM, &ma);
     if (rc) return rc;

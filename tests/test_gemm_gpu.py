@@ -22,6 +22,8 @@ SIZES = [
     (2, 320, 96),          # swap, K = 1.5 k-blocks
     (1100, 3000, 520),     # persistent (256 x 128 tiles, two accumulators): ragged M and N, K tail, several tiles per CTA
     (4000, 4100, 72),      # persistent, many tiles of two k-blocks: the accumulators alternate quickly
+    (1800, 1500, 136),     # persistent with 96-column tiles (fills the SMs better than 128), ragged M and N
+    (2048, 1536, 1536),    # persistent with 96-column tiles, the model's o product at prefill
 ]
 
 
