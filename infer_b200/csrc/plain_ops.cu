@@ -562,7 +562,8 @@ IB_EXPORT int ib_rmsnorm(const float* x, const float* w, float eps, int64_t n_ro
     if (n_rows <= 0) return IB_OK;
     if (hidden <= 0) return ib::fail(IB_ERR_ARG, "ib_rmsnorm: hidden must be positive");
     const int threads = hidden >= 1024 ? 256 : 128;
-    if (n_rows >= 64 && hidden % 4 == 0 && !((uintptr_t(x) | uintptr_t(w) | uintptr_t(out)) & 15)) {
+    // (the choice does not look at the number of rows: a row's result must not depend on what else is in the step)
+    if (hidden % 4 == 0 && !((uintptr_t(x) | uintptr_t(w) | uintptr_t(out)) & 15)) {
         const unsigned blocks = unsigned((n_rows + 7) / 8);
         if (out_dtype == IB_F32)
             IB_LAUNCH(rmsnorm_warp_kernel<float>, blocks, 256, 0, x, w, eps, hidden, rows, (float*)out, n_rows);
