@@ -34,10 +34,11 @@ MODULES: Dict[str, str] = {
     "chain": "linear_chain.cu",
     "gemm": "gemm_tcgen05.cu",
     "attn": "attention_fast.cu",
+    "attn_tc": "attention_tc.cu",
 }
-HEADERS = ["common.cuh", "gemm_static.h"]
+HEADERS = ["common.cuh", "gemm_static.h", "tma_map.cuh"]
 # modules that are compiled per model size: the variant that build_all() makes (others are built at first use)
-DEFAULT_DEFINES = {"attn": {"IB_HEAD_DIM": 128}}
+DEFAULT_DEFINES = {"attn": {"IB_HEAD_DIM": 128}, "attn_tc": {"IB_HEAD_DIM": 128}}
 
 
 class BuildError(RuntimeError):

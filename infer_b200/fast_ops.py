@@ -219,6 +219,12 @@ def _decode_splits(st, n_decode: int, n_kv: int, visible: int) -> int:
     return n
 
 
+# The prefill kernel on tcgen05 / tensor memory (attention_tc.cu) serves head sizes 64 and 128; INFER_B200_ATTN_TC=0
+# leaves prefill to the mma.sync kernel.
+ATTENTION_TC = os.environ.get("INFER_B200_ATTN_TC", "1") == "1"
+ATTENTION_TC_HEAD_DIMS = (64, 128)
+
+
 def attention_fast(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
                    seg_start: torch.Tensor, seg_pos0: torch.Tensor, n_heads: int, n_kv: int, head_dim: int,
                    window: Optional[int], scale: float, has_decode: bool, max_q_len: int, max_ctx_len: int,
@@ -244,11 +250,22 @@ def attention_fast(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor
         visible = min(max_ctx_len, window) if window else max_ctx_len
         n_splits = _decode_splits(st, n_decode if n_decode is not None else S, n_kv, visible) if has_decode else 1
     out = torch.empty_like(q)
+    # Segments of two or more tokens go to the tcgen05 kernel where it takes the head size; one-token segments, and
+    # everything else, to the mma.sync kernels (a call with max_q_len = 1 launches no prefill kernel).
+    tc = ATTENTION_TC and max_q_len > 1 and head_dim in ATTENTION_TC_HEAD_DIMS and page_size == 16
+    if tc:
+        g = _fn("attn_tc", "ib_attention_prefill_tc", [c_void_p] * 5 + [c_int] + [c_void_p] * 2 + [c_int, c_int64] + [c_int] * 5 +
+                [c_float, c_int64, c_int] + [c_void_p] * 2, {"IB_HEAD_DIM": head_dim})
+        _call(g, q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), block_table.data_ptr(),
+              block_table.shape[1], seg_start.data_ptr(), seg_pos0.data_ptr(), S, T, n_heads, n_kv, head_dim, page_size,
+              int(window or 0), float(scale), n_pages, int(max_q_len), st.status.data_ptr(), _stream())
+        if not has_decode:
+            return out
     f = _fn("attn", "ib_attention_fast", [c_void_p] * 5 + [c_int] + [c_void_p] * 2 + [c_int] * 6 + [c_float, c_int64] +
             [c_int] * 3 + [c_void_p] * 2, {"IB_HEAD_DIM": head_dim})
     _call(f, q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), block_table.data_ptr(),
           block_table.shape[1], seg_start.data_ptr(), seg_pos0.data_ptr(), S, n_heads, n_kv, head_dim, page_size,
-          int(window or 0), float(scale), n_pages, int(has_decode), int(max_q_len), int(n_splits),
+          int(window or 0), float(scale), n_pages, int(has_decode), 1 if tc else int(max_q_len), int(n_splits),
           st.status.data_ptr(), _stream())
     return out
 

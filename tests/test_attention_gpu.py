@@ -74,6 +74,18 @@ def test_prefill_with_window(heads, kv, hd):
     _run(heads, kv, hd, 200, [(10, 260)])
 
 
+@pytest.mark.parametrize("tc", [True, False], ids=["tcgen05", "mma.sync"])
+@pytest.mark.parametrize("heads,kv,hd", [(12, 2, 128), (14, 2, 64)])
+def test_prefill_long(heads, kv, hd, tc, monkeypatch):
+    """Several query tiles and many key tiles per segment, through the tensor-memory kernel (128 queries x 128 keys per
+    tile, keys two tiles ahead) and through the mma.sync kernel: contexts that end inside a tile, a window that drops
+    whole tiles, a portion that starts in the middle of a page."""
+    from infer_b200 import fast_ops
+    monkeypatch.setattr(fast_ops, "ATTENTION_TC", tc)
+    _run(heads, kv, hd, None, [(0, 700), (1000, 300), (130, 129), (5, 2)])
+    _run(heads, kv, hd, 300, [(0, 650), (900, 140)])
+
+
 @pytest.mark.parametrize("heads,kv,hd", [(12, 2, 128), (4, 4, 16)])
 def test_mixed_step(heads, kv, hd):
     _run(heads, kv, hd, None, [(100, 1), (0, 40), (517, 1), (30, 5), (0, 1)], 2)
