@@ -360,29 +360,36 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             tmem_ld_wait();
             IB_T(j, 2);
             const bool full_tile = key0 + BN - 1 <= q_first && key0 >= (p.window > 0 ? max(0, q_first + BM - 1 - p.window + 1) : 0);
-            // (written without short-circuit operators: a branch per element costs more than the arithmetic)
+            // Raw scores: the scale goes into the exponent's multiply-add below. Most tiles lie wholly below the diagonal
+            // and inside the window and need no mask. (Masks are written without short-circuit operators: a branch per
+            // element costs more than the arithmetic.)
             float mxs[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-            const float scale_log2 = p.scale_log2;
-            const int hi = full_tile ? 0x7fffffff : row_pos - key0, lo = full_tile ? -0x7fffffff : row_lo - key0;   // visible: lo <= c <= hi
+            const float scale_log2 = p.scale_log2;       // > 0
+            if (full_tile) {
 #pragma unroll
-            for (int c = 0; c < BN; c++) {
-                const bool vis = (c <= hi) & (c >= lo);
-                s[c] = vis ? s[c] * scale_log2 : -INFINITY;
-                mxs[c & 3] = fmaxf(mxs[c & 3], s[c]);
+                for (int c = 0; c < BN; c++) mxs[c & 3] = fmaxf(mxs[c & 3], s[c]);
+            } else {
+                const int hi = row_pos - key0, lo = row_lo - key0;       // visible: lo <= c <= hi
+#pragma unroll
+                for (int c = 0; c < BN; c++) {
+                    const bool vis = (c <= hi) & (c >= lo);
+                    s[c] = vis ? s[c] : -INFINITY;
+                    mxs[c & 3] = fmaxf(mxs[c & 3], s[c]);
+                }
             }
-            const float mx = fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3]));
+            const float mx = fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3])) * scale_log2;
             // O and the probabilities refer to m_ref, which follows the running maximum in steps
             const bool raise = mx > m_ref + RESCALE_STEP || (m_ref == -INFINITY && mx > -INFINITY);
             const float alpha = raise ? fast_exp2(m_ref - mx) : 1.0f;   // m_ref = -inf gives 0: nothing was summed yet
             if (raise) { m_ref = mx; l *= alpha; }
             IB_T(j, 3);
             // with no visible key so far every score is -inf: subtracting 0 instead of -inf keeps exp2 at 0, not NaN
-            const float m_sub = m_ref == -INFINITY ? 0.0f : m_ref;
+            const float m_neg = m_ref == -INFINITY ? 0.0f : -m_ref;
             float sums[2] = {0.0f, 0.0f};
             uint32_t pk[BN / 2];                         // the row of P, packed
 #pragma unroll
             for (int c = 0; c < BN; c += 2) {
-                const float a = fast_exp2(s[c] - m_sub), b = fast_exp2(s[c + 1] - m_sub);
+                const float a = fast_exp2(fmaf(s[c], scale_log2, m_neg)), b = fast_exp2(fmaf(s[c + 1], scale_log2, m_neg));
                 __nv_bfloat162 two = __floats2bfloat162_rn(a, b);
                 pk[c / 2] = *reinterpret_cast<uint32_t*>(&two);
                 sums[(c >> 1) & 1] += a + b;

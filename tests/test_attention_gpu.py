@@ -27,12 +27,11 @@ def _run(heads, kv, hd, window, segs, n_splits=None, seed=0):
     ref = torch.zeros(T, heads, hd, dtype=torch.float64)
     r = 0
     for s, (c, n) in enumerate(segs):
-        for i in range(n):
-            p = c + i
-            qq = torch.zeros(p + 1, heads, hd, dtype=torch.float64)
-            qq[p] = q[r].double()
-            ref[r] = pm.attention(qq, ks[s][:p + 1].double(), vs[s][:p + 1].double(), window, scale)[p]
-            r += 1
+        # the step's queries sit at rows c .. c + n - 1 of a sequence of c + n positions; causal, so one call serves all
+        qq = torch.zeros(c + n, heads, hd, dtype=torch.float64)
+        qq[c:] = q[r:r + n].double()
+        ref[r:r + n] = pm.attention(qq, ks[s][:c + n].double(), vs[s][:c + n].double(), window, scale)[c:]
+        r += n
     st = fast_ops.device_state(DEV)
     st.status.zero_()
     out = fast_ops.attention_fast(
