@@ -53,7 +53,7 @@ constexpr int STATUS_TIMEOUT = 106, STATUS_BAD_PAGE = 3;
 constexpr int TAB_MAX = 2048;               // page ids kept in shared memory: 32,768 positions
 
 constexpr int Q_BYTES = DB * BM * 128, K_BYTES = DB * BN * 128, V_BYTES = DB * BN * 128, P_BYTES = PB * BM * 128;
-constexpr int SMEM_BYTES = Q_BYTES + 2 * K_BYTES + V_BYTES + P_BYTES + 1024 /*alignment*/ + 128 /*barriers*/;
+constexpr int SMEM_BYTES = Q_BYTES + 2 * K_BYTES + 2 * V_BYTES + P_BYTES + 1024 /*alignment*/ + 128 /*barriers*/;
 constexpr int TMEM_COLS = (2 * BN + HD) > 256 ? 512 : ((2 * BN + HD) > 128 ? 256 : 128);
 constexpr int S_COL = 0, O_COL = 2 * BN;    // two S tiles of BN columns each, then O's HD columns
 
@@ -175,13 +175,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
-    const uint32_t q_s = base, k_s = q_s + Q_BYTES, v_s = k_s + 2 * K_BYTES, p_s = v_s + V_BYTES, bars = p_s + P_BYTES;
+    const uint32_t q_s = base, k_s = q_s + Q_BYTES, v_s = k_s + 2 * K_BYTES, p_s = v_s + 2 * V_BYTES, bars = p_s + P_BYTES;
     uint8_t* v_ptr = base_ptr + Q_BYTES + 2 * K_BYTES;
-    uint8_t* p_ptr = v_ptr + V_BYTES;
-    volatile uint32_t* slots = reinterpret_cast<volatile uint32_t*>(p_ptr + P_BYTES + 96);   // [0] TMEM base, [1] abort
-    // k_full, k_empty and s_full come in pairs (two K tiles in shared memory, two S tiles in tensor memory)
+    uint8_t* p_ptr = v_ptr + 2 * V_BYTES;
+    volatile uint32_t* slots = reinterpret_cast<volatile uint32_t*>(p_ptr + P_BYTES + 112);  // [0] TMEM base, [1] abort
+    // k_full, k_empty, v_full, v_empty and s_full come in pairs (two K and two V tiles in shared memory, two S tiles in
+    // tensor memory): tile j uses member j & 1, for the (j >> 1)-th time
     const uint32_t q_full = bars, k_full = bars + 8, k_empty = bars + 24, s_full = bars + 40, v_full = bars + 56,
-                   v_empty = bars + 64, p_full = bars + 72, o_full = bars + 80;
+                   v_empty = bars + 72, p_full = bars + 88, o_full = bars + 96;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     // The last query tiles have the most keys: they start first, for every head.
@@ -220,8 +221,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
-        for (int b = 0; b < 2; b++) { mbar_init(k_full + 8 * b, 1); mbar_init(k_empty + 8 * b, 1); mbar_init(s_full + 8 * b, 1); }
-        mbar_init(v_full, 1); mbar_init(v_empty, 1); mbar_init(p_full, 4); mbar_init(o_full, 1);
+        for (int b = 0; b < 2; b++) {
+            mbar_init(k_full + 8 * b, 1); mbar_init(k_empty + 8 * b, 1); mbar_init(s_full + 8 * b, 1);
+            mbar_init(v_full + 8 * b, 1); mbar_init(v_empty + 8 * b, 1);
+        }
+        mbar_init(p_full, 4); mbar_init(o_full, 1);
         slots[1] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         prefetch_tensormap(&tm_q); prefetch_tensormap(&tm_k); prefetch_tensormap(&tm_v);
@@ -242,13 +246,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             mbar_expect_tx(q_full, Q_BYTES);
             for (int db = 0; db < DB; db++) tma_load_2d(q_s + db * (BM * 128), &tm_q, q_full, h * HD + db * 64, t0 + qt * BM);
         }
-        int pend_k[2] = {-1, -1}, pend_v = -1;           // tiles whose copies were issued into each buffer last
+        int pend_k[2] = {-1, -1}, pend_v[2] = {-1, -1};  // tiles whose copies were issued into each buffer last
         // Loads the K (which = 0) or V (which = 1) pages of tile j. Pages that hold nothing this step may read are
         // skipped (their rows are masked, and zeroed for V).
         auto load_tile = [&](int j, int which) {
             const int key0 = (kt0 + j) * BN;
-            const uint32_t full = which ? v_full : k_full + 8 * (j & 1);
-            const uint32_t dst0 = which ? v_s : k_s + (j & 1) * K_BYTES;
+            const uint32_t full = (which ? v_full : k_full) + 8 * (j & 1);
+            const uint32_t dst0 = which ? v_s + (j & 1) * V_BYTES : k_s + (j & 1) * K_BYTES;
             int page = -1;
             if (lane < PAGES_PER_TILE) {
                 const int key = key0 + lane * PAGE;
@@ -266,7 +270,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                 for (int db = 0; db < DB; db++)
                     tma_load_2d(dst0 + db * (BN * 128) + lane * (PAGE * 128), which ? &tm_v : &tm_k, full, db * 64, row);
             }
-            if (valid > 0) { if (which) pend_v = j; else pend_k[j & 1] = j; }
+            if (valid > 0) { if (which) pend_v[j & 1] = j; else pend_k[j & 1] = j; }
         };
         auto wait_all = [&](uint32_t bar, uint32_t parity) -> bool {      // lane 0 waits, every lane learns the outcome
             int got = 1;
@@ -274,8 +278,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             return __shfl_sync(0xffffffffu, got, 0) != 0;
         };
         load_tile(0, 0);
-        if (n_tiles > 1) load_tile(1, 0);
         load_tile(0, 1);
+        if (n_tiles > 1) { load_tile(1, 0); load_tile(1, 1); }
         bool failed = false;
         for (int j = 0; j < n_tiles && !failed; j++) {
             if (__shfl_sync(0xffffffffu, int(slots[1]), 0)) { failed = true; break; }
@@ -283,18 +287,19 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                 if (!wait_all(k_empty + 8 * (j & 1), (j >> 1) & 1)) { failed = true; break; }
                 load_tile(j + 2, 0);
             }
-            if (j + 1 < n_tiles) {                       // P(j) V(j) is complete: the V buffer takes tile j + 1
-                if (!wait_all(v_empty, j & 1)) { failed = true; break; }
-                load_tile(j + 1, 1);
+            if (j + 2 < n_tiles) {                       // P(j) V(j) is complete: its V buffer takes tile j + 2
+                if (!wait_all(v_empty + 8 * (j & 1), (j >> 1) & 1)) { failed = true; break; }
+                load_tile(j + 2, 1);
             }
         }
         if (failed && lane == 0) {
             if (!slots[1]) { atomicExch(p.status, STATUS_TIMEOUT); slots[1] = 1; }
             // Drain: wait (bounded) for the copies that may still be on their way, so that none lands after the CTA is gone.
             mbar_wait(q_full, 0);
-            for (int b = 0; b < 2; b++)
+            for (int b = 0; b < 2; b++) {
                 if (pend_k[b] >= 0) mbar_wait(k_full + 8 * b, (pend_k[b] >> 1) & 1);
-            if (pend_v >= 0) mbar_wait(v_full, pend_v & 1);
+                if (pend_v[b] >= 0) mbar_wait(v_full + 8 * b, (pend_v[b] >> 1) & 1);
+            }
         }
     } else if (warp == 1) {
         // ---------------------------------------------------------------- MMA issuer
@@ -320,17 +325,17 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             };
             bool ok = mbar_wait(q_full, 0) && issue_qk(0) && (n_tiles < 2 || issue_qk(1));
             for (int j = 0; j < n_tiles && ok && !slots[1]; j++) {
-                ok = mbar_wait(p_full, j & 1) && mbar_wait(v_full, j & 1);
+                ok = mbar_wait(p_full, j & 1) && mbar_wait(v_full + 8 * (j & 1), (j >> 1) & 1);
                 if (!ok) break;
                 tc_fence_after();
 #pragma unroll
                 for (int k = 0; k < BN / 16; k++) {      // 16 keys per step: 32 bytes along P's rows, 2 groups of 8 rows of V
                     const uint64_t pd = make_desc(p_s + (k / 4) * (BM * 128), 16, 1024) + uint64_t(2 * (k % 4));
-                    const uint64_t vd = make_desc(v_s + k * (16 * 128), BN * 128, 1024);
+                    const uint64_t vd = make_desc(v_s + (j & 1) * V_BYTES + k * (16 * 128), BN * 128, 1024);
                     umma_f16(o_tmem, pd, vd, idesc_o, (j > 0 || k > 0) ? 1u : 0u);
                 }
                 umma_commit(o_full);
-                umma_commit(v_empty);
+                umma_commit(v_empty + 8 * (j & 1));
                 IB_T(j, 7);
                 // the softmax threads have read S(j) (they wrote P(j) from it): its buffer takes S(j + 2)
                 if (j + 2 < n_tiles) ok = issue_qk(j + 2);
@@ -424,14 +429,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             // Rows of V that hold nothing this step may read (positions after the segment's last token, pages the table
             // does not hold) become zeros, so that 0 x garbage cannot make a NaN.
             if (key0 + BN - 1 > last_written || key0 < lo_key) {
-                ok = mbar_wait(v_full, j & 1);
+                ok = mbar_wait(v_full + 8 * (j & 1), (j >> 1) & 1);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 for (int u = r; u < BN * DB; u += BM) {
                     const int key_row = u % BN, db = u / BN;
                     const int key = key0 + key_row;
                     if (key > last_written || page_of(key) < 0) {
-                        uint4* line = reinterpret_cast<uint4*>(v_ptr + db * (BN * 128) + key_row * 128);
+                        uint4* line = reinterpret_cast<uint4*>(v_ptr + (j & 1) * V_BYTES + db * (BN * 128) + key_row * 128);
 #pragma unroll
                         for (int e = 0; e < 8; e++) line[e] = make_uint4(0u, 0u, 0u, 0u);
                     }
