@@ -531,18 +531,22 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
-template <int PBN, typename TOut>
+template <int PBN, bool WIDE, typename TOut>
 __global__ void __launch_bounds__(NUM_THREADS)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
     constexpr int S = PSTAGES;
+    // WIDE: 128 tokens x 256 features per tile, one M=128 x N=256 MMA per k-step (the A operand is read once for
+    // twice the columns: less shared-memory traffic per flop); else 256 tokens x PBN features, two M=128 MMAs.
+    constexpr int TM = WIDE ? 128 : PBM, TN = WIDE ? 256 : PBN;
+    constexpr int A_BYTES = TM * BK * 2, B_BYTES = TN * BK * 2;
     const uint32_t bars = base + S * P_STAGE_BYTES;               // full[S], empty[S], acc_full[2], acc_empty[2]
     volatile uint32_t* slots = reinterpret_cast<volatile uint32_t*>(base_ptr + S * P_STAGE_BYTES + (2 * S + 4) * 8);
     // slots[0] = TMEM base address, slots[1] = abort flag
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tiles_m = int((p.rows_a + PBM - 1) / PBM), tiles_n = int((p.rows_b + PBN - 1) / PBN);
+    const int tiles_m = int((p.rows_a + TM - 1) / TM), tiles_n = int((p.rows_b + TN - 1) / TN);
     const int n_tiles = tiles_m * tiles_n;
     const int n_kb = p.kb_total;
     auto full_bar = [&](int s) { return bars + 8u * s; };
@@ -580,10 +584,10 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
                         atomicExch(p.status, STATUS_TIMEOUT_PRODUCER); slots[1] = 1; break;
                     }
                     if (slots[1]) break;
-                    const uint32_t a_dst = base + s * P_STAGE_BYTES, b_dst = a_dst + P_A_BYTES;
-                    mbar_expect_tx(full_bar(s), P_A_BYTES + PBN * BK * 2);
-                    tma_load_2d(a_dst, &tm_a, full_bar(s), kb * BK, tm * PBM);
-                    tma_load_2d(b_dst, &tm_b, full_bar(s), kb * BK, tn * PBN);
+                    const uint32_t a_dst = base + s * P_STAGE_BYTES, b_dst = a_dst + A_BYTES;
+                    mbar_expect_tx(full_bar(s), A_BYTES + B_BYTES);
+                    tma_load_2d(a_dst, &tm_a, full_bar(s), kb * BK, tm * TM);
+                    tma_load_2d(b_dst, &tm_b, full_bar(s), kb * BK, tn * TN);
                     issued = it + 1;
                 }
             }
@@ -595,7 +599,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
     } else if (warp == 1) {
         // ---------------------------------------------------------------- MMA issuer
         if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc(PBN);
+            constexpr uint32_t idesc = make_idesc(TN);
             int it = 0, lt = 0;
             for (int tile = blockIdx.x; tile < n_tiles && !slots[1]; tile += gridDim.x, lt++) {
                 const int b = lt & 1;
@@ -611,12 +615,16 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
                     }
                     tc_fence_after();
                     const uint32_t a_addr = base + s * P_STAGE_BYTES;
-                    const uint64_t a0 = make_desc(a_addr), a1 = make_desc(a_addr + P_A_BYTES / 2), bd = make_desc(a_addr + P_A_BYTES);
+                    const uint64_t a0 = make_desc(a_addr), a1 = make_desc(a_addr + 128 * BK * 2), bd = make_desc(a_addr + A_BYTES);
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; k++) {
                         const uint32_t acc = (kb > 0 || k > 0) ? 1u : 0u;
-                        umma_f16(d0, a0 + uint64_t(2 * k), bd + uint64_t(2 * k), idesc, acc);
-                        umma_f16(d1, a1 + uint64_t(2 * k), bd + uint64_t(2 * k), idesc, acc);
+                        if constexpr (WIDE) {
+                            umma_f16(d0, a0 + uint64_t(2 * k), bd + uint64_t(2 * k), idesc, acc);
+                        } else {
+                            umma_f16(d0, a0 + uint64_t(2 * k), bd + uint64_t(2 * k), idesc, acc);
+                            umma_f16(d1, a1 + uint64_t(2 * k), bd + uint64_t(2 * k), idesc, acc);
+                        }
                     }
                     umma_commit(empty_bar(s));
                 }
@@ -638,6 +646,19 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
+            if constexpr (WIDE) {
+                const int64_t a_row = int64_t(tm) * TM + quad * 32 + lane;
+#pragma unroll 1
+                for (int c = 0; c < TN; c += 16) {
+                    uint32_t raw[16];
+                    tmem_ld16(tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(b * 256 + c), raw);
+                    tmem_ld_wait();
+                    float v[16];
+#pragma unroll
+                    for (int j = 0; j < 16; j++) v[j] = __uint_as_float(raw[j]);
+                    epilogue_store<TOut>(p, v, a_row, int64_t(tn) * TN + c);
+                }
+            } else
 #pragma unroll 1
             for (int m = 0; m < 2; m++) {
                 const int64_t a_row = int64_t(tm) * PBM + m * 128 + quad * 32 + lane;
@@ -684,17 +705,17 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, di
                       p.cluster_split ? unsigned(p.splits) : 1u, ma, mb, p);
 }
 
-template <int PBN, typename TOut>
+template <int PBN, bool WIDE, typename TOut>
 int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, int sm_count, cudaStream_t stream) {
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_persistent_kernel<PBN, TOut>, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_persistent_kernel<PBN, WIDE, TOut>, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES);
         if (e != cudaSuccess) return ib::fail(IB_ERR_CUDA, "gemm_tc: cannot set shared memory size: %s", cudaGetErrorString(e));
         configured = true;
     }
-    const int64_t tiles = ((p.rows_a + PBM - 1) / PBM) * ((p.rows_b + PBN - 1) / PBN);
+    const int64_t tiles = WIDE ? ((p.rows_a + 127) / 128) * ((p.rows_b + 255) / 256) : ((p.rows_a + PBM - 1) / PBM) * ((p.rows_b + PBN - 1) / PBN);
     const unsigned ctas = unsigned(tiles < sm_count ? tiles : sm_count);
-    return ib::launch("gemm_tc", gemm_tc_persistent_kernel<PBN, TOut>, dim3(ctas), dim3(NUM_THREADS), size_t(P_SMEM_BYTES), stream, 1u, ma, mb, p);
+    return ib::launch("gemm_tc", gemm_tc_persistent_kernel<PBN, WIDE, TOut>, dim3(ctas), dim3(NUM_THREADS), size_t(P_SMEM_BYTES), stream, 1u, ma, mb, p);
 }
 
 // Stages of the ring: the default leaves room for a second CTA on the SM (prefill: one tile's epilogue overlaps the
@@ -745,11 +766,13 @@ IB_EXPORT int ib_gemm_tc_plan(int64_t M, int64_t N, int64_t K, int sm_count, int
     static const bool persistent_on = [] { const char* e = getenv("INFER_B200_GEMM_PERSISTENT"); return !(e && e[0] == '0'); }();
     if (!*swap && s == 1 && persistent_on && sm_count > 0) {
         // share of the SMs at work over the rounds a tile width needs; the narrower tile moves a tenth more operand
-        // bytes per flop. bn = 256 stands for the 256 x 128 tile, 192 for 256 x 96.
+        // bytes per flop. bn = 512 stands for the 128 x 256 tile, 256 for 256 x 128, 192 for 256 x 96.
         const int64_t tm = (M + PBM - 1) / PBM;
         const int64_t t128 = tm * ((N + 127) / 128), t96 = tm * ((N + 95) / 96);
         auto fill = [&](int64_t t) { return double(t) / double(((t + sm_count - 1) / sm_count) * sm_count); };
-        if (t128 * 2 >= sm_count) *bn = fill(t96) * 0.9 > fill(t128) ? 192 : 256;
+        // one M=128 x N=256 MMA per k-step instead of two of N=128 (measured: gate/up 96 -> 93 us, q/k/v 15.3 -> 13.5 us)
+        static const bool wide_on = [] { const char* e = getenv("INFER_B200_GEMM_WIDE"); return !(e && e[0] == '0'); }();
+        if (t128 * 2 >= sm_count) *bn = fill(t96) * 0.9 > fill(t128) ? 192 : (wide_on ? 512 : 256);
     }
     *workspace_floats = (s > 1 && !*swap) ? int64_t(s) * tiles * BM * (*bn) : 0;
     *n_counters = (s > 1 && !*swap) ? tiles : 0;
@@ -767,8 +790,8 @@ IB_EXPORT int ib_gemm_tc(const void* x, const void* w, const float* bias, const 
     if (M <= 0 || N <= 0) return IB_OK;
     if (K <= 0 || K % 8) return ib::fail(IB_ERR_ARG, "gemm_tc: K = %lld must be a positive multiple of 8", (long long)K);
     if ((uintptr_t(x) & 15) || (uintptr_t(w) & 15)) return ib::fail(IB_ERR_ARG, "gemm_tc: operand bases must be 16-byte aligned");
-    if (bn != 16 && bn != 32 && bn != 64 && bn != 128 && bn != 192 && bn != 256)
-        return ib::fail(IB_ERR_ARG, "gemm_tc: bn must be 16, 32, 64, 128, or 192 or 256 (the persistent kernel's 96 and 128 columns)");
+    if (bn != 16 && bn != 32 && bn != 64 && bn != 128 && bn != 192 && bn != 256 && bn != 512)
+        return ib::fail(IB_ERR_ARG, "gemm_tc: bn must be 16, 32, 64, 128, or 192, 256 or 512 (the persistent kernel: 96 columns, 128 columns, one 256-wide MMA)");
     if (bn >= 192 && (swap || splits > 1)) return ib::fail(IB_ERR_ARG, "gemm_tc: the persistent kernel takes the plain mapping without K slices");
     if (!status) return ib::fail(IB_ERR_ARG, "gemm_tc: a status word is required");
     if (epi != 0 && epi != 2) return ib::fail(IB_ERR_ARG, "gemm_tc: unknown epilogue %d", epi);
@@ -797,10 +820,10 @@ IB_EXPORT int ib_gemm_tc(const void* x, const void* w, const float* bias, const 
     if (!f32 && out_dtype != IB_BF16) return ib::fail(IB_ERR_ARG, "gemm_tc: unknown output dtype %d", out_dtype);
     CUtensorMap ma, mb;
     if (bn >= 192) {
-        const int pbn = bn == 256 ? 128 : 96;
-        int rc = get_map(x, p.rows_a, K, PBM, &ma);
+        const int pbn = bn == 192 ? 96 : 128;
+        int rc = get_map(x, p.rows_a, K, bn == 512 ? 128 : PBM, &ma);
         if (rc) return rc;
-        rc = get_map(w, p.rows_b, K, pbn, &mb);
+        rc = get_map(w, p.rows_b, K, bn == 512 ? 256 : pbn, &mb);
         if (rc) return rc;
         static int sms = 0;
         if (!sms) {
@@ -809,8 +832,11 @@ IB_EXPORT int ib_gemm_tc(const void* x, const void* w, const float* bias, const 
                 return ib::fail(IB_ERR_CUDA, "gemm_tc: cannot read the number of SMs");
         }
         p.splits = 1; p.cluster_split = 0; p.stages = PSTAGES;
-        if (pbn == 128) return f32 ? launch_persistent<128, float>(ma, mb, p, sms, stream) : launch_persistent<128, bf16>(ma, mb, p, sms, stream);
-        return f32 ? launch_persistent<96, float>(ma, mb, p, sms, stream) : launch_persistent<96, bf16>(ma, mb, p, sms, stream);
+        if (bn == 512) {
+            return f32 ? launch_persistent<128, true, float>(ma, mb, p, sms, stream) : launch_persistent<128, true, bf16>(ma, mb, p, sms, stream);
+        }
+        if (pbn == 128) return f32 ? launch_persistent<128, false, float>(ma, mb, p, sms, stream) : launch_persistent<128, false, bf16>(ma, mb, p, sms, stream);
+        return f32 ? launch_persistent<96, false, float>(ma, mb, p, sms, stream) : launch_persistent<96, false, bf16>(ma, mb, p, sms, stream);
     }
     int rc = get_map(swap ? w : x, p.rows_a, K, BM, &ma);
     if (rc) return rc;
