@@ -220,10 +220,14 @@ attn_decode_kernel(const AttnParams p) {
     const uint32_t my_smem = smem_u32(my_ptr);
     const int my_pages = pg_end > pg_begin + warp ? (pg_end - pg_begin - warp + DEC_WARPS - 1) / DEC_WARPS : 0;
 
+    // The ids of this warp's first 32 pages in one load (lane i holds the i-th): a read of the table per page would put
+    // a round trip to L2 in front of every copy.
+    int lane_page = -1;
+    if (lane < my_pages) lane_page = table[pg_begin + warp + lane * DEC_WARPS];
     auto issue = [&](int i) {
         if (i < my_pages) {
             const int pg = pg_begin + warp + i * DEC_WARPS;
-            int page = table[pg];
+            int page = i < 32 ? __shfl_sync(0xffffffffu, lane_page, i) : table[pg];
             if (page < 0 || page >= p.n_pages) { atomicExch(p.status, 3); page = -1; }
             const uint32_t dst = my_smem + (i % DEC_STAGES) * DEC_STAGE_BYTES;
             const int64_t base = page < 0 ? 0 : ((int64_t(page) * p.n_kv + kvh) * PAGE) * HD;
