@@ -521,7 +521,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 // warps drain one tile while the MMA warp already works on the next; the operand ring runs on across tiles.
 // The tile is 256 x 128, or 256 x 96 where that fills the SMs better (a matrix of 1536 features has 12 or 16 column
 // tiles; with 8 row tiles that is 96 or 128 CTAs' worth of work for 148 SMs).
-constexpr int PBM = 256, PSTAGES = 4;
+#ifndef IB_GEMM_PSTAGES
+#define IB_GEMM_PSTAGES 4
+#endif
+constexpr int PBM = 256, PSTAGES = IB_GEMM_PSTAGES;
 constexpr int P_A_BYTES = PBM * BK * 2;
 constexpr int P_STAGE_BYTES = P_A_BYTES + 128 * BK * 2;           // sized for the wider tile
 constexpr int P_SMEM_BYTES = PSTAGES * P_STAGE_BYTES + 1024 + 256;
