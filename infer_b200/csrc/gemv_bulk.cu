@@ -154,22 +154,28 @@ bulk_gemv_kernel(const GemvParams p) {
 
     if (warp == WARPS) {
         // ---------------------------------------------------------------- producer: lane r copies row r of every stage
+        // (ring slot, its use count, stage within the tile and tile are carried along: 64-bit divisions by run-time
+        // values would cost more per stage than the copies)
+        int s = 0, st = 0;
+        uint32_t round = 0;
+        int64_t tile = group;
         for (int64_t i = 0; i < n_iter; i++) {
-            const int s = int(i % NS);
             if (i >= NS) {
                 int ok = 1;
-                if (lane == 0) ok = mbar_wait(empty_bar(s), uint32_t((i / NS) - 1) & 1u) ? 1 : 0;
+                if (lane == 0) ok = mbar_wait(empty_bar(s), (round - 1) & 1u) ? 1 : 0;
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) { if (lane == 0) { atomicExch(p.status, STATUS_TIMEOUT); failed = 1; } break; }
             }
-            const int64_t n0 = (group + (i / spt) * p.groups) * ROWS;
-            const int64_t k0 = (s_begin + i % spt) * KC;
+            const int64_t n0 = tile * ROWS;
+            const int64_t k0 = (s_begin + st) * KC;
             const int live_rows = int(min(int64_t(ROWS), N - n0));
             const uint32_t bytes = uint32_t(min(int64_t(KC), K - k0) * 2);
             if (lane == 0) mbar_expect_tx(full_bar(s), bytes * uint32_t(live_rows));
             __syncwarp();
             if (lane < live_rows) bulk_load(stage0 + s * STAGE_BYTES + lane * PITCH, p.w + (n0 + lane) * K + k0, bytes, full_bar(s));
             if (i == NS - 1 || i == n_iter - 1) ib::pdl_launch_dependents();     // the first ring is on its way
+            if (++s == NS) { s = 0; round++; }
+            if (++st == spt) { st = 0; tile += p.groups; }
         }
         if (n_iter == 0) ib::pdl_launch_dependents();
         ib::l2_prefetch_share(p.prefetch, p.prefetch_bytes, blockIdx.x, gridDim.x);
@@ -287,9 +293,11 @@ bulk_gemv_kernel(const GemvParams p) {
         }
     }
 
+    int s = 0, st = 0;
+    uint32_t round = 0;
+    int64_t tile = group;
     for (int64_t i = 0; i < n_iter; i++) {
-        const int s = int(i % NS);
-        const int64_t k0 = (s_begin + i % spt) * KC;
+        const int64_t k0 = (s_begin + st) * KC;
         if (!hoist) {
             // activations of this warp's chunks: independent of the weights, so they are loaded before the wait
 #pragma unroll
@@ -301,16 +309,16 @@ bulk_gemv_kernel(const GemvParams p) {
                     b[u][nt] = (k_ok[u] && x_ok[nt]) ? __ldg(reinterpret_cast<const uint4*>(xr[nt] + k)) : zero;
             }
         }
-        if (!mbar_wait(full_bar(s), uint32_t(i / NS) & 1u)) {
+        if (!mbar_wait(full_bar(s), round & 1u)) {
             if (lane == 0) { atomicExch(p.status, STATUS_TIMEOUT); failed = 1; }
             break;
         }
-        const uint8_t* st = stages + s * STAGE_BYTES;
+        const uint8_t* stg = stages + s * STAGE_BYTES;
 #pragma unroll
         for (int u = 0; u < CPW; u++) {
             const int cb = ((warp + u * WARPS) * 32 + t * 8) * 2;
-            const uint4 a0 = k_ok[u] ? *reinterpret_cast<const uint4*>(st + g * PITCH + cb) : zero;
-            const uint4 a1 = k_ok[u] ? *reinterpret_cast<const uint4*>(st + (g + 8) * PITCH + cb) : zero;
+            const uint4 a0 = k_ok[u] ? *reinterpret_cast<const uint4*>(stg + g * PITCH + cb) : zero;
+            const uint4 a1 = k_ok[u] ? *reinterpret_cast<const uint4*>(stg + (g + 8) * PITCH + cb) : zero;
 #pragma unroll
             for (int nt = 0; nt < NT; nt++) {
                 mma_bf16(acc[nt], a0.x, a1.x, a0.y, a1.y, b[u][nt].x, b[u][nt].y);
@@ -319,11 +327,14 @@ bulk_gemv_kernel(const GemvParams p) {
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(empty_bar(s));
-        if ((i + 1) % spt != 0) continue;
+        if (++s == NS) { s = 0; round++; }
+        if (++st != spt) continue;
+        st = 0;
 
         // ---------------------------------------------------------------- the tile is complete
-        const int64_t tile = group + (i / spt) * p.groups;
-        const int64_t n0 = tile * ROWS;
+        const int64_t this_tile = tile;
+        tile += p.groups;
+        const int64_t n0 = this_tile * ROWS;
         asm volatile("bar.sync 1, 256;" ::: "memory");   // the previous tile's sums have been read (consumers only)
 #pragma unroll
         for (int nt = 0; nt < NT; nt++) {
@@ -360,7 +371,7 @@ bulk_gemv_kernel(const GemvParams p) {
         if constexpr (EPI == 2) {
             if (r < 8) {
                 const float gate = v, up = part[ant][col][r + 8];
-                const int64_t f = tile * 8 + r;
+                const int64_t f = this_tile * 8 + r;
                 if (f < N / 2) out[int64_t(m) * (N / 2) + f] = ib::from_f32<TOut>(gate / (1.0f + expf(-gate)) * up);
             }
         } else {
