@@ -351,9 +351,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             for (int i = 0; i < pre; i++)
                 tma_load_2d(base + i * C::STAGE_BYTES + C::A_BYTES, &tm_b, full_bar(i), (kb0 + i) * BK, tile_b * BN);
             issued = pre;
-            for (int i = pre; i < n_kb; i++) {
-                const int s = i % S;
-                const uint32_t round = i / S;
+            int s = pre % S;                             // (slot and round carried along: S is a run-time value)
+            uint32_t round = pre / S;
+            for (int i = pre; i < n_kb; i++, s = (s + 1 == S ? 0 : s + 1), round += (s == 0)) {
                 if (i >= S && !mbar_wait(empty_bar(s), (round - 1) & 1)) {
                     atomicExch(p.status, STATUS_TIMEOUT_PRODUCER); slots[1] = 1; break;
                 }
@@ -374,9 +374,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         // ---------------------------------------------------------------- MMA issuer
         if (lane == 0) {
             constexpr uint32_t idesc = make_idesc(BN);
-            for (int i = 0; i < n_kb; i++) {
-                const int s = i % S;
-                if (!mbar_wait(full_bar(s), (i / S) & 1)) {
+            int s = 0;
+            uint32_t round = 0;
+            for (int i = 0; i < n_kb; i++, s = (s + 1 == S ? 0 : s + 1), round += (s == 0)) {
+                if (!mbar_wait(full_bar(s), round & 1)) {
                     atomicExch(p.status, STATUS_TIMEOUT_MMA); slots[1] = 1; break;
                 }
                 tc_fence_after();
