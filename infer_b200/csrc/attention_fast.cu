@@ -45,7 +45,8 @@ constexpr int DEC_WARPS = 4, DEC_STAGES = 3;
 constexpr int MAX_SPLITS = 8;                   // slices of the key range per (segment, kv head) = cluster size
 constexpr int DEC_STAGE_BYTES = 2 * PAGE * ROW_BYTES;                       // K page + V page
 constexpr int DEC_SMEM = DEC_WARPS * DEC_STAGES * DEC_STAGE_BYTES;
-constexpr int DEC_MERGE_BYTES = DEC_WARPS * (16 * HD + 32) * 4;
+constexpr int MO_PITCH = HD + 8;                // floats between rows of a warp's partial output: 8-byte stores of a half-warp hit 32 banks
+constexpr int DEC_MERGE_BYTES = DEC_WARPS * (16 * MO_PITCH + 32) * 4;
 static_assert(DEC_MERGE_BYTES <= DEC_SMEM, "merge area must fit the stage area");
 
 constexpr int PF_BM = 64, PF_BN = 64, PF_WARPS = 4;
@@ -130,10 +131,13 @@ __device__ __forceinline__ void softmax_update(float (*s)[4], float* m, float* l
         }
 #pragma unroll
     for (int h = 0; h < 2; h++) l[h] = l[h] * corr[h] + sum[h];
+    // once the running maximum has settled the factors are exactly 1 for every row of the warp: skip the multiplies
+    if (__any_sync(0xffffffffu, (corr[0] != 1.0f) | (corr[1] != 1.0f))) {
 #pragma unroll
-    for (int n = 0; n < OT; n++) {
-        o[n][0] *= corr[0]; o[n][1] *= corr[0];
-        o[n][2] *= corr[1]; o[n][3] *= corr[1];
+        for (int n = 0; n < OT; n++) {
+            o[n][0] *= corr[0]; o[n][1] *= corr[0];
+            o[n][2] *= corr[1]; o[n][3] *= corr[1];
+        }
     }
 }
 
@@ -186,17 +190,25 @@ __device__ __forceinline__ void pv_tile(float (*o)[4], const float (*s)[4], uint
 // owns the page of the new position rotates k, puts k and v into its shared-memory copy of the page and into the
 // cache: one launch instead of two.
 
+#ifdef IB_ATTN_DEC_TRACE
+// Profiling build: thread 0 of the first CTA records the SM clock at the marks of the decode kernel.
+__device__ long long ib_dec_trace[32];
+#define IB_DT(k) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0) ib_dec_trace[k] = clock64(); } while (0)
+#else
+#define IB_DT(k) do {} while (0)
+#endif
+
 template <bool FUSED>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
 attn_decode_kernel(const AttnParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
-    __shared__ float wgt[MAX_SPLITS][16];                // weight of every rank's partial, per head of the group
     // This kernel is a chain of latencies and leaves HBM nearly idle: a good time to fetch a later product's weights.
     ib::l2_prefetch_share(p.prefetch, p.prefetch_bytes, (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x,
                           gridDim.x * gridDim.y * gridDim.z);
     // Everything this kernel reads before the wait below was written before the step began (segment and block
     // tables, the cache rows of earlier positions): with the rotation and the cache write fused in, the pages of the
     // old keys are requested while the kernel that makes q, k and v is still running.
+    IB_DT(0);
     const bool early = FUSED && p.write_cache;
     if (!early) ib::pdl_wait();
     const int split = blockIdx.x, kvh = blockIdx.y, seg = blockIdx.z;
@@ -257,7 +269,9 @@ attn_decode_kernel(const AttnParams p) {
             asm volatile("prefetch.global.L1 [%0];" ::"l"(p.sin + int64_t(pos) * (HD / 2) + lane * 32));
         }
     }
+    IB_DT(1);
     if (early) ib::pdl_wait();                           // q, k and v of this step come from the predecessor
+    IB_DT(2);
 
     // Query fragments straight from global memory: tile row = head within the group, zero beyond it.
     uint32_t qf[KS][4];
@@ -292,11 +306,10 @@ attn_decode_kernel(const AttnParams p) {
             qf[ks][3] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(qb + (g + 8) * HD + d + 8) : 0u;
         }
     }
-    for (int i = 0; i < my_pages; i++) {
-        cp_wait<DEC_STAGES - 2>();
-        __syncwarp();
-        uint8_t* stage = my_ptr + (i % DEC_STAGES) * DEC_STAGE_BYTES;
-        const uint32_t k_smem = smem_u32(stage), v_smem = k_smem + PAGE * ROW_BYTES;
+    IB_DT(3);
+    // Prepares page i of this warp (its stage has landed): for the page of the new position, rotates k and puts k and v
+    // into the shared-memory copy and into the cache. Returns the first key of the page.
+    auto prepare = [&](int i, uint8_t* stage) -> int {
         const int pg = pg_begin + warp + i * DEC_WARPS;
         const int key0 = pg * PAGE;
         if constexpr (FUSED) {
@@ -328,14 +341,49 @@ attn_decode_kernel(const AttnParams p) {
                 __syncwarp();
             }
         }
-        float s[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
-        qk_tile<2>(s, qf, k_smem);
-        softmax_update<2, HD / 8>(s, m, l, o, p.scale_log2, [&](int, int key) { return key0 + key >= lo && key0 + key <= pos; });
-        pv_tile<2>(o, s, v_smem);
+        return key0;
+    };
+    // Two pages (32 keys) can share one softmax round (DEC_PAIRS): the running maximum, the sum and the rescaling of
+    // the output cost the same for 32 keys as for 16. It needs a fourth stage to keep copies ahead of the arithmetic,
+    // and with 139 KB of shared memory the kernel no longer fits beside its neighbours' CTAs, which costs more (their
+    // weight streams start later) than the shorter loop gains: 16.7 against 9.2 us in a captured step. Off.
+    constexpr bool DEC_PAIRS = DEC_STAGES >= 4;
+    int i = 0;
+    while (i < my_pages) {
+        const bool two = DEC_PAIRS && i + 1 < my_pages;
+        if (two) cp_wait<(DEC_STAGES >= 3 ? DEC_STAGES - 3 : 0)>(); else cp_wait<DEC_STAGES - 2>();
+        __syncwarp();
+        if (i < 8) IB_DT(4 + 2 * i);
+        uint8_t* stage_a = my_ptr + (i % DEC_STAGES) * DEC_STAGE_BYTES;
+        uint8_t* stage_b = my_ptr + ((i + 1) % DEC_STAGES) * DEC_STAGE_BYTES;
+        const int key_a = prepare(i, stage_a);
+        const uint32_t ka = smem_u32(stage_a), va = ka + PAGE * ROW_BYTES;
+        if (two) {
+            const int key_b = prepare(i + 1, stage_b);
+            const uint32_t kb = smem_u32(stage_b), vb = kb + PAGE * ROW_BYTES;
+            float s[4][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}, {0, 0, 0, 0}, {0, 0, 0, 0}};
+            qk_tile<2>(s, qf, ka);
+            qk_tile<2>(s + 2, qf, kb);
+            softmax_update<4, HD / 8>(s, m, l, o, p.scale_log2, [&](int, int key) {
+                const int k = key < PAGE ? key_a + key : key_b + key - PAGE;
+                return (k >= lo) & (k <= pos);
+            });
+            pv_tile<2>(o, s, va);
+            pv_tile<2>(o, s + 2, vb);
+        } else {
+            float s[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
+            qk_tile<2>(s, qf, ka);
+            softmax_update<2, HD / 8>(s, m, l, o, p.scale_log2, [&](int, int key) { return (key_a + key >= lo) & (key_a + key <= pos); });
+            pv_tile<2>(o, s, va);
+        }
         __syncwarp();
         issue(i + DEC_STAGES - 1);
+        if (two) issue(i + DEC_STAGES);
+        if (i < 8) IB_DT(5 + 2 * i);
+        i += two ? 2 : 1;
     }
     cp_wait<0>();
+    IB_DT(20);
     ib::pdl_launch_dependents();
 #pragma unroll
     for (int h = 0; h < 2; h++) {
@@ -344,12 +392,12 @@ attn_decode_kernel(const AttnParams p) {
     }
     __syncthreads();                                     // every warp is done with its stages: reuse them for the merge
     float* mo = reinterpret_cast<float*>(smem);          // [warp][16][HD], after the CTA merge: [0][16][HD] holds the CTA's sum
-    float* mml = mo + DEC_WARPS * 16 * HD;               // [warp][16][2]; after the CTA merge [0][16][2]
+    float* mml = mo + DEC_WARPS * 16 * MO_PITCH;         // [warp][16][2]
 #pragma unroll
     for (int n = 0; n < HD / 8; n++) {
-        float* b = mo + (warp * 16) * HD + n * 8 + t4 * 2;
-        b[g * HD] = o[n][0]; b[g * HD + 1] = o[n][1];
-        b[(g + 8) * HD] = o[n][2]; b[(g + 8) * HD + 1] = o[n][3];
+        float* b = mo + (warp * 16) * MO_PITCH + n * 8 + t4 * 2;
+        *reinterpret_cast<float2*>(b + g * MO_PITCH) = make_float2(o[n][0], o[n][1]);
+        *reinterpret_cast<float2*>(b + (g + 8) * MO_PITCH) = make_float2(o[n][2], o[n][3]);
     }
     if (t4 == 0) {
         mml[(warp * 16 + g) * 2] = m[0]; mml[(warp * 16 + g) * 2 + 1] = l[0];
@@ -369,7 +417,7 @@ attn_decode_kernel(const AttnParams p) {
             const float Ms = M == -INFINITY ? 0.0f : M;
             float acc = 0.0f;
 #pragma unroll
-            for (int w = 0; w < DEC_WARPS; w++) acc += mo[(w * 16 + row) * HD + d] * exp2f(mml[(w * 16 + row) * 2] - Ms);
+            for (int w = 0; w < DEC_WARPS; w++) acc += mo[(w * 16 + row) * MO_PITCH + d] * exp2f(mml[(w * 16 + row) * 2] - Ms);
             cta_val[e] = acc;
         }
         if (threadIdx.x < G) {
@@ -381,6 +429,7 @@ attn_decode_kernel(const AttnParams p) {
             for (int w = 0; w < DEC_WARPS; w++) cta_l += mml[(w * 16 + row) * 2 + 1] * exp2f(mml[(w * 16 + row) * 2] - Ms);
         }
     }
+    IB_DT(21);
     bf16* out_row = p.out + (int64_t(t) * p.n_heads + int64_t(kvh) * G) * HD;
     if (n_splits == 1) {
         __shared__ float inv_l[16];
@@ -390,49 +439,51 @@ attn_decode_kernel(const AttnParams p) {
         for (int idx = threadIdx.x; idx < G * HD; idx += DEC_WARPS * 32, e++) out_row[idx] = __float2bfloat16_rn(cta_val[e] * inv_l[idx / HD]);
         return;
     }
-    __syncthreads();                                     // all reads of the per-warp areas are done
+    // The slices of the key range meet through distributed shared memory: every rank owns a share of the G * HD output
+    // elements and receives the other ranks' values for them (and every rank's maximum and sum per head) into arrays
+    // of its own, apart from the page ring that slower warps of the owner may still be using. One cluster barrier
+    // after the pushes; the owner then adds the slices in rank order and nobody touches remote memory again, so the
+    // ranks leave independently.
+    __shared__ float recv_o[16 * HD];                    // [rank][share]
+    __shared__ float recv_ml[MAX_SPLITS][16][2];
+    cg::cluster_group cl = cg::this_cluster();
+    IB_DT(22);
+    const int total = G * HD, share = (total + n_splits - 1) / n_splits;
     {
         int e = 0;
-        for (int idx = threadIdx.x; idx < G * HD; idx += DEC_WARPS * 32, e++) mo[idx] = cta_val[e];
-        if (threadIdx.x < G) { mml[threadIdx.x * 2] = cta_m; mml[threadIdx.x * 2 + 1] = cta_l; }
+        for (int idx = threadIdx.x; idx < total; idx += DEC_WARPS * 32, e++) {
+            const int owner = idx / share;
+            cl.map_shared_rank(recv_o, owner)[split * share + (idx - owner * share)] = cta_val[e];
+        }
+        if (threadIdx.x < G) {
+            for (int r = 0; r < n_splits; r++) {
+                float* ml = cl.map_shared_rank(&recv_ml[0][0][0], r) + (split * 16 + threadIdx.x) * 2;
+                ml[0] = cta_m; ml[1] = cta_l;
+            }
+        }
     }
-    cg::cluster_group cl = cg::this_cluster();
     cl.sync();
-    // Weights of the ranks' partials: exp2(m_r - M) / sum_r l_r exp2(m_r - M), per head, from every rank's (m, l).
-    if (threadIdx.x < G) {
-        const int row = threadIdx.x;
-        float mr[MAX_SPLITS], lr[MAX_SPLITS], M = -INFINITY;
+    IB_DT(23);
+    for (int j = threadIdx.x; j < share; j += DEC_WARPS * 32) {
+        const int idx = split * share + j;
+        if (idx >= total) break;
+        const int row = idx / HD;
+        float M = -INFINITY;
+#pragma unroll
+        for (int r = 0; r < MAX_SPLITS; r++) if (r < n_splits) M = fmaxf(M, recv_ml[r][row][0]);
+        const float Ms = M == -INFINITY ? 0.0f : M;
+        float acc = 0.0f, L = 0.0f;
 #pragma unroll
         for (int r = 0; r < MAX_SPLITS; r++) {
             if (r < n_splits) {
-                const float* rml = cl.map_shared_rank(mml, r);
-                mr[r] = rml[row * 2]; lr[r] = rml[row * 2 + 1];
-            } else { mr[r] = -INFINITY; lr[r] = 0.0f; }
-            M = fmaxf(M, mr[r]);
+                const float w = exp2f(recv_ml[r][row][0] - Ms);
+                L += recv_ml[r][row][1] * w;
+                acc += recv_o[r * share + j] * w;
+            }
         }
-        const float Ms = M == -INFINITY ? 0.0f : M;
-        float L = 0.0f;
-#pragma unroll
-        for (int r = 0; r < MAX_SPLITS; r++) { mr[r] = exp2f(mr[r] - Ms); L += lr[r] * mr[r]; }
-        const float inv = L > 0.0f ? 1.0f / L : 0.0f;
-#pragma unroll
-        for (int r = 0; r < MAX_SPLITS; r++) wgt[r][row] = mr[r] * inv;
+        out_row[idx] = __float2bfloat16_rn(L > 0.0f ? acc / L : 0.0f);
     }
-    __syncthreads();
-    // Each rank combines its share of the G * HD output elements from all ranks, in rank order.
-    const int total = G * HD, share = (total + n_splits - 1) / n_splits;
-    const int e_begin = split * share, e_end = min(total, e_begin + share);
-    for (int idx = e_begin + threadIdx.x; idx < e_end; idx += DEC_WARPS * 32) {
-        const int row = idx / HD;
-        float v[MAX_SPLITS];
-#pragma unroll
-        for (int r = 0; r < MAX_SPLITS; r++) v[r] = r < n_splits ? cl.map_shared_rank(mo, r)[idx] : 0.0f;
-        float acc = 0.0f;
-#pragma unroll
-        for (int r = 0; r < MAX_SPLITS; r++) acc += v[r] * wgt[r][row];
-        out_row[idx] = __float2bfloat16_rn(acc);
-    }
-    cl.sync();                                           // shared memory of every rank stays alive until all have read
+    IB_DT(24);
 }
 
 // ================================================================================================ prefill
@@ -546,6 +597,12 @@ attn_prefill_kernel(const AttnParams p) {
 }  // namespace
 
 IB_EXPORT int ib_attention_head_dim() { return HD; }
+
+#ifdef IB_ATTN_DEC_TRACE
+IB_EXPORT int ib_attention_decode_trace(long long* host) {
+    return cudaMemcpyFromSymbol(host, ib_dec_trace, sizeof(ib_dec_trace)) == cudaSuccess ? IB_OK : IB_ERR_CUDA;
+}
+#endif
 
 namespace {
 
