@@ -90,6 +90,14 @@ __device__ __forceinline__ void mma_bf16(float* c, uint32_t a0, uint32_t a1, uin
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+#ifdef IB_GEMV_TRACE
+// Profiling build: the first consumer thread of the first CTA records the SM clock at the kernel's marks.
+__device__ long long ib_gemv_trace[64];
+#define IB_GT(k) do { if (blockIdx.x == 0 && threadIdx.x == 0 && (k) < 64) ib_gemv_trace[k] = clock64(); } while (0)
+#else
+#define IB_GT(k) do {} while (0)
+#endif
+
 struct GemvParams {
     const bf16* x;            // [M, K]; or, with norm_w, float rows that are RMS-normalised first (K <= KC_MAX)
     const float* norm_w;      // [K] or null
@@ -101,6 +109,7 @@ struct GemvParams {
     int M;
     int64_t N, K;
     int cluster;              // CTAs per tile
+    int gate_ring;            // 1: the ring's second slot is requested only after the consumers have requested the activations
     int kc;                   // elements of K per stage and row: a multiple of 64, at most KC_MAX
     int ns;                   // stages in the ring: 2 .. NS_MAX, ns * ROWS * (kc * 2 + 64) <= RING_BYTES
     int64_t tiles;
@@ -114,7 +123,7 @@ template <int NT, int EPI, typename TOut>
 __global__ void __launch_bounds__(THREADS, 2)
 bulk_gemv_kernel(const GemvParams p) {
     extern __shared__ __align__(128) uint8_t stages[];   // [ns][ROWS][pitch]
-    __shared__ __align__(8) uint64_t bars[2 * NS_MAX];   // full[ns], empty[ns]
+    __shared__ __align__(8) uint64_t bars[2 * NS_MAX + 1]; // full[ns], empty[ns], activations requested
     __shared__ float red[WARPS][NT][8][ROWS];
     __shared__ float part[NT][8][ROWS];                  // this CTA's sum; read by the cluster's first CTA
     __shared__ float sumsq[WARPS][NT * 8];               // the warps' shares of a row's sum of squares (fused norm)
@@ -141,6 +150,7 @@ bulk_gemv_kernel(const GemvParams p) {
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < NS; s++) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), WARPS); }
+        mbar_init(bar0 + 8u * (2 * NS_MAX), WARPS);
         failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -160,6 +170,15 @@ bulk_gemv_kernel(const GemvParams p) {
         uint32_t round = 0;
         int64_t tile = group;
         for (int64_t i = 0; i < n_iter; i++) {
+            if (i == 1 && p.gate_ring) {
+                // With every SM's ring being filled at once, activations requested after the dependency wait would
+                // queue behind megabytes of weights and the consumers would start microseconds late: the second slot
+                // waits until the consumers have sent their requests.
+                int ok = 1;
+                if (lane == 0) ok = mbar_wait(bar0 + 8u * (2 * NS_MAX), 0) ? 1 : 0;
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) { if (lane == 0) { atomicExch(p.status, STATUS_TIMEOUT); failed = 1; } break; }
+            }
             if (i >= NS) {
                 int ok = 1;
                 if (lane == 0) ok = mbar_wait(empty_bar(s), (round - 1) & 1u) ? 1 : 0;
@@ -187,6 +206,7 @@ bulk_gemv_kernel(const GemvParams p) {
         return;
     }
     // -------------------------------------------------------------------- consumers (warps 0..7)
+    IB_GT(0);
     if (p.norm_w) {                                      // the norm's weight does not come from the predecessor: into L1 now
 #pragma unroll
         for (int u = 0; u < CPW_MAX; u++) {
@@ -195,6 +215,7 @@ bulk_gemv_kernel(const GemvParams p) {
         }
     }
     ib::pdl_wait();                                      // activations come from the predecessor
+    IB_GT(1);
     bool x_ok[NT];
     const bf16* xr[NT];
 #pragma unroll
@@ -235,6 +256,7 @@ bulk_gemv_kernel(const GemvParams p) {
                     hi[u][nt] = (k_ok[u] && x_ok[nt]) ? src[1] : zero;
                 }
             }
+            if (lane == 0) mbar_arrive(bar0 + 8u * (2 * NS_MAX));        // the requests are out: the producer may go on
             auto sq = [](float a, uint4 q) {
                 a = fmaf(__uint_as_float(q.x), __uint_as_float(q.x), a);
                 a = fmaf(__uint_as_float(q.y), __uint_as_float(q.y), a);
@@ -290,14 +312,19 @@ bulk_gemv_kernel(const GemvParams p) {
                 for (int nt = 0; nt < NT; nt++)
                     b[u][nt] = (k_ok[u] && x_ok[nt]) ? __ldg(reinterpret_cast<const uint4*>(xr[nt] + (warp + u * WARPS) * 32)) : zero;
             }
+            if (lane == 0) mbar_arrive(bar0 + 8u * (2 * NS_MAX));
         }
+    } else if (lane == 0) {
+        mbar_arrive(bar0 + 8u * (2 * NS_MAX));
     }
 
+    IB_GT(2);
     int s = 0, st = 0;
     uint32_t round = 0;
     int64_t tile = group;
     for (int64_t i = 0; i < n_iter; i++) {
         const int64_t k0 = (s_begin + st) * KC;
+        IB_GT(4 + 4 * int(i));
         if (!hoist) {
             // activations of this warp's chunks: independent of the weights, so they are loaded before the wait
 #pragma unroll
@@ -313,6 +340,7 @@ bulk_gemv_kernel(const GemvParams p) {
             if (lane == 0) { atomicExch(p.status, STATUS_TIMEOUT); failed = 1; }
             break;
         }
+        IB_GT(5 + 4 * int(i));
         const uint8_t* stg = stages + s * STAGE_BYTES;
 #pragma unroll
         for (int u = 0; u < CPW; u++) {
@@ -327,6 +355,7 @@ bulk_gemv_kernel(const GemvParams p) {
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(empty_bar(s));
+        IB_GT(6 + 4 * int(i));
         if (++s == NS) { s = 0; round++; }
         if (++st != spt) continue;
         st = 0;
@@ -367,6 +396,7 @@ bulk_gemv_kernel(const GemvParams p) {
             asm volatile("bar.sync 1, 256;" ::: "memory");
         }
         const int m = ant * 8 + col;
+        IB_GT(7 + 4 * int(i));
         if (!writer || !active || m >= p.M || failed) continue;
         if constexpr (EPI == 2) {
             if (r < 8) {
@@ -454,6 +484,8 @@ IB_EXPORT int ib_linear_skinny_bulk(const void* x, const float* norm_w, float no
     GemvParams p;
     p.x = (const bf16*)x; p.norm_w = norm_w; p.eps = norm_eps; p.w = (const bf16*)w; p.bias = bias; p.residual = residual; p.out = out;
     p.M = int(M); p.N = N; p.K = K; p.cluster = cluster; p.status = status; p.tiles = tiles; p.kc = kc; p.ns = ns;
+    // gate the ring's second slot where the whole GPU's rings fill at once (a CTA per half SM) and a tile is one stage
+    p.gate_ring = (n_stages == 1 && cluster == 1 && tiles >= 2LL * sms) ? 1 : 0;
     p.prefetch = prefetch; p.prefetch_bytes = prefetch_bytes & ~int64_t(15);
     // Two CTAs fit an SM; with more tiles than that, a CTA walks over several and its ring never drains between them.
     constexpr int64_t PER_SM = IB_GEMV_CTAS_PER_SM;
@@ -463,3 +495,9 @@ IB_EXPORT int ib_linear_skinny_bulk(const void* x, const float* norm_w, float no
     if (M <= 8) return launch<1>(p, out_dtype, epi, grid_ctas, stream);
     return launch<2>(p, out_dtype, epi, grid_ctas, stream);
 }
+
+#ifdef IB_GEMV_TRACE
+IB_EXPORT int ib_linear_skinny_bulk_trace(long long* host) {
+    return cudaMemcpyFromSymbol(host, ib_gemv_trace, sizeof(ib_gemv_trace)) == cudaSuccess ? IB_OK : IB_ERR_CUDA;
+}
+#endif
