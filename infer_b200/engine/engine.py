@@ -74,13 +74,20 @@ FEEDBACK_TOKEN = -1           # as a decode entry's token: "what the sampler pro
 GRAPH_WIDTH_PAGES = 32        # decode-only block tables are padded to a multiple of this many pages (512 positions)
 GRAPH_WARMUP_STEPS = 2        # eager steps of a shape before its graph is captured
 MAX_GRAPHS = 48
-GRAPH_COPIES = 2              # executable copies per shape, launched in turn
+GRAPH_COPIES = 2              # executable copies per decode shape, launched in turn
+# Steps that hold prompt portions are captured too once their exact shape (segment lengths, wanted rows, table widths)
+# has come a few times, as it does when prompts are cut into portions of the token budget: up to this many shapes, one
+# executable each, and only steps of at most this many tokens (a graph keeps its activations allocated).
+PORTION_GRAPH_AFTER = 2
+MAX_PORTION_GRAPHS = 6
+PORTION_GRAPH_MAX_TOKENS = 8192
 
 
 class _GraphEntry:
     def __init__(self, static: torch.Tensor):
         self.static, self.graphs, self.turn, self.warm, self.n_launches = static, [], 0, 0, 0
         self.pinned, self.flip = None, 0
+        self.copies = GRAPH_COPIES
 
 
 class Engine:
@@ -117,9 +124,11 @@ class Engine:
         # The sampler leaves every request's last token here (indexed by state slot); a decode entry whose token is
         # FEEDBACK_TOKEN reads it, so that the host need not see a token before the next step is launched.
         self.next_tokens = torch.zeros(max(1, max_requests), dtype=torch.int32, device=self.rt.device)
-        # Decode-only steps of the bfloat16 path are captured into CUDA graphs, one per (batch, wanted rows, table widths).
+        # Decode-only steps of the bfloat16 path are captured into CUDA graphs, one per (batch, wanted rows, table widths);
+        # steps with prompt portions once their exact shape has repeated.
         self.use_graphs = bool(cuda_graphs) and dtype == torch.bfloat16
         self._graphs: Dict[tuple, _GraphEntry] = {}
+        self._portion_seen: Dict[tuple, int] = {}         # how often a shape with prompt portions has come
         self._graph_pool = torch.cuda.graph_pool_handle() if self.use_graphs else None
 
     # ------------------------------------------------------------------ construction helpers
@@ -222,14 +231,33 @@ class Engine:
                 t = cache.block_table(e.rid, gi)
                 tab[s, :len(t)] = t
         entry = None
+        key = None
         if graphs and T == S:
             key = (S, n_want, tuple(widths))
+        elif graphs and T <= PORTION_GRAPH_MAX_TOKENS:
+            pkey = ("portions", tuple(seg_lens), n_want, tuple(widths))
+            if pkey in self._graphs:
+                key = pkey
+            else:
+                if len(self._portion_seen) > 256:
+                    self._portion_seen.clear()
+                seen = self._portion_seen[pkey] = self._portion_seen.get(pkey, 0) + 1
+                if seen > PORTION_GRAPH_AFTER:
+                    key = pkey
+        if key is not None:
             entry = self._graphs.get(key)
             if entry is None:
-                if len(self._graphs) >= MAX_GRAPHS:
-                    self._graphs.pop(next(iter(self._graphs)))
+                portion = key[0] == "portions"
+                if portion:
+                    old = [k for k in self._graphs if k[0] == "portions"]
+                    if len(old) >= MAX_PORTION_GRAPHS:
+                        self._graphs.pop(old[0])
+                elif len(self._graphs) >= MAX_GRAPHS:
+                    self._graphs.pop(next(k for k in self._graphs if k[0] != "portions"))
                 entry = self._graphs[key] = _GraphEntry(torch.empty(buf.size, dtype=torch.int32, device=self.rt.device))
                 entry.pinned = [torch.empty(buf.size, dtype=torch.int32).pin_memory() for _ in range(2)]
+                if portion:
+                    entry.copies, entry.warm = 1, GRAPH_WARMUP_STEPS - 1      # the shape has run eagerly before
             # two pinned staging buffers alternate, so that one is free while the other's copy may still be in flight
             entry.flip ^= 1
             host = entry.pinned[entry.flip]
@@ -281,10 +309,10 @@ class Engine:
         with torch.cuda.device(self.rt.device):
             if entry is None:
                 logits = self.model.forward(ctx, self.cache_views)
-            elif len(entry.graphs) == GRAPH_COPIES:
+            elif len(entry.graphs) == entry.copies:
                 # Copies of the graph take turns: launching an executable graph again while its previous launch is
                 # still running is serialised by the driver, which would put the launch cost between two steps.
-                entry.turn = (entry.turn + 1) % GRAPH_COPIES
+                entry.turn = (entry.turn + 1) % entry.copies
                 graph, logits = entry.graphs[entry.turn]
                 graph.replay()
                 ops._LAUNCHES[0] += entry.n_launches

@@ -137,3 +137,32 @@ def test_far_key_stands_out():
     ref = pm.forward(cfg, H.as_compute(W, dtype), ids).numpy()
     rows = sorted(got)
     H.check_f32(np.stack([got[p] for p in rows]), ref[rows], "far key")
+
+
+def test_repeated_portion_shapes_are_captured_and_replay_like_eager():
+    """Steps with prompt portions are captured into CUDA graphs once their exact shape has come a few times (prompts cut
+    at the token budget): the replays give the bits of the eager path, for other tokens and other pages."""
+    from infer_b200.engine import StepEntry
+    name = "b"
+    cfg = H.TINY[name]
+    eager = _engine(name, torch.bfloat16, cuda_graphs=False)
+    graph = _engine(name, torch.bfloat16)
+    for r in range(7):
+        ids = H.random_ids(cfg, 41, 100 + r)
+        outs = []
+        for eng in (eager, graph):
+            eng.add_request("x")
+            a = eng.step([StepEntry("x", ids[:24], [0, 23])]).float().cpu()
+            b = eng.step([StepEntry("x", ids[24:40], [15])]).float().cpu()
+            c = eng.step([StepEntry("x", ids[40:], [0])]).float().cpu()
+            eng.check_status()
+            eng.end_request("x")
+            outs.append((a, b, c))
+        for x, y in zip(*outs):
+            assert torch.equal(x, y), f"round {r}"
+    portion_keys = [k for k in graph._graphs if k[0] == "portions"]
+    assert len(portion_keys) == 2 and all(len(graph._graphs[k].graphs) == 1 for k in portion_keys)
+    ref = H.oracle(cfg, SEED, H.STORED_DTYPE[name], torch.bfloat16, ids)
+    refr = H.oracle(cfg, SEED, H.STORED_DTYPE[name], torch.bfloat16, ids, torch.bfloat16)
+    got = torch.cat(outs[1]).numpy()
+    H.check_bf16(got, ref[[0, 23, 39, 40]], refr[[0, 23, 39, 40]], "captured portions")
