@@ -50,6 +50,7 @@ constexpr int KC_MAX = 1536;              // most elements of K per stage and ro
 constexpr int CPW_MAX = KC_MAX / 32 / WARPS;   // most 32-element chunks per warp and stage
 constexpr int NS_MAX = 8;                 // most stages in the ring
 constexpr int RING_BYTES = 2 * ROWS * (KC_MAX * 2 + 64);
+constexpr int NW_BYTES = KC_MAX * 4;         // the fused norm's weight, behind the ring
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
 constexpr int STATUS_TIMEOUT = 104;
 
@@ -110,6 +111,8 @@ struct GemvParams {
     int64_t N, K;
     int cluster;              // CTAs per tile
     int gate_ring;            // 1: the ring's second slot is requested only after the consumers have requested the activations
+    int nw_smem;              // 1: the fused norm's weight is staged in shared memory behind the ring (measured: q/k/v
+                              //    4.1 -> 3.2 us; with every SM's ring filling at once, gate/up, it costs 0.4 us instead)
     int kc;                   // elements of K per stage and row: a multiple of 64, at most KC_MAX
     int ns;                   // stages in the ring: 2 .. NS_MAX, ns * ROWS * (kc * 2 + 64) <= RING_BYTES
     int64_t tiles;
@@ -119,7 +122,7 @@ struct GemvParams {
     int64_t prefetch_bytes;
 };
 
-template <int NT, int EPI, typename TOut>
+template <int NT, int EPI, typename TOut, bool NWS>
 __global__ void __launch_bounds__(THREADS, 2)
 bulk_gemv_kernel(const GemvParams p) {
     extern __shared__ __align__(128) uint8_t stages[];   // [ns][ROWS][pitch]
@@ -207,11 +210,20 @@ bulk_gemv_kernel(const GemvParams p) {
     }
     // -------------------------------------------------------------------- consumers (warps 0..7)
     IB_GT(0);
-    if (p.norm_w) {                                      // the norm's weight does not come from the predecessor: into L1 now
+    // The norm's weight does not come from the predecessor: it goes into shared memory behind the ring now (up to 8 rows:
+    // with 16 the static arrays leave no room beside a second CTA, and it is fetched into L1 instead).
+    float* nw_s = reinterpret_cast<float*>(stages + RING_BYTES);
+    constexpr bool NW_SMEM = NWS;              // (a template parameter: as a run-time flag it cost 1 us per kernel)
+    if (p.norm_w) {
+        if constexpr (NW_SMEM) {
+            for (int64_t k = threadIdx.x * 4; k < K; k += WARPS * 32 * 4)
+                *reinterpret_cast<float4*>(nw_s + k) = __ldg(reinterpret_cast<const float4*>(p.norm_w + k));
+        } else {
 #pragma unroll
-        for (int u = 0; u < CPW_MAX; u++) {
-            const int64_t k = (warp + u * WARPS) * 32 + t * 8;
-            if (k < K) asm volatile("prefetch.global.L1 [%0];" ::"l"(p.norm_w + k));
+            for (int u = 0; u < CPW_MAX; u++) {
+                const int64_t k = (warp + u * WARPS) * 32 + t * 8;
+                if (k < K) asm volatile("prefetch.global.L1 [%0];" ::"l"(p.norm_w + k));
+            }
         }
     }
     ib::pdl_wait();                                      // activations come from the predecessor
@@ -268,6 +280,7 @@ bulk_gemv_kernel(const GemvParams p) {
 #pragma unroll
                 for (int nt = 0; nt < NT; nt++) ss[nt] = sq(sq(ss[nt], b[u][nt]), hi[u][nt]);
             }
+            IB_GT(60);
 #pragma unroll
             for (int nt = 0; nt < NT; nt++) {
                 ss[nt] += __shfl_xor_sync(0xffffffffu, ss[nt], 1);
@@ -275,6 +288,7 @@ bulk_gemv_kernel(const GemvParams p) {
                 if (t == 0) sumsq[warp][nt * 8 + g] = ss[nt];
             }
             asm volatile("bar.sync 1, 256;" ::: "memory");
+            IB_GT(61);
             float scale[NT];
 #pragma unroll
             for (int nt = 0; nt < NT; nt++) {
@@ -292,8 +306,13 @@ bulk_gemv_kernel(const GemvParams p) {
                 const int64_t k = (warp + u * WARPS) * 32 + t * 8;
                 float4 w0 = make_float4(0.f, 0.f, 0.f, 0.f), w1 = w0;
                 if (k_ok[u]) {
-                    w0 = __ldg(reinterpret_cast<const float4*>(p.norm_w + k));
-                    w1 = __ldg(reinterpret_cast<const float4*>(p.norm_w + k) + 1);
+                    if constexpr (NW_SMEM) {
+                        w0 = *reinterpret_cast<const float4*>(nw_s + k);
+                        w1 = *reinterpret_cast<const float4*>(nw_s + k + 4);
+                    } else {
+                        w0 = __ldg(reinterpret_cast<const float4*>(p.norm_w + k));
+                        w1 = __ldg(reinterpret_cast<const float4*>(p.norm_w + k) + 1);
+                    }
                 }
 #pragma unroll
                 for (int nt = 0; nt < NT; nt++) {
@@ -420,16 +439,22 @@ int launch(const GemvParams& p, int out_dtype, int epi, int grid_ctas, cudaStrea
     const dim3 grid{unsigned(grid_ctas), 1u, 1u};
     const dim3 block{THREADS, 1u, 1u};
     const unsigned cl = unsigned(p.cluster);
-#define IB_GEMV_LAUNCH(EPI_, T_)                                                                                   \
+#define IB_GEMV_LAUNCH_(EPI_, T_, NWS_)                                                                            \
     do {                                                                                                           \
         static bool configured = false;                                                                            \
         if (!configured) {                                                                                         \
-            cudaError_t e = cudaFuncSetAttribute(bulk_gemv_kernel<NT, EPI_, T_>,                                   \
-                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, RING_BYTES);         \
+            cudaError_t e = cudaFuncSetAttribute(bulk_gemv_kernel<NT, EPI_, T_, NWS_>,                             \
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, RING_BYTES + NW_BYTES); \
             if (e != cudaSuccess) return ib::fail(IB_ERR_CUDA, "linear_skinny_bulk: cannot set shared memory size: %s", cudaGetErrorString(e)); \
             configured = true;                                                                                     \
         }                                                                                                          \
-        return ib::launch("linear_skinny_bulk", bulk_gemv_kernel<NT, EPI_, T_>, grid, block, size_t(RING_BYTES), stream, cl, p); \
+        return ib::launch("linear_skinny_bulk", bulk_gemv_kernel<NT, EPI_, T_, NWS_>, grid, block,                 \
+                          size_t(RING_BYTES) + (NWS_ ? size_t(NW_BYTES) : 0), stream, cl, p);                      \
+    } while (0)
+#define IB_GEMV_LAUNCH(EPI_, T_)                                                                                   \
+    do {                                                                                                           \
+        if (NT == 1 && p.norm_w && p.nw_smem) IB_GEMV_LAUNCH_(EPI_, T_, true);                                     \
+        IB_GEMV_LAUNCH_(EPI_, T_, false);                                                                          \
     } while (0)
     if (epi == 2) {
         if (out_dtype != IB_BF16) return ib::fail(IB_ERR_ARG, "linear_skinny_bulk: the SwiGLU epilogue writes bfloat16");
@@ -442,6 +467,7 @@ int launch(const GemvParams& p, int out_dtype, int epi, int grid_ctas, cudaStrea
     if (out_dtype == IB_F32) IB_GEMV_LAUNCH(0, float);
     if (out_dtype == IB_BF16) IB_GEMV_LAUNCH(0, bf16);
 #undef IB_GEMV_LAUNCH
+#undef IB_GEMV_LAUNCH_
     return ib::fail(IB_ERR_ARG, "linear_skinny_bulk: unknown output dtype %d", out_dtype);
 }
 
@@ -486,6 +512,7 @@ IB_EXPORT int ib_linear_skinny_bulk(const void* x, const float* norm_w, float no
     p.M = int(M); p.N = N; p.K = K; p.cluster = cluster; p.status = status; p.tiles = tiles; p.kc = kc; p.ns = ns;
     // gate the ring's second slot where the whole GPU's rings fill at once (a CTA per half SM) and a tile is one stage
     p.gate_ring = (n_stages == 1 && cluster == 1 && tiles >= 2LL * sms) ? 1 : 0;
+    p.nw_smem = (norm_w && !p.gate_ring) ? 1 : 0;
     p.prefetch = prefetch; p.prefetch_bytes = prefetch_bytes & ~int64_t(15);
     // Two CTAs fit an SM; with more tiles than that, a CTA walks over several and its ring never drains between them.
     constexpr int64_t PER_SM = IB_GEMV_CTAS_PER_SM;
