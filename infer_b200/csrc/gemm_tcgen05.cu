@@ -88,6 +88,9 @@ __device__ __forceinline__ uint32_t map_cluster(uint32_t local_smem, uint32_t ra
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_smem), "r"(rank));
     return remote;
 }
+__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
 __device__ __forceinline__ float ld_cluster_f32(uint32_t addr) {
     float v;
     asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
@@ -179,6 +182,8 @@ template <int BN> struct Cfg {
     static constexpr int MAX_STAGES = BN >= 128 ? 6 : 8;                    // a CTA alone on its SM (decode: all of the ring in flight)
     static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
     static constexpr int SMEM_EXTRA = 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static constexpr int RECV_OFFSET = 256;                                 // behind the barriers
+    static constexpr int RECV_BYTES = BM * (BN + 8) * 4;                    // cluster split-K: the slices' columns of one owner
     static constexpr int SMEM_BYTES = MAX_STAGES * STAGE_BYTES + SMEM_EXTRA;
     static_assert(BM * BN * 4 <= STAGES * STAGE_BYTES, "a float partial tile must fit the smallest ring");
 };
@@ -196,16 +201,18 @@ __device__ __forceinline__ void epilogue_store(const GemmParams& p, const float*
         const int64_t half = p.N / 2;
         if (p.swap) {
             // lanes 0-7 and 16-23 of a warp hold gate rows, lanes 8-15 and 24-31 the matching up rows
+            // (no short-circuit operators and the arithmetic outside the condition: a branch per element, taken by half
+            // of the lanes, cost several times the arithmetic)
             const int64_t n = a_row;
-            const bool is_gate = (n & 8) == 0;
+            const bool row_ok = ((n & 8) == 0) & (n < p.N);
+            TOut* dst = out + (n >> 4) * 8 + (n & 7);
 #pragma unroll
             for (int j = 0; j < 16; j++) {
                 const float other = __shfl_xor_sync(0xffffffffu, v[j], 8);
                 const int64_t m = b_row0 + j;
-                if (is_gate && n < p.N && m < p.M && j < ncols) {
-                    const float gte = v[j];
-                    store_elem<TOut>(out + m * half + (n >> 4) * 8 + (n & 7), gte / (1.0f + expf(-gte)) * other);
-                }
+                const float gte = v[j];
+                const float act = __fdividef(gte, 1.0f + __expf(-gte)) * other;
+                if (row_ok & (m < p.M) & (j < ncols)) store_elem<TOut>(dst + m * half, act);
             }
         } else {
             const int64_t m = a_row, n0 = b_row0;
@@ -292,6 +299,14 @@ __device__ __forceinline__ void epilogue_store(const GemmParams& p, const float*
     }
 }
 
+#ifdef IB_GEMM_TRACE
+// Profiling build: the first CTA's producer, MMA and first epilogue thread record the SM clock at their marks.
+__device__ long long ib_gemm_trace[32];
+#define IB_MT(k) do { if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) ib_gemm_trace[k] = clock64(); } while (0)
+#else
+#define IB_MT(k) do {} while (0)
+#endif
+
 template <int BN, typename TOut>
 __global__ void __launch_bounds__(NUM_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const GemmParams p) {
@@ -306,6 +321,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     // slots[0] = TMEM base address, slots[1] = abort flag, slots[2] = "this CTA reduces the split-K slices"
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) IB_MT(0);
     // grid (tiles a, tiles b, slices), or with the slices as one cluster: (slices, tiles a, tiles b)
     const int tile_a = p.cluster_split ? blockIdx.y : blockIdx.x, tile_b = p.cluster_split ? blockIdx.z : blockIdx.y;
     const int split = p.cluster_split ? blockIdx.x : blockIdx.z;
@@ -333,6 +349,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = slots[0];
+    if (threadIdx.x == 0) IB_MT(1);
     // The set-up above overlapped the predecessor. Each role waits for it where it first touches what the predecessor
     // may have written: the producer before it loads activations, the epilogue before it reads or writes the output.
 
@@ -347,7 +364,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 mbar_expect_tx(full_bar(i), C::STAGE_BYTES);
                 tma_load_2d(base + i * C::STAGE_BYTES, &tm_a, full_bar(i), (kb0 + i) * BK, tile_a * BM);
             }
+            IB_MT(2);
             ib::pdl_wait();
+            IB_MT(3);
             for (int i = 0; i < pre; i++)
                 tma_load_2d(base + i * C::STAGE_BYTES + C::A_BYTES, &tm_b, full_bar(i), (kb0 + i) * BK, tile_b * BN);
             issued = pre;
@@ -364,6 +383,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 tma_load_2d(b_dst, &tm_b, full_bar(s), (kb0 + i) * BK, tile_b * BN);
                 issued = i + 1;
             }
+            IB_MT(4);
             if (slots[1]) {
                 // Drain: wait (bounded) until every copy this thread started has landed, so that none writes into
                 // shared memory after the CTA is gone.
@@ -381,6 +401,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     atomicExch(p.status, STATUS_TIMEOUT_MMA); slots[1] = 1; break;
                 }
                 tc_fence_after();
+                if (i == 0) IB_MT(5);
+                if (i == n_kb / 2) IB_MT(6);
                 const uint32_t a_addr = base + s * C::STAGE_BYTES, b_addr = a_addr + C::A_BYTES;
                 const uint64_t a_desc = make_desc(a_addr), b_desc = make_desc(b_addr);
 #pragma unroll
@@ -391,6 +413,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 umma_commit(empty_bar(s));
             }
             umma_commit(tmem_full_bar);
+            IB_MT(7);
         }
         ib::pdl_launch_dependents();
     } else {
@@ -403,20 +426,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         if (!ok) { atomicExch(p.status, STATUS_TIMEOUT_EPILOGUE); slots[1] = 1; }
         ok = __all_sync(0xffffffffu, ok);
         tc_fence_after();
+        if (threadIdx.x == 64) IB_MT(8);
         if (ok) {
             const int n_tiles = gridDim.x * gridDim.y;
             const int tile = tile_b * gridDim.x + tile_a;
             if (p.cluster_split) {
-                // This slice's tile goes to the start of the ring (every stage has been consumed), column-major like
-                // the workspace slices: the cluster adds the slices below.
-                float* mine = reinterpret_cast<float*>(base_ptr) + r;
+                // The K slices of a tile are the CTAs of one cluster. Every slice pushes the columns of its float tile to
+                // the CTA that owns them (a receive area behind the ring: a fast slice may push while the owner's ring is
+                // still in use), through distributed shared memory; after one cluster barrier the owners add what they
+                // received, in slice order, and nobody touches remote memory again.
+                const int per = (BN + p.splits - 1) / p.splits;               // columns per owner
+                const uint32_t recv = base + uint32_t(p.stages) * C::STAGE_BYTES + C::RECV_OFFSET;
+                const uint32_t mine = recv + uint32_t((split * per) * BM + r) * 4u;   // [slice][column of the owner][row]
+                int owner = 0, lc = 0;                            // (carried along: no division per column)
+                uint32_t dst = map_cluster(mine, 0u);
 #pragma unroll 1
                 for (int c = 0; c < BN; c += 16) {
                     uint32_t raw[16];
                     tmem_ld16(tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(c), raw);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int j = 0; j < 16; j++) mine[(c + j) * BM] = __uint_as_float(raw[j]);
+                    for (int j = 0; j < 16; j++) {
+                        st_cluster_f32(dst, __uint_as_float(raw[j]));
+                        dst += BM * 4u;
+                        if (++lc == per) { lc = 0; owner++; dst = map_cluster(mine, uint32_t(owner)); }
+                    }
                 }
             } else if (p.splits == 1) {
 #pragma unroll 1
@@ -478,35 +512,35 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         }
     }
     if (p.cluster_split) {
-        // Every CTA of the cluster adds its share of the tile's columns over all slices, in ascending order of the
-        // slice, reading the other CTAs' tiles through distributed shared memory, and runs the epilogue on them.
+        if (threadIdx.x == 64) IB_MT(11);
         __syncwarp();
-        cluster_sync();
+        cluster_sync();                                  // every slice's pushes have arrived
+        if (threadIdx.x == 64) IB_MT(12);
         if (warp >= 2 && !slots[1]) {
             const int r = (warp & 3) * 32 + lane;
             const int64_t a_row = int64_t(tile_a) * BM + r;
             const int per = (BN + p.splits - 1) / p.splits;
             const int c_begin = min(BN, split * per), c_end = min(BN, c_begin + per);
-            const uint32_t local = base + uint32_t(r) * 4u;
+            const float* recv = reinterpret_cast<const float*>(base_ptr + size_t(p.stages) * C::STAGE_BYTES + C::RECV_OFFSET) + r;
             for (int c0 = c_begin; c0 < c_end; c0 += 16) {
                 const int ncols = min(16, c_end - c0);
                 float v[16];
 #pragma unroll
                 for (int j = 0; j < 16; j++) v[j] = 0.0f;
                 for (int z = 0; z < p.splits; z++) {
-                    const uint32_t remote = map_cluster(local, uint32_t(z));
 #pragma unroll
                     for (int j = 0; j < 16; j++)
-                        if (j < ncols) v[j] += ld_cluster_f32(remote + uint32_t(c0 + j) * (BM * 4u));
+                        if (j < ncols) v[j] += recv[((z * per) + (c0 - c_begin) + j) * BM];
                 }
                 epilogue_store<TOut>(p, v, a_row, int64_t(tile_b) * BN + c0, ncols);
             }
         }
-        __syncwarp();
-        cluster_sync();                                  // no CTA leaves while its tile may still be read
+        if (threadIdx.x == 64) IB_MT(13);
     }
+    if (threadIdx.x == 64) IB_MT(9);
     tc_fence_before();
     __syncthreads();
+    if (threadIdx.x == 64) IB_MT(10);
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, C::TMEM_COLS);
@@ -876,7 +910,8 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, di
         configured = true;
     }
     if (p.stages < 1 || p.stages > C::MAX_STAGES) return ib::fail(IB_ERR_ARG, "gemm_tc: %d stages (at most %d)", p.stages, C::MAX_STAGES);
-    const size_t smem = size_t(p.stages) * C::STAGE_BYTES + C::SMEM_EXTRA;
+    const size_t smem = size_t(p.stages) * C::STAGE_BYTES + C::SMEM_EXTRA + (p.cluster_split ? C::RECV_BYTES : 0);
+    if (smem > size_t(C::SMEM_BYTES)) return ib::fail(IB_ERR_ARG, "gemm_tc: %d stages and the receive area do not fit", p.stages);
     return ib::launch("gemm_tc", gemm_tc_kernel<BN, TOut>, grid, dim3(NUM_THREADS), smem, stream,
                       p.cluster_split ? unsigned(p.splits) : 1u, ma, mb, p);
 }
@@ -914,6 +949,13 @@ int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& 
 template <int BN> int pick_stages(const GemmParams& p) {
     using C = Cfg<BN>;
     if (!p.swap) return C::STAGES;
+    if (p.cluster_split) {
+        // as many stages as the slice has k-blocks and no more: with the receive area a short slice then still fits
+        // beside a second CTA, and its neighbours in the stream can start under it
+        const int most = C::MAX_STAGES - 2;
+        const int want = p.kb_per_split < 2 ? 2 : p.kb_per_split;
+        return want > most ? most : want;
+    }
     const int want = p.kb_per_split < C::STAGES ? C::STAGES : p.kb_per_split;
     return want > C::MAX_STAGES ? C::MAX_STAGES : want;
 }
@@ -1107,3 +1149,9 @@ IB_EXPORT int ib_gemm_tc_static(const void* x, const void* w, const float* bias,
     }
     return ib_gemm_tc(x, w, bias, residual, out, M, N, K, out_dtype, 0, swap, bn, splits, workspace, counters, status, stream);
 }
+
+#ifdef IB_GEMM_TRACE
+IB_EXPORT int ib_gemm_tc_trace(long long* host) {
+    return cudaMemcpyFromSymbol(host, ib_gemm_trace, sizeof(ib_gemm_trace)) == cudaSuccess ? IB_OK : IB_ERR_CUDA;
+}
+#endif
