@@ -201,18 +201,21 @@ __device__ __forceinline__ void epilogue_store(const GemmParams& p, const float*
         const int64_t half = p.N / 2;
         if (p.swap) {
             // lanes 0-7 and 16-23 of a warp hold gate rows, lanes 8-15 and 24-31 the matching up rows
-            // (no short-circuit operators and the arithmetic outside the condition: a branch per element, taken by half
-            // of the lanes, cost several times the arithmetic)
+            // Columns go in pairs: the gate lane finishes column j with its partner's up value, the up lane column j + 1
+            // with its partner's gate value, so every lane computes and stores a result (one exchange per pair). No
+            // short-circuit operators, the arithmetic outside the condition: a branch per element cost several times it.
             const int64_t n = a_row;
-            const bool row_ok = ((n & 8) == 0) & (n < p.N);
+            const bool is_gate = (n & 8) == 0;
+            const bool row_ok = n < p.N;
             TOut* dst = out + (n >> 4) * 8 + (n & 7);
 #pragma unroll
-            for (int j = 0; j < 16; j++) {
-                const float other = __shfl_xor_sync(0xffffffffu, v[j], 8);
-                const int64_t m = b_row0 + j;
-                const float gte = v[j];
-                const float act = __fdividef(gte, 1.0f + __expf(-gte)) * other;
-                if (row_ok & (m < p.M) & (j < ncols)) store_elem<TOut>(dst + m * half, act);
+            for (int j = 0; j < 16; j += 2) {
+                const float got = __shfl_xor_sync(0xffffffffu, is_gate ? v[j + 1] : v[j], 8);
+                const float gte = is_gate ? v[j] : got, up = is_gate ? got : v[j + 1];
+                const int jj = is_gate ? j : j + 1;
+                const int64_t m = b_row0 + jj;
+                const float act = __fdividef(gte, 1.0f + __expf(-gte)) * up;
+                if (row_ok & (m < p.M) & (jj < ncols)) store_elem<TOut>(dst + m * half, act);
             }
         } else {
             const int64_t m = a_row, n0 = b_row0;
