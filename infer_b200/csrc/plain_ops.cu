@@ -74,29 +74,47 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
         out[r_out * hidden + i] = ib::from_f32<TOut>(xr[i] * scale * w[i]);
 }
 
-// The same norm for rows whose length is a multiple of 4 and whose buffers are 16-byte aligned: one warp per row,
-// 16-byte loads, the second pass over the row served by L1. Prefill spends a tenth of its time in norms otherwise.
+// The same norm for rows whose length is a multiple of 4 and whose buffers are 16-byte aligned: a block of four warps
+// per row, 16-byte loads kept in registers between the two passes (rows of up to 6144 elements; longer rows read the
+// row a second time, from L1). The sum of squares is put together in thread, lane and warp order, whatever the number
+// of rows is.
+constexpr int NORM_THREADS = 128, NORM_KEEP = 12;
 template <typename TOut>
-__global__ void __launch_bounds__(256)
-rmsnorm_warp_kernel(const float* __restrict__ x, const float* __restrict__ w, float eps, int64_t hidden,
-                    const int* __restrict__ rows, TOut* __restrict__ out, int64_t n_rows) {
+__global__ void __launch_bounds__(NORM_THREADS)
+rmsnorm_vec_kernel(const float* __restrict__ x, const float* __restrict__ w, float eps, int64_t hidden,
+                   const int* __restrict__ rows, TOut* __restrict__ out) {
     ib::pdl_wait();
-    const int lane = threadIdx.x & 31;
-    const int64_t r_out = int64_t(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (r_out >= n_rows) return;
+    __shared__ float red[NORM_THREADS / 32];
+    const int64_t r_out = blockIdx.x;
     const int64_t r_in = rows ? rows[r_out] : r_out;
     const float4* xr = reinterpret_cast<const float4*>(x + r_in * hidden);
     const float4* wr = reinterpret_cast<const float4*>(w);
     const int64_t n4 = hidden / 4;
+    float4 keep[NORM_KEEP];
     float ss = 0.0f;
-    for (int64_t i = lane; i < n4; i += 32) {
+#pragma unroll
+    for (int j = 0; j < NORM_KEEP; j++) {
+        const int64_t i = threadIdx.x + int64_t(j) * NORM_THREADS;
+        keep[j] = i < n4 ? xr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int j = 0; j < NORM_KEEP; j++) {
+        const float4 v = keep[j];
+        ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+    }
+    for (int64_t i = threadIdx.x + int64_t(NORM_KEEP) * NORM_THREADS; i < n4; i += NORM_THREADS) {
         const float4 v = xr[i];
         ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
     }
     ss = ib::warp_sum(ss);
-    const float scale = rsqrtf(ss / float(hidden) + eps);
-    for (int64_t i = lane; i < n4; i += 32) {
-        const float4 v = xr[i], g = wr[i];
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float total = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NORM_THREADS / 32; i++) total += red[i];
+    const float scale = rsqrtf(total / float(hidden) + eps);
+    auto emit = [&](int64_t i, float4 v) {
+        const float4 g = wr[i];
         const float a = v.x * scale * g.x, b = v.y * scale * g.y, c = v.z * scale * g.z, d = v.w * scale * g.w;
         if constexpr (sizeof(TOut) == 4) {
             reinterpret_cast<float4*>(out + r_out * hidden)[i] = make_float4(a, b, c, d);
@@ -107,7 +125,13 @@ rmsnorm_warp_kernel(const float* __restrict__ x, const float* __restrict__ w, fl
             u.y = *reinterpret_cast<uint32_t*>(&hi);
             reinterpret_cast<uint2*>(out + r_out * hidden)[i] = u;
         }
+    };
+#pragma unroll
+    for (int j = 0; j < NORM_KEEP; j++) {
+        const int64_t i = threadIdx.x + int64_t(j) * NORM_THREADS;
+        if (i < n4) emit(i, keep[j]);
     }
+    for (int64_t i = threadIdx.x + int64_t(NORM_KEEP) * NORM_THREADS; i < n4; i += NORM_THREADS) emit(i, xr[i]);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -564,11 +588,10 @@ IB_EXPORT int ib_rmsnorm(const float* x, const float* w, float eps, int64_t n_ro
     const int threads = hidden >= 1024 ? 256 : 128;
     // (the choice does not look at the number of rows: a row's result must not depend on what else is in the step)
     if (hidden % 4 == 0 && !((uintptr_t(x) | uintptr_t(w) | uintptr_t(out)) & 15)) {
-        const unsigned blocks = unsigned((n_rows + 7) / 8);
         if (out_dtype == IB_F32)
-            IB_LAUNCH(rmsnorm_warp_kernel<float>, blocks, 256, 0, x, w, eps, hidden, rows, (float*)out, n_rows);
+            IB_LAUNCH(rmsnorm_vec_kernel<float>, unsigned(n_rows), NORM_THREADS, 0, x, w, eps, hidden, rows, (float*)out);
         else if (out_dtype == IB_BF16)
-            IB_LAUNCH(rmsnorm_warp_kernel<bf16>, blocks, 256, 0, x, w, eps, hidden, rows, (bf16*)out, n_rows);
+            IB_LAUNCH(rmsnorm_vec_kernel<bf16>, unsigned(n_rows), NORM_THREADS, 0, x, w, eps, hidden, rows, (bf16*)out);
         else
             return ib::fail(IB_ERR_ARG, "ib_rmsnorm: unknown output dtype %d", out_dtype);
         return ib::check_launch("ib_rmsnorm");

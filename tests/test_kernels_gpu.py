@@ -34,7 +34,7 @@ def test_embedding(dtype):
     assert status.item() == 1 and float(out[1].abs().sum()) == 0.0      # refused, not read out of bounds
 
 
-@pytest.mark.parametrize("hidden", [1, 33, 96, 1536, 3000])
+@pytest.mark.parametrize("hidden", [1, 33, 96, 1536, 3000, 6148, 8192])
 def test_rmsnorm(hidden):
     ops = _ops()
     x = torch.randn(7, hidden, device=DEV) * 3
