@@ -61,6 +61,7 @@ def main(argv=None) -> int:
     ap.add_argument("--kv-heads", type=int, default=2)
     ap.add_argument("--head-dim", type=int, default=128)
     ap.add_argument("--splits", type=int, default=0)
+    ap.add_argument("--bn", type=int, default=0, help="tc: the tile code instead of the planner's (many tokens, no K slices)")
     ap.add_argument("--cluster", type=int, default=0)
     ap.add_argument("--regs", action="store_true", help="skinny: the register-streaming kernel instead of the bulk-copy one")
     ap.add_argument("--fused", action="store_true", help="attention: the decode kernel that also rotates and stores k/v")
@@ -92,6 +93,9 @@ def main(argv=None) -> int:
         if plan is not None and args.splits:
             tiles = -(-(N if plan[0] else M) // 128) * -(-(M if plan[0] else N) // plan[1])
             plan = (plan[0], plan[1], args.splits, args.splits * tiles * 128 * plan[1], tiles)
+
+        if plan is not None and args.bn:
+            plan = (0, args.bn, 1, 0, 0)
 
         def run(i):
             r = res

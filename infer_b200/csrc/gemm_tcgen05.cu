@@ -193,8 +193,10 @@ template <> __device__ __forceinline__ void store_elem<float>(float* p, float v)
 template <> __device__ __forceinline__ void store_elem<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
 
 // Applies bias/residual and stores 16 accumulator values of tile row `r`, tile columns [c0, c0 + 16).
-template <typename TOut>
-__device__ __forceinline__ void epilogue_store(const GemmParams& p, const float* v, int64_t a_row, int64_t b_row0, int ncols = 16) {
+// PRE: the residual's 16 floats were loaded by the caller ahead of time (plain mapping, whole chunk inside N, N % 8 == 0).
+template <typename TOut, bool PRE = false>
+__device__ __forceinline__ void epilogue_store(const GemmParams& p, const float* v, int64_t a_row, int64_t b_row0, int ncols = 16,
+                                               const float4* pre_res = nullptr) {
     TOut* out = reinterpret_cast<TOut*>(p.out);
     if (p.epi == 2) {
         // Feature rows come in blocks of 16: 8 gate rows, then the 8 matching up rows. out[m, 8 blk + r] = silu(g) * u.
@@ -266,7 +268,8 @@ __device__ __forceinline__ void epilogue_store(const GemmParams& p, const float*
                 const float4* r4 = reinterpret_cast<const float4*>(p.residual + m * p.N + n0);
 #pragma unroll
                 for (int j = 0; j < 4; j++) {
-                    const float4 r = r4[j];
+                    float4 r;
+                    if constexpr (PRE) r = pre_res[j]; else r = r4[j];
                     x[4 * j] += r.x; x[4 * j + 1] += r.y; x[4 * j + 2] += r.z; x[4 * j + 3] += r.w;
                 }
             }
@@ -557,8 +560,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 // peak. Here a CTA owns an SM, walks over 256 x 128 tiles (two M=128 MMAs per k-step share one B tile: a quarter
 // less operand traffic per flop) and keeps two accumulators of 256 columns in tensor memory, so that the epilogue
 // warps drain one tile while the MMA warp already works on the next; the operand ring runs on across tiles.
-// The tile is 256 x 128, or 256 x 96 where that fills the SMs better (a matrix of 1536 features has 12 or 16 column
-// tiles; with 8 row tiles that is 96 or 128 CTAs' worth of work for 148 SMs).
+// The tile is 256 x 128 with two MMAs per k-step, or (the default) 128 tokens x 256, 192 or 176 features with one,
+// whichever width fills the SMs best (a matrix of 1536 features has 6, 8 or 9 column tiles; with 16 row tiles that
+// is 96, 128 or 144 CTAs' worth of work for 148 SMs).
 #ifndef IB_GEMM_PSTAGES
 #define IB_GEMM_PSTAGES 4
 #endif
@@ -572,6 +576,67 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
+// The epilogue of the persistent kernels for one thread's accumulator row: COLS columns from tensor memory at `taddr`
+// to out[a_row, n_base ...]. Columns go in groups of 64: four tensor-memory loads under one wait, and with a residual
+// the group's 64 floats are requested before that wait (the first group's by the caller, before the accumulator is
+// even complete, through res_first/res_next), so that a row costs a few memory round trips instead of one per 16 columns.
+constexpr int DRAIN_GROUP = 4;
+struct ResidualAhead {
+    float4 r[DRAIN_GROUP][4];
+    bool on;                                                      // the vector path of epilogue_store will be taken
+};
+template <int COLS>
+__device__ __forceinline__ void residual_request(const GemmParams& p, ResidualAhead& ra, int64_t a_row, int64_t n_base, int c) {
+    if (!ra.on) return;
+    const float* row = p.residual + a_row * p.N + n_base + c;
+#pragma unroll
+    for (int g = 0; g < DRAIN_GROUP; g++) {
+        if (c + 16 * g < COLS && n_base + c + 16 * g + 16 <= p.N) {
+            const float4* r4 = reinterpret_cast<const float4*>(row + 16 * g);
+#pragma unroll
+            for (int j = 0; j < 4; j++) ra.r[g][j] = r4[j];
+        }
+    }
+}
+template <typename TOut, int COLS>
+__device__ __forceinline__ void drain_row(const GemmParams& p, uint32_t taddr, int64_t a_row, int64_t n_base, ResidualAhead& ra) {
+    static_assert(COLS % 16 == 0, "columns come in chunks of 16");
+    if (p.epi != 0 || p.residual == nullptr) {
+        // nothing to read from memory: chunk by chunk (measured faster than groups for the SwiGLU and bias epilogues)
+#pragma unroll 1
+        for (int c = 0; c < COLS; c += 16) {
+            uint32_t raw[16];
+            tmem_ld16(taddr + uint32_t(c), raw);
+            tmem_ld_wait();
+            float v[16];
+#pragma unroll
+            for (int j = 0; j < 16; j++) v[j] = __uint_as_float(raw[j]);
+            epilogue_store<TOut>(p, v, a_row, n_base + c);
+        }
+        return;
+    }
+#pragma unroll 1
+    for (int c = 0; c < COLS; c += 16 * DRAIN_GROUP) {
+        uint32_t raw[DRAIN_GROUP][16];
+#pragma unroll
+        for (int g = 0; g < DRAIN_GROUP; g++)
+            if (c + 16 * g < COLS) tmem_ld16(taddr + uint32_t(c + 16 * g), raw[g]);
+        tmem_ld_wait();
+#pragma unroll
+        for (int g = 0; g < DRAIN_GROUP; g++) {
+            if (c + 16 * g < COLS) {
+                float v[16];
+#pragma unroll
+                for (int j = 0; j < 16; j++) v[j] = __uint_as_float(raw[g][j]);
+                const int64_t n0 = n_base + c + 16 * g;
+                if (ra.on && n0 + 16 <= p.N) epilogue_store<TOut, true>(p, v, a_row, n0, 16, ra.r[g]);
+                else epilogue_store<TOut, false>(p, v, a_row, n0);
+            }
+        }
+        if (c + 16 * DRAIN_GROUP < COLS) residual_request<COLS>(p, ra, a_row, n_base, c + 16 * DRAIN_GROUP);
+    }
+}
+
 template <int PBN, bool WIDE, typename TOut>
 __global__ void __launch_bounds__(NUM_THREADS)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const GemmParams p) {
@@ -579,9 +644,10 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
     constexpr int S = PSTAGES;
-    // WIDE: 128 tokens x 256 features per tile, one M=128 x N=256 MMA per k-step (the A operand is read once for
-    // twice the columns: less shared-memory traffic per flop); else 256 tokens x PBN features, two M=128 MMAs.
-    constexpr int TM = WIDE ? 128 : PBM, TN = WIDE ? 256 : PBN;
+    // WIDE: 128 tokens x PBN features per tile (PBN up to 256), one M=128 x N=PBN MMA per k-step (the A operand is
+    // read once for all columns: less shared-memory traffic per flop); else 256 tokens x PBN features, two M=128 MMAs.
+    constexpr int TM = WIDE ? 128 : PBM, TN = PBN;
+    static_assert(PBN % 16 == 0 && PBN <= (WIDE ? 256 : 128), "tile width");
     constexpr int A_BYTES = TM * BK * 2, B_BYTES = TN * BK * 2;
     const uint32_t bars = base + S * P_STAGE_BYTES;               // full[S], empty[S], acc_full[2], acc_empty[2]
     volatile uint32_t* slots = reinterpret_cast<volatile uint32_t*>(base_ptr + S * P_STAGE_BYTES + (2 * S + 4) * 8);
@@ -679,40 +745,28 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
         const int quad = warp & 3;
         ib::pdl_wait();
         int lt = 0;
+        ResidualAhead ra;
         for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, lt++) {
             const int tm = tile % tiles_m, tn = tile / tiles_m;
             const int b = lt & 1;
+            const int64_t row0 = int64_t(tm) * TM + quad * 32 + lane, n_base = int64_t(tn) * TN;
+            // the first 64 residual values of this thread's row travel while the tile's last MMAs still run
+            ra.on = p.epi == 0 && p.residual != nullptr && (p.N & 7) == 0 && row0 < p.M;
+            residual_request<TN>(p, ra, row0, n_base, 0);
             bool ok = !slots[1] && mbar_wait(acc_full_bar(b), (lt >> 1) & 1);
             if (!ok && !slots[1]) { atomicExch(p.status, STATUS_TIMEOUT_EPILOGUE); slots[1] = 1; }
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
+            const uint32_t taddr = tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(b * 256);
             if constexpr (WIDE) {
-                const int64_t a_row = int64_t(tm) * TM + quad * 32 + lane;
-#pragma unroll 1
-                for (int c = 0; c < TN; c += 16) {
-                    uint32_t raw[16];
-                    tmem_ld16(tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(b * 256 + c), raw);
-                    tmem_ld_wait();
-                    float v[16];
-#pragma unroll
-                    for (int j = 0; j < 16; j++) v[j] = __uint_as_float(raw[j]);
-                    epilogue_store<TOut>(p, v, a_row, int64_t(tn) * TN + c);
-                }
-            } else
-#pragma unroll 1
-            for (int m = 0; m < 2; m++) {
-                const int64_t a_row = int64_t(tm) * PBM + m * 128 + quad * 32 + lane;
-#pragma unroll 1
-                for (int c = 0; c < PBN; c += 16) {
-                    uint32_t raw[16];
-                    tmem_ld16(tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(b * 256 + m * 128 + c), raw);
-                    tmem_ld_wait();
-                    float v[16];
-#pragma unroll
-                    for (int j = 0; j < 16; j++) v[j] = __uint_as_float(raw[j]);
-                    epilogue_store<TOut>(p, v, a_row, int64_t(tn) * PBN + c);
-                }
+                drain_row<TOut, TN>(p, taddr, row0, n_base, ra);
+            } else {
+                drain_row<TOut, TN>(p, taddr, row0, n_base, ra);
+                const int64_t row1 = row0 + 128;
+                ra.on = p.epi == 0 && p.residual != nullptr && (p.N & 7) == 0 && row1 < p.M;
+                residual_request<TN>(p, ra, row1, n_base, 0);
+                drain_row<TOut, TN>(p, taddr + 128u, row1, n_base, ra);
             }
             tc_fence_before();
             __syncwarp();
@@ -927,7 +981,7 @@ int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const GemmPa
         if (e != cudaSuccess) return ib::fail(IB_ERR_CUDA, "gemm_tc: cannot set shared memory size: %s", cudaGetErrorString(e));
         configured = true;
     }
-    const int64_t tiles = WIDE ? ((p.rows_a + 127) / 128) * ((p.rows_b + 255) / 256) : ((p.rows_a + PBM - 1) / PBM) * ((p.rows_b + PBN - 1) / PBN);
+    const int64_t tiles = WIDE ? ((p.rows_a + 127) / 128) * ((p.rows_b + PBN - 1) / PBN) : ((p.rows_a + PBM - 1) / PBM) * ((p.rows_b + PBN - 1) / PBN);
     const unsigned ctas = unsigned(tiles < sm_count ? tiles : sm_count);
     return ib::launch("gemm_tc", gemm_tc_persistent_kernel<PBN, WIDE, TOut>, dim3(ctas), dim3(NUM_THREADS), size_t(P_SMEM_BYTES), stream, 1u, ma, mb, p);
 }
@@ -1000,14 +1054,25 @@ IB_EXPORT int ib_gemm_tc_plan(int64_t M, int64_t N, int64_t K, int sm_count, int
     // Many tokens and enough 256 x 128 tiles to occupy the GPU: the persistent kernel (bn = 256 stands for it).
     static const bool persistent_on = [] { const char* e = getenv("INFER_B200_GEMM_PERSISTENT"); return !(e && e[0] == '0'); }();
     if (!*swap && s == 1 && persistent_on && sm_count > 0) {
-        // share of the SMs at work over the rounds a tile width needs; the narrower tile moves a tenth more operand
-        // bytes per flop. bn = 512 stands for the 128 x 256 tile, 256 for 256 x 128, 192 for 256 x 96.
-        const int64_t tm = (M + PBM - 1) / PBM;
-        const int64_t t128 = tm * ((N + 127) / 128), t96 = tm * ((N + 95) / 96);
-        auto fill = [&](int64_t t) { return double(t) / double(((t + sm_count - 1) / sm_count) * sm_count); };
-        // one M=128 x N=256 MMA per k-step instead of two of N=128 (measured: gate/up 96 -> 93 us, q/k/v 15.3 -> 13.5 us)
+        // bn = 512, 384, 352 stand for tiles of 128 tokens x 256, 192, 176 features (one MMA per k-step), 256 for
+        // 256 x 128 (two MMAs). Among the 128-row tiles the one with the least estimated time wins: rounds over the
+        // SMs times (width + 224), the constant being what a tile costs beside its columns (operand rows of the
+        // A side, the exposed epilogue). A matrix of 1536 features gets 16 x 9 tiles of 176 columns for 148 SMs
+        // (measured at 2,048 tokens: down 60 us against 70 with 256 columns, o 21 against 25).
+        const int64_t tm = (M + PBM - 1) / PBM, tm128 = (M + 127) / 128;
+        const int64_t t128 = tm * ((N + 127) / 128);
         static const bool wide_on = [] { const char* e = getenv("INFER_B200_GEMM_WIDE"); return !(e && e[0] == '0'); }();
-        if (t128 * 2 >= sm_count) *bn = fill(t96) * 0.9 > fill(t128) ? 192 : (wide_on ? 512 : 256);
+        if (t128 * 2 >= sm_count) {
+            *bn = 256;
+            if (wide_on) {
+                int64_t best = -1;
+                for (int width : {256, 192, 176}) {
+                    const int64_t t = tm128 * ((N + width - 1) / width);
+                    const int64_t cost = ((t + sm_count - 1) / sm_count) * (width + 224);
+                    if (best < 0 || cost < best) { best = cost; *bn = 2 * width; }
+                }
+            }
+        }
         // pairs of CTAs on 256 x 256 tiles where those keep most pairs busy: correct, but measured no faster than the
         // one-CTA 128 x 256 tiles (gate/up 97 against 93 us), so only with INFER_B200_GEMM_PAIR=1
         static const bool pair_on = [] { const char* e = getenv("INFER_B200_GEMM_PAIR"); return e && e[0] == '1'; }();
@@ -1030,9 +1095,9 @@ IB_EXPORT int ib_gemm_tc(const void* x, const void* w, const float* bias, const 
     if (M <= 0 || N <= 0) return IB_OK;
     if (K <= 0 || K % 8) return ib::fail(IB_ERR_ARG, "gemm_tc: K = %lld must be a positive multiple of 8", (long long)K);
     if ((uintptr_t(x) & 15) || (uintptr_t(w) & 15)) return ib::fail(IB_ERR_ARG, "gemm_tc: operand bases must be 16-byte aligned");
-    if (bn != 16 && bn != 32 && bn != 64 && bn != 128 && bn != 192 && bn != 256 && bn != 512 && bn != 1024)
-        return ib::fail(IB_ERR_ARG, "gemm_tc: bn must be 16, 32, 64, 128, or 192, 256, 512 (the persistent kernel: 96 columns, 128 columns, one 256-wide MMA) or 1024 (CTA pairs)");
-    if (bn >= 192 && (swap || splits > 1)) return ib::fail(IB_ERR_ARG, "gemm_tc: the persistent kernel takes the plain mapping without K slices");
+    if (bn != 16 && bn != 32 && bn != 64 && bn != 128 && bn != 256 && bn != 352 && bn != 384 && bn != 512 && bn != 1024)
+        return ib::fail(IB_ERR_ARG, "gemm_tc: bn must be 16, 32, 64, 128, or 256 (the persistent kernel on 256 x 128 tiles), 352, 384, 512 (on 128 x 176, 128 x 192, 128 x 256 with one MMA per k-step) or 1024 (CTA pairs)");
+    if (bn >= 256 && (swap || splits > 1)) return ib::fail(IB_ERR_ARG, "gemm_tc: the persistent kernel takes the plain mapping without K slices");
     if (!status) return ib::fail(IB_ERR_ARG, "gemm_tc: a status word is required");
     if (epi != 0 && epi != 2) return ib::fail(IB_ERR_ARG, "gemm_tc: unknown epilogue %d", epi);
     if (epi == 2 && (N % 16 || bias || residual)) return ib::fail(IB_ERR_ARG, "gemm_tc: the SwiGLU epilogue needs N %% 16 == 0 and no bias or residual");
@@ -1059,11 +1124,11 @@ IB_EXPORT int ib_gemm_tc(const void* x, const void* w, const float* bias, const 
     const bool f32 = out_dtype == IB_F32;
     if (!f32 && out_dtype != IB_BF16) return ib::fail(IB_ERR_ARG, "gemm_tc: unknown output dtype %d", out_dtype);
     CUtensorMap ma, mb;
-    if (bn >= 192) {
-        const int pbn = bn == 192 ? 96 : 128;
-        int rc = get_map(x, p.rows_a, K, (bn == 512 || bn == 1024) ? 128 : PBM, &ma);
+    if (bn >= 256) {
+        const bool wide = bn >= 352 && bn <= 512;
+        int rc = get_map(x, p.rows_a, K, (wide || bn == 1024) ? 128 : PBM, &ma);
         if (rc) return rc;
-        rc = get_map(w, p.rows_b, K, bn == 1024 ? 128 : (bn == 512 ? 256 : pbn), &mb);
+        rc = get_map(w, p.rows_b, K, bn == 1024 ? 128 : (wide ? bn / 2 : 128), &mb);
         if (rc) return rc;
         static int sms = 0;
         if (!sms) {
@@ -1073,11 +1138,10 @@ IB_EXPORT int ib_gemm_tc(const void* x, const void* w, const float* bias, const 
         }
         p.splits = 1; p.cluster_split = 0; p.stages = PSTAGES;
         if (bn == 1024) return f32 ? launch_pair<float>(ma, mb, p, sms, stream) : launch_pair<bf16>(ma, mb, p, sms, stream);
-        if (bn == 512) {
-            return f32 ? launch_persistent<128, true, float>(ma, mb, p, sms, stream) : launch_persistent<128, true, bf16>(ma, mb, p, sms, stream);
-        }
-        if (pbn == 128) return f32 ? launch_persistent<128, false, float>(ma, mb, p, sms, stream) : launch_persistent<128, false, bf16>(ma, mb, p, sms, stream);
-        return f32 ? launch_persistent<96, false, float>(ma, mb, p, sms, stream) : launch_persistent<96, false, bf16>(ma, mb, p, sms, stream);
+        if (bn == 512) return f32 ? launch_persistent<256, true, float>(ma, mb, p, sms, stream) : launch_persistent<256, true, bf16>(ma, mb, p, sms, stream);
+        if (bn == 384) return f32 ? launch_persistent<192, true, float>(ma, mb, p, sms, stream) : launch_persistent<192, true, bf16>(ma, mb, p, sms, stream);
+        if (bn == 352) return f32 ? launch_persistent<176, true, float>(ma, mb, p, sms, stream) : launch_persistent<176, true, bf16>(ma, mb, p, sms, stream);
+        return f32 ? launch_persistent<128, false, float>(ma, mb, p, sms, stream) : launch_persistent<128, false, bf16>(ma, mb, p, sms, stream);
     }
     int rc = get_map(swap ? w : x, p.rows_a, K, BM, &ma);
     if (rc) return rc;

@@ -20,10 +20,10 @@ SIZES = [
     (2048, 2048, 1536),    # plain, prefill-sized
     (130, 301, 96),        # plain, odd N
     (2, 320, 96),          # swap, K = 1.5 k-blocks
-    (1100, 3000, 520),     # persistent (256 x 128 tiles, two accumulators): ragged M and N, K tail, several tiles per CTA
+    (1100, 3000, 520),     # persistent (128 x 256 tiles, two accumulators): ragged M and N, K tail, several tiles per CTA
     (4000, 4100, 72),      # persistent, many tiles of two k-blocks: the accumulators alternate quickly
-    (1800, 1500, 136),     # persistent with 96-column tiles (fills the SMs better than 128), ragged M and N
-    (2048, 1536, 1536),    # persistent with 96-column tiles, the model's o product at prefill
+    (1800, 1500, 136),     # persistent with 128 x 176 tiles (they fill the SMs better than 256 columns), ragged M and N
+    (2048, 1536, 1536),    # persistent with 128 x 176 tiles, the model's o product at prefill
 ]
 
 
@@ -107,6 +107,33 @@ def test_gemm_tc_cta_pairs(M, N, K):
     r2 = res.clone()
     fast_ops.gemm_tc(x, w, None, r2, torch.float32, out=r2, plan=plan)
     assert ((r2 - _ref(x, w, None, res)).abs() / cond).max().item() < 2e-6
+    assert st.status.item() == 0
+
+
+@pytest.mark.parametrize("code", [256, 352, 384, 512])
+@pytest.mark.parametrize("M,N,K", [(2048, 1536, 1536), (1100, 3000, 520), (300, 260, 72)])
+def test_gemm_tc_wide_tiles(M, N, K, code):
+    """The persistent kernel's tiles chosen by hand: 256 x 128 (plan code 256, two MMAs per k-step) and 128 rows by 176,
+    192 and 256 columns (codes 352, 384, 512: one MMA): exact and ragged tiles, a K tail, fewer tiles than SMs; bias, residual in place, SwiGLU."""
+    from infer_b200 import fast_ops
+    g = torch.Generator(device=DEV).manual_seed(M + N + K + code)
+    x = torch.randn(M, K, device=DEV, generator=g).bfloat16()
+    w = (torch.randn(N, K, device=DEV, generator=g) * 0.05).bfloat16()
+    bias = torch.randn(N, device=DEV, generator=g)
+    res = torch.randn(M, N, device=DEV, generator=g)
+    cond = x.float().abs() @ w.float().abs().T + 1.0
+    st = fast_ops.device_state(DEV)
+    st.status.zero_()
+    plan = (0, code, 1, 0, 0)
+    got = fast_ops.gemm_tc(x, w, bias, None, torch.float32, plan=plan)
+    assert ((got - _ref(x, w, bias, None)).abs() / cond).max().item() < 2e-6
+    r2 = res.clone()
+    fast_ops.gemm_tc(x, w, None, r2, torch.float32, out=r2, plan=plan)
+    assert ((r2 - _ref(x, w, None, res)).abs() / cond).max().item() < 2e-6
+    if N % 16 == 0:
+        act = fast_ops.gemm_tc(x, w, out_dtype=torch.bfloat16, plan=plan, swiglu=True)
+        same = fast_ops.gemm_tc(x, w, out_dtype=torch.bfloat16, plan=(0, 128, 1, 0, 0), swiglu=True)
+        assert torch.equal(act, same)
     assert st.status.item() == 0
 
 
