@@ -3,13 +3,14 @@
 //
 // Two kernels share one launch call; each segment (a request's tokens in this step) goes to one of them:
 //
-//  decode  (segments of ONE token)   grid (segments, kv heads, splits). The query heads that share a kv head are
+//  decode  (segments of ONE token)   grid (slices, kv heads, segments). The query heads that share a kv head are
 //          the rows of one 16-row tile, so a key or value is read once for the whole group. The key range is cut
-//          into `splits` slices (flash-decoding); inside a CTA each of the 4 warps walks its own pages (a page is a
+//          into slices (flash-decoding); inside a CTA each of the 4 warps walks its own pages (a page is a
 //          contiguous 16 x head_dim block per kv head) through a 3-stage cp.async ring, with its own running
-//          maximum, sum and output, merged in shared memory at the end. With more than one slice the CTA stores
-//          (max, sum, unnormalised output) to the workspace, and the CTA that arrives last at the (segment, kv head)
-//          counter adds the slices in ascending order and writes the result.
+//          maximum, sum and output, merged in shared memory at the end. Up to 8 slices form a thread-block cluster
+//          and meet through distributed shared memory; for long contexts at small batches several clusters share a
+//          (segment, kv head): each leaves (max, sum, unnormalised output) in the workspace and the CTA that arrives
+//          last at the (segment, kv head) counter adds the clusters in ascending order and writes the result.
 //
 //  prefill (segments of 2 or more tokens)   grid (heads, query tiles from the last to the first, segments). 64 queries of one head per CTA,
 //          16 per warp; keys in tiles of 64 (4 pages) aligned to absolute multiples of 64, double-buffered with
@@ -42,7 +43,9 @@ constexpr int KS = HD / 16;                     // k-steps over the head dimensi
 constexpr float LOG2E = 1.4426950408889634f;
 
 constexpr int DEC_WARPS = 4, DEC_STAGES = 3;
-constexpr int MAX_SPLITS = 8;                   // slices of the key range per (segment, kv head) = cluster size
+constexpr int MAX_SPLITS = 8;                   // slices of the key range per cluster
+constexpr int MAX_SUPER = 32;                   // clusters per (segment, kv head)
+constexpr int WS_STRIDE = 16 * HD + 32;         // floats a cluster leaves in the workspace: [16][HD] output, [16][2] max and sum
 constexpr int DEC_STAGE_BYTES = 2 * PAGE * ROW_BYTES;                       // K page + V page
 constexpr int DEC_SMEM = DEC_WARPS * DEC_STAGES * DEC_STAGE_BYTES;
 constexpr int MO_PITCH = HD + 8;                // floats between rows of a warp's partial output: 8-byte stores of a half-warp hit 32 banks
@@ -62,7 +65,7 @@ struct AttnParams {
     int n_heads, n_kv, group, window;
     float scale_log2;                      // softmax scale * log2(e)
     int64_t n_pages;
-    int n_splits;
+    int n_splits, n_super;
     float* workspace; unsigned int* counters; int* status;
 };
 
@@ -211,8 +214,12 @@ attn_decode_kernel(const AttnParams p) {
     IB_DT(0);
     const bool early = FUSED && p.write_cache;
     if (!early) ib::pdl_wait();
-    const int split = blockIdx.x, kvh = blockIdx.y, seg = blockIdx.z;
-    const int n_splits = gridDim.x;
+    // blockIdx.x = super-slice * cluster size + rank in the cluster: the key range is cut into gridDim.x slices, the
+    // n_splits slices of a cluster meet through distributed shared memory, and clusters (n_super > 1: long contexts at
+    // small batches, where one cluster per (segment, kv head) would leave most SMs idle) through the workspace
+    const int n_splits = p.n_splits;
+    const int split = blockIdx.x & (n_splits - 1), slice = blockIdx.x, kvh = blockIdx.y, seg = blockIdx.z;
+    const int n_slices = gridDim.x;
     const int t = p.seg_start[seg];
     const bool is_decode = p.seg_start[seg + 1] - t == 1;         // uniform over the cluster
     if (!is_decode) return;
@@ -220,8 +227,8 @@ attn_decode_kernel(const AttnParams p) {
     const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
     const int first_page = lo / PAGE, last_page = pos / PAGE;
     const int n_pg = last_page - first_page + 1;
-    const int pps = (n_pg + n_splits - 1) / n_splits;
-    const int pg_begin = min(last_page + 1, first_page + split * pps), pg_end = min(last_page + 1, pg_begin + pps);
+    const int pps = (n_pg + n_slices - 1) / n_slices;
+    const int pg_begin = min(last_page + 1, first_page + slice * pps), pg_end = min(last_page + 1, pg_begin + pps);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t4 = lane & 3;
     const int* table = p.block_table + int64_t(seg) * p.max_blocks;
@@ -464,6 +471,8 @@ attn_decode_kernel(const AttnParams p) {
     }
     cl.sync();
     IB_DT(23);
+    const bool last_level = p.n_super == 1;
+    float* ws = last_level ? nullptr : p.workspace + ((int64_t(seg) * p.n_kv + kvh) * p.n_super + blockIdx.x / n_splits) * WS_STRIDE;
     for (int j = threadIdx.x; j < share; j += DEC_WARPS * 32) {
         const int idx = split * share + j;
         if (idx >= total) break;
@@ -481,9 +490,70 @@ attn_decode_kernel(const AttnParams p) {
                 acc += recv_o[r * share + j] * w;
             }
         }
-        out_row[idx] = __float2bfloat16_rn(L > 0.0f ? acc / L : 0.0f);
+        if (last_level) out_row[idx] = __float2bfloat16_rn(L > 0.0f ? acc / L : 0.0f);
+        else ws[idx] = acc;                              // unnormalised, relative to this cluster's maximum of the row
     }
     IB_DT(24);
+    if (last_level) return;
+    // Clusters beside one another: each leaves its unnormalised share and, per head, its maximum and sum in the
+    // workspace; the CTA that arrives last at the (segment, kv head) counter adds the clusters in index order (the
+    // result does not depend on who is last) and leaves the counter at zero for the next launch.
+    if (split == 0 && threadIdx.x < G) {
+        const int row = threadIdx.x;
+        float M = -INFINITY, L = 0.0f;
+#pragma unroll
+        for (int r = 0; r < MAX_SPLITS; r++) if (r < n_splits) M = fmaxf(M, recv_ml[r][row][0]);
+        const float Ms = M == -INFINITY ? 0.0f : M;
+#pragma unroll
+        for (int r = 0; r < MAX_SPLITS; r++) if (r < n_splits) L += recv_ml[r][row][1] * exp2f(recv_ml[r][row][0] - Ms);
+        ws[16 * HD + row * 2] = M;
+        ws[16 * HD + row * 2 + 1] = L;
+    }
+    __shared__ int is_last;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned int* counter = p.counters + seg * p.n_kv + kvh;
+        const unsigned int prev = atomicAdd(counter, 1u);
+        is_last = prev == gridDim.x - 1u;
+        if (is_last) *counter = 0u;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    const float* all = p.workspace + (int64_t(seg) * p.n_kv + kvh) * p.n_super * WS_STRIDE;
+    for (int idx = threadIdx.x; idx < total; idx += DEC_WARPS * 32) {
+        const int row = idx / HD;
+        const float* ml = all + 16 * HD + row * 2;
+        float M = -INFINITY;
+        // four clusters' values are requested together: one round trip to L2 per four clusters, not three per cluster
+        for (int c0 = 0; c0 < p.n_super; c0 += 4) {
+            float mm[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) mm[u] = c0 + u < p.n_super ? __ldcg(ml + (c0 + u) * WS_STRIDE) : -INFINITY;
+#pragma unroll
+            for (int u = 0; u < 4; u++) M = fmaxf(M, mm[u]);
+        }
+        const float Ms = M == -INFINITY ? 0.0f : M;
+        float acc = 0.0f, L = 0.0f;
+        for (int c0 = 0; c0 < p.n_super; c0 += 4) {
+            float mm[4], ll[4], vv[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const bool in = c0 + u < p.n_super;
+                mm[u] = in ? __ldcg(ml + (c0 + u) * WS_STRIDE) : -INFINITY;
+                ll[u] = in ? __ldcg(ml + (c0 + u) * WS_STRIDE + 1) : 0.0f;
+                vv[u] = in ? __ldcg(all + (c0 + u) * WS_STRIDE + idx) : 0.0f;
+            }
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const float w = exp2f(mm[u] - Ms);
+                L += ll[u] * w;
+                acc += vv[u] * w;
+            }
+        }
+        out_row[idx] = __float2bfloat16_rn(L > 0.0f ? acc / L : 0.0f);
+    }
 }
 
 // ================================================================================================ prefill
@@ -606,7 +676,11 @@ IB_EXPORT int ib_attention_decode_trace(long long* host) {
 
 namespace {
 
-int check_common(int n_segments, int n_heads, int n_kv, int head_dim, int page_size, int n_splits, const int* status) {
+int check_common(int n_segments, int n_heads, int n_kv, int head_dim, int page_size, int n_splits, const int* status,
+                 int n_super = 1, const float* workspace = nullptr, const unsigned int* counters = nullptr) {
+    if (n_super < 1 || n_super > MAX_SUPER) return ib::fail(IB_ERR_ARG, "attention_fast: 1 to %d clusters per (segment, kv head), got %d", MAX_SUPER, n_super);
+    if (n_super > 1 && (n_splits != MAX_SPLITS || !workspace || !counters))
+        return ib::fail(IB_ERR_ARG, "attention_fast: several clusters per (segment, kv head) need 8 slices each, a workspace and counters");
     if (head_dim != HD) return ib::fail(IB_ERR_ARG, "attention_fast: built for head_dim %d, called with %d", HD, head_dim);
     if (page_size != PAGE) return ib::fail(IB_ERR_ARG, "attention_fast: pages must hold %d positions, got %d", PAGE, page_size);
     if (n_kv <= 0 || n_heads % n_kv) return ib::fail(IB_ERR_ARG, "attention_fast: heads %d not a multiple of kv heads %d", n_heads, n_kv);
@@ -633,23 +707,26 @@ int configure() {
 
 // Attention for every segment of a step. q/out [tokens, heads*HD] bfloat16; caches [pages, kv_heads, 16, HD] bfloat16;
 // seg_start [S+1], seg_pos0 [S], block_table [S, max_blocks] int32. has_decode / max_q_len tell which kernels to
-// launch (a kernel skips segments of the other kind). n_splits: slices per (segment, kv head) of the decode kernel,
-// 1, 2, 4 or 8 (they form a thread-block cluster).
+// launch (a kernel skips segments of the other kind). n_splits: slices of the decode kernel's cluster, 1, 2, 4 or 8;
+// n_super: clusters per (segment, kv head), more than one only with 8 slices each, a workspace of
+// segments * kv_heads * n_super * (16 * HD + 32) floats and segments * kv_heads zeroed counters (left at zero).
 IB_EXPORT int ib_attention_fast(const void* q, const void* k_cache, const void* v_cache, void* out, const int* block_table,
                                 int max_blocks, const int* seg_start, const int* seg_pos0, int n_segments, int n_heads,
                                 int n_kv, int head_dim, int page_size, int window, float scale, int64_t n_pages,
-                                int has_decode, int max_q_len, int n_splits, int* status, cudaStream_t stream) {
+                                int has_decode, int max_q_len, int n_splits, int* status, cudaStream_t stream,
+                                int n_super, float* workspace, unsigned int* counters) {
     if (n_segments <= 0) return IB_OK;
-    int rc = check_common(n_segments, n_heads, n_kv, head_dim, page_size, n_splits, status);
+    int rc = check_common(n_segments, n_heads, n_kv, head_dim, page_size, n_splits, status, n_super, workspace, counters);
     if (rc) return rc;
     AttnParams p = {};
     p.q = (const bf16*)q; p.k_cache = (const bf16*)k_cache; p.v_cache = (const bf16*)v_cache; p.out = (bf16*)out;
     p.block_table = block_table; p.max_blocks = max_blocks; p.seg_start = seg_start; p.seg_pos0 = seg_pos0;
     p.n_heads = n_heads; p.n_kv = n_kv; p.group = n_heads / n_kv; p.window = window;
     p.scale_log2 = scale * LOG2E; p.n_pages = n_pages; p.n_splits = n_splits; p.status = status;
+    p.n_super = n_super; p.workspace = workspace; p.counters = counters;
     if ((rc = configure())) return rc;
     if (has_decode) {
-        const dim3 grid{unsigned(n_splits), unsigned(n_kv), unsigned(n_segments)};
+        const dim3 grid{unsigned(n_splits * n_super), unsigned(n_kv), unsigned(n_segments)};
         rc = ib::launch("attention_fast (decode)", attn_decode_kernel<false>, grid, dim3(DEC_WARPS * 32), size_t(DEC_SMEM), stream,
                         unsigned(n_splits), p);
         if (rc) return rc;
@@ -671,9 +748,9 @@ IB_EXPORT int ib_attention_decode_fused(const void* qkv, const float* cos_t, con
                                         const int* seg_pos0, int n_segments, int n_heads, int n_kv, int head_dim,
                                         int page_size, int window, float scale, int64_t n_pages, int write_cache,
                                         int n_splits, int* status, const void* prefetch, int64_t prefetch_bytes,
-                                        cudaStream_t stream) {
+                                        cudaStream_t stream, int n_super, float* workspace, unsigned int* counters) {
     if (n_segments <= 0) return IB_OK;
-    int rc = check_common(n_segments, n_heads, n_kv, head_dim, page_size, n_splits, status);
+    int rc = check_common(n_segments, n_heads, n_kv, head_dim, page_size, n_splits, status, n_super, workspace, counters);
     if (rc) return rc;
     if ((HD / 2) % 16) return ib::fail(IB_ERR_ARG, "attention_decode_fused: head_dim/2 must be a multiple of 16, head_dim is %d", HD);
     if (!cos_t || !sin_t) return ib::fail(IB_ERR_ARG, "attention_decode_fused: rotation tables are required");
@@ -685,8 +762,9 @@ IB_EXPORT int ib_attention_decode_fused(const void* qkv, const float* cos_t, con
     p.block_table = block_table; p.max_blocks = max_blocks; p.seg_start = seg_start; p.seg_pos0 = seg_pos0;
     p.n_heads = n_heads; p.n_kv = n_kv; p.group = n_heads / n_kv; p.window = window;
     p.scale_log2 = scale * LOG2E; p.n_pages = n_pages; p.n_splits = n_splits; p.status = status;
+    p.n_super = n_super; p.workspace = workspace; p.counters = counters;
     if ((rc = configure())) return rc;
-    const dim3 grid{unsigned(n_splits), unsigned(n_kv), unsigned(n_segments)};
+    const dim3 grid{unsigned(n_splits * n_super), unsigned(n_kv), unsigned(n_segments)};
     return ib::launch("attention_decode_fused", attn_decode_kernel<true>, grid, dim3(DEC_WARPS * 32), size_t(DEC_SMEM), stream,
                       unsigned(n_splits), p);
 }

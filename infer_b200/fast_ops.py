@@ -27,12 +27,14 @@ class DeviceState:
         self.sm_count = torch.cuda.get_device_properties(device).multi_processor_count
         self._workspace = torch.empty(0, dtype=torch.float32, device=device)
         self._counters = torch.zeros(4096, dtype=torch.int32, device=device)
+        self._retired = []
         self.grid_barrier = torch.zeros(4, dtype=torch.int32, device=device)    # words of linear_chain's grid barrier
 
     def workspace(self, n_floats: int) -> torch.Tensor:
         if self._workspace.numel() < n_floats:
             if torch.cuda.is_current_stream_capturing():
                 raise KernelError("the kernel workspace must be sized before a CUDA graph is captured")
+            self._retired.append(self._workspace)        # captured graphs may still point at it
             self._workspace = torch.empty(max(n_floats, 1 << 22), dtype=torch.float32, device=self.device)
         return self._workspace
 
@@ -40,6 +42,7 @@ class DeviceState:
         if self._counters.numel() < n:
             if torch.cuda.is_current_stream_capturing():
                 raise KernelError("the kernel counters must be sized before a CUDA graph is captured")
+            self._retired.append(self._counters)
             self._counters = torch.zeros(max(n, 4096), dtype=torch.int32, device=self.device)
         return self._counters
 
@@ -208,15 +211,33 @@ def attention_supported(n_heads: int, n_kv: int, head_dim: int, page_size: int) 
     return head_dim % 16 == 0 and 16 <= head_dim <= 128 and page_size == 16 and n_heads // n_kv <= 16
 
 
-def _decode_splits(st, n_decode: int, n_kv: int, visible: int) -> int:
-    """Slices per (segment, kv head): a power of two up to 8 (they form a cluster), enough CTAs for about one per SM,
-    and at least 8 pages (two per warp) in a slice."""
+ATTENTION_MAX_CLUSTERS = 32       # clusters of 8 slices per (segment, kv head), for long contexts at small batches
+ATTENTION_CLUSTER_PAGES = 16      # pages a slice keeps at least when a (segment, kv head) gets several clusters
+ATTENTION_CLUSTER_FROM = 96       # ... which it gets when one cluster's slices would each walk at least this many pages
+
+
+def _decode_splits(st, n_decode: int, n_kv: int, visible: int):
+    """(slices per cluster, clusters per (segment, kv head)). Slices: a power of two up to 8, enough CTAs for about
+    one per SM, and at least 8 pages (two per warp) in a slice. Clusters: more than one only for long contexts (the
+    second level costs about 5 us per layer: measured at batch 8 it loses at 8,192 tokens, 1.56 against 1.44 ms per
+    step, and wins at 30,000, 2.50 against 2.78; at batch 1 and 30,000 tokens 1.41 against 2.21), then as many as keep
+    16 pages (four per warp) in a slice, up to two CTAs per SM."""
     units = max(1, n_decode * n_kv)
     pages = max(1, -(-visible // 16))
     n = 1
     while n < 8 and units * n < st.sm_count and pages // (2 * n) >= 8:
         n *= 2
-    return n
+    clusters = 1
+    if n == 8 and pages >= 8 * ATTENTION_CLUSTER_FROM:
+        clusters = max(1, min(pages // (8 * ATTENTION_CLUSTER_PAGES), (2 * st.sm_count) // (units * 8), ATTENTION_MAX_CLUSTERS))
+    return n, clusters
+
+
+def _decode_scratch(st, n_segments: int, n_kv: int, head_dim: int, clusters: int):
+    """Workspace and counters for several clusters per (segment, kv head); (None, None) for one."""
+    if clusters <= 1:
+        return None, None
+    return st.workspace(n_segments * n_kv * clusters * (16 * head_dim + 32)), st.counters(n_segments * n_kv)
 
 
 # The prefill kernel on tcgen05 / tensor memory (attention_tc.cu) serves head sizes 64 and 128; INFER_B200_ATTN_TC=0
@@ -228,7 +249,7 @@ ATTENTION_TC_HEAD_DIMS = (64, 128)
 def attention_fast(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
                    seg_start: torch.Tensor, seg_pos0: torch.Tensor, n_heads: int, n_kv: int, head_dim: int,
                    window: Optional[int], scale: float, has_decode: bool, max_q_len: int, max_ctx_len: int,
-                   n_decode: Optional[int] = None, n_splits: Optional[int] = None) -> Optional[torch.Tensor]:
+                   n_decode: Optional[int] = None, n_splits: Optional[int] = None, n_clusters: int = 1) -> Optional[torch.Tensor]:
     """Tensor-core attention of a step's segments over the paged bfloat16 cache; None if the shape is refused.
     The library is compiled for this head size at first use."""
     n_pages, ckv, page_size, chd = k_cache.shape
@@ -248,7 +269,8 @@ def attention_fast(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor
     st = device_state(q.device)
     if n_splits is None:
         visible = min(max_ctx_len, window) if window else max_ctx_len
-        n_splits = _decode_splits(st, n_decode if n_decode is not None else S, n_kv, visible) if has_decode else 1
+        n_splits, n_clusters = _decode_splits(st, n_decode if n_decode is not None else S, n_kv, visible) if has_decode else (1, 1)
+    ws, cnt = _decode_scratch(st, S, n_kv, head_dim, n_clusters)
     out = torch.empty_like(q)
     # Segments of two or more tokens go to the tcgen05 kernel where it takes the head size; one-token segments, and
     # everything else, to the mma.sync kernels (a call with max_q_len = 1 launches no prefill kernel).
@@ -262,11 +284,11 @@ def attention_fast(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor
         if not has_decode:
             return out
     f = _fn("attn", "ib_attention_fast", [c_void_p] * 5 + [c_int] + [c_void_p] * 2 + [c_int] * 6 + [c_float, c_int64] +
-            [c_int] * 3 + [c_void_p] * 2, {"IB_HEAD_DIM": head_dim})
+            [c_int] * 3 + [c_void_p] * 2 + [c_int] + [c_void_p] * 2, {"IB_HEAD_DIM": head_dim})
     _call(f, q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), block_table.data_ptr(),
           block_table.shape[1], seg_start.data_ptr(), seg_pos0.data_ptr(), S, n_heads, n_kv, head_dim, page_size,
           int(window or 0), float(scale), n_pages, int(has_decode), 1 if tc else int(max_q_len), int(n_splits),
-          st.status.data_ptr(), _stream())
+          st.status.data_ptr(), _stream(), int(n_clusters), _ptr(ws), _ptr(cnt))
     return out
 
 
@@ -278,7 +300,8 @@ def attention_decode_fused(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tens
                            v_cache: torch.Tensor, block_table: torch.Tensor, seg_start: torch.Tensor,
                            seg_pos0: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, window: Optional[int],
                            scale: float, max_ctx_len: int, write_cache: bool = True,
-                           n_splits: Optional[int] = None, prefetch: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+                           n_splits: Optional[int] = None, prefetch: Optional[torch.Tensor] = None,
+                           n_clusters: int = 1) -> Optional[torch.Tensor]:
     """Decode-only steps: rotation of q and k, the cache write of the new positions and attention in ONE kernel.
     qkv [S, (heads + 2 kv) * head_dim] packed rows with the bias added. Returns [S, heads * head_dim]."""
     n_pages, ckv, page_size, chd = k_cache.shape
@@ -300,15 +323,16 @@ def attention_decode_fused(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tens
     st = device_state(qkv.device)
     if n_splits is None:
         visible = min(max_ctx_len, window) if window else max_ctx_len
-        n_splits = _decode_splits(st, S, n_kv, visible)
+        n_splits, n_clusters = _decode_splits(st, S, n_kv, visible)
+    ws, cnt = _decode_scratch(st, S, n_kv, head_dim, n_clusters)
     out = torch.empty((S, n_heads * head_dim), dtype=torch.bfloat16, device=qkv.device)
     pf_ptr, pf_bytes = _prefetch_args(prefetch)
     f = _fn("attn", "ib_attention_decode_fused", [c_void_p] * 7 + [c_int] + [c_void_p] * 2 + [c_int] * 6 + [c_float, c_int64] +
-            [c_int] * 2 + [c_void_p] * 2 + [c_int64, c_void_p], {"IB_HEAD_DIM": head_dim})
+            [c_int] * 2 + [c_void_p] * 2 + [c_int64, c_void_p] + [c_int] + [c_void_p] * 2, {"IB_HEAD_DIM": head_dim})
     _call(f, qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
           block_table.data_ptr(), block_table.shape[1], seg_start.data_ptr(), seg_pos0.data_ptr(), S, n_heads, n_kv,
           head_dim, page_size, int(window or 0), float(scale), n_pages, int(write_cache), int(n_splits),
-          st.status.data_ptr(), pf_ptr, pf_bytes, _stream())
+          st.status.data_ptr(), pf_ptr, pf_bytes, _stream(), int(n_clusters), _ptr(ws), _ptr(cnt))
     return out
 
 

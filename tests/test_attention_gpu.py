@@ -12,7 +12,7 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
 
-def _run(heads, kv, hd, window, segs, n_splits=None, seed=0):
+def _run(heads, kv, hd, window, segs, n_splits=None, seed=0, n_clusters=1):
     """segs: list of (context length before the step, tokens in the step)."""
     from infer_b200 import fast_ops
     lens = [c + n for c, n in segs]
@@ -37,7 +37,8 @@ def _run(heads, kv, hd, window, segs, n_splits=None, seed=0):
     out = fast_ops.attention_fast(
         q.reshape(T, -1).contiguous().to(DEV), kc.to(DEV), vc.to(DEV), table.to(DEV),
         torch.tensor(seg_start, dtype=torch.int32, device=DEV), torch.tensor([c for c, _ in segs], dtype=torch.int32, device=DEV),
-        heads, kv, hd, window, scale, any(n == 1 for _, n in segs), max(n for _, n in segs), max(lens), n_splits=n_splits)
+        heads, kv, hd, window, scale, any(n == 1 for _, n in segs), max(n for _, n in segs), max(lens), n_splits=n_splits,
+        n_clusters=n_clusters)
     assert out is not None
     assert st.status.item() == 0
     got = out.cpu().double().view_as(ref)
@@ -54,6 +55,32 @@ LAYOUTS = [(12, 2, 128), (14, 2, 64), (4, 4, 16), (8, 1, 32), (5, 5, 48), (3, 1,
 @pytest.mark.parametrize("splits", [1, 4, None])
 def test_decode(heads, kv, hd, splits):
     _run(heads, kv, hd, None, [(0, 1), (1, 1), (15, 1), (16, 1), (255, 1), (1000, 1), (33, 1)], splits)
+
+
+@pytest.mark.parametrize("heads,kv,hd,clusters", [(12, 2, 128, 2), (12, 2, 128, 32), (14, 2, 64, 5), (3, 1, 96, 3)])
+def test_decode_with_several_clusters_per_kv_head(heads, kv, hd, clusters):
+    """Long contexts at small batches: several clusters of 8 slices share a (segment, kv head) and meet in the
+    workspace. Contexts that leave most slices empty (1 and 40 keys over up to 256 slices), ragged ones, and a key
+    range of thousands; twice, so that the counters must have come back to zero; the same bits whoever arrives last."""
+    from infer_b200 import fast_ops
+    segs = [(0, 1), (39, 1), (1300, 1), (2051, 1)]
+    first = _run(heads, kv, hd, None, segs, 8, seed=3, n_clusters=clusters)
+    again = _run(heads, kv, hd, None, segs, 8, seed=3, n_clusters=clusters)
+    assert torch.equal(first, again)
+    assert int(fast_ops.device_state(DEV)._counters.abs().sum()) == 0
+    _run(heads, kv, hd, 700, segs[1:], 8, seed=4, n_clusters=clusters)      # a window that begins inside a late slice
+
+
+def test_decode_cluster_count_follows_context_and_batch():
+    from infer_b200 import fast_ops
+    st = fast_ops.device_state(DEV)
+    assert fast_ops._decode_splits(st, 8, 2, 2048) == (8, 1)                # the serving shape: one cluster
+    n, c = fast_ops._decode_splits(st, 1, 2, 30000)
+    assert n == 8 and c > 1 and 2 * 8 * c <= 2 * st.sm_count and (30000 // 16) // (8 * c) >= 16
+    assert fast_ops._decode_splits(st, 8, 2, 8192) == (8, 1)                # not long enough to pay for the second level
+    assert fast_ops._decode_splits(st, 64, 2, 30000)[1] == 1                # enough requests: no second level
+    with pytest.raises(fast_ops.KernelError):
+        _run(12, 2, 128, None, [(300, 1)], 4, n_clusters=2)                 # several clusters need 8 slices each
 
 
 @pytest.mark.parametrize("heads,kv,hd", LAYOUTS)
@@ -121,7 +148,7 @@ def test_refused_shapes_fall_back():
 
 @pytest.mark.parametrize("heads,kv,hd", [(12, 2, 128), (14, 2, 64), (8, 1, 32), (3, 1, 96)])
 @pytest.mark.parametrize("window", [None, 40])
-@pytest.mark.parametrize("splits", [1, 8, None])
+@pytest.mark.parametrize("splits", [1, 8, None, (8, 3)])
 def test_fused_decode_equals_rotate_store_then_attend(heads, kv, hd, window, splits):
     """The one-kernel decode path (rotation, cache write, attention) against the plain rotate-and-store kernel
     followed by the separate attention kernel: same output, and the same cache contents afterwards."""
@@ -144,8 +171,9 @@ def test_fused_decode_equals_rotate_store_then_attend(heads, kv, hd, window, spl
     k2, v2 = kc.clone().to(DEV), vc.clone().to(DEV)
     st = fast_ops.device_state(DEV)
     st.status.zero_()
+    splits, clusters = splits if isinstance(splits, tuple) else (splits, 1)
     got = fast_ops.attention_decode_fused(qkv, cos, sin, k2, v2, table.to(DEV), seg_start, pos0, heads, kv, hd, window, scale,
-                                          max(lens), True, splits)
+                                          max(lens), True, splits, n_clusters=clusters)
     assert got is not None and st.status.item() == 0
     assert not torch.isnan(got.float()).any()
     assert (got.float() - ref.float()).abs().max() < 1e-2
