@@ -263,7 +263,7 @@ def main():
     pk = peaks()
     n_layers = args.layers
     total_steps = args.steps + args.warmup
-    eng = build_engine(n_layers, 64, args.context, 2 * total_steps + 64)
+    eng = build_engine(n_layers, max(64, args.batch), args.context, 2 * total_steps + 64)
     cfg = CONFIG
 
     if args.mode == "decode":

@@ -260,7 +260,7 @@ __device__ __forceinline__ void epilogue_store(const GemmParams& p, const float*
         const int64_t m = a_row;
         if (m >= p.M) return;
         const int64_t n0 = b_row0;
-        if (n0 + 16 <= p.N && (p.N & 7) == 0) {
+        if (ncols == 16 && n0 + 16 <= p.N && (p.N & 7) == 0) {
             float x[16];
 #pragma unroll
             for (int j = 0; j < 16; j++) x[j] = v[j] + (p.bias ? p.bias[n0 + j] : 0.0f);
@@ -295,7 +295,7 @@ __device__ __forceinline__ void epilogue_store(const GemmParams& p, const float*
 #pragma unroll
             for (int j = 0; j < 16; j++) {
                 const int64_t n = n0 + j;
-                if (n < p.N) {
+                if (n < p.N && j < ncols) {
                     float x = v[j] + (p.bias ? p.bias[n] : 0.0f);
                     if (p.residual) x += p.residual[m * p.N + n];
                     store_elem<TOut>(out + m * p.N + n, x);
@@ -1009,7 +1009,8 @@ template <int BN> int pick_stages(const GemmParams& p) {
     if (p.cluster_split) {
         // as many stages as the slice has k-blocks and no more: with the receive area a short slice then still fits
         // beside a second CTA, and its neighbours in the stream can start under it
-        const int most = C::MAX_STAGES - 2;
+        const int room = (C::SMEM_BYTES - C::SMEM_EXTRA - C::RECV_BYTES) / C::STAGE_BYTES;
+        const int most = room < C::MAX_STAGES - 2 ? room : C::MAX_STAGES - 2;
         const int want = p.kb_per_split < 2 ? 2 : p.kb_per_split;
         return want > most ? most : want;
     }
@@ -1027,13 +1028,14 @@ IB_EXPORT int ib_gemm_tc_plan(int64_t M, int64_t N, int64_t K, int sm_count, int
     if (K % 8) return ib::fail(IB_ERR_ARG, "gemm_tc: K = %lld is not a multiple of 8 (TMA needs a 16-byte row pitch)", (long long)K);
     if (M >= (1LL << 31) || N >= (1LL << 31) || K >= (1LL << 31)) return ib::fail(IB_ERR_ARG, "gemm_tc: a size exceeds 2^31");
     const int kb_total = int((K + BK - 1) / BK);
-    *swap = M <= 64 ? 1 : 0;
-    if (*swap) *bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64); else *bn = 128;
+    *swap = M <= 128 ? 1 : 0;
+    if (*swap) *bn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128)); else *bn = 128;
     const int64_t rows_a = *swap ? N : M, rows_b = *swap ? M : N;
     const int64_t tiles = ((rows_a + BM - 1) / BM) * ((rows_b + *bn - 1) / *bn);
     if ((rows_b + *bn - 1) / *bn > 65535) return ib::fail(IB_ERR_ARG, "gemm_tc: too many tiles on the grid's second axis");
     // Slices of K only when the tiles alone leave most of the GPU idle.
     int s = 1;
+    bool cluster = false;                                         // (plain mapping) the slices form a cluster
     if (sm_count > 0 && tiles * 2 < sm_count) {
         if (*swap) {
             // decode: the slices of a tile form a cluster (at most 8 CTAs) and are added through distributed shared
@@ -1046,6 +1048,14 @@ IB_EXPORT int ib_gemm_tc_plan(int64_t M, int64_t N, int64_t K, int sm_count, int
             s = int((sm_count + tiles - 1) / tiles);
             if (s > 16) s = 16;
             if (s > kb_total / 4) s = kb_total / 4 > 0 ? kb_total / 4 : 1;
+            // 2, 4 or 8 slices meet in the cluster's shared memory like those of the swapped mapping (the most that
+            // leaves at most a quarter of the CTAs to a second round)
+            // (unless the tiles are so few that even 8 slices each leave half of the GPU idle: then up to 16 through
+            // the workspace)
+            for (int c = 8; c >= 2 && tiles * 16 > sm_count; c /= 2) {
+                const int kper = (kb_total + c - 1) / c;
+                if (c <= s * 2 && tiles * c <= sm_count + sm_count / 4 && kper >= 2 && (kb_total + kper - 1) / kper == c) { s = c; cluster = true; break; }
+            }
         }
     }
     const int per = (kb_total + s - 1) / s;
@@ -1079,8 +1089,8 @@ IB_EXPORT int ib_gemm_tc_plan(int64_t M, int64_t N, int64_t K, int sm_count, int
         const int64_t t256 = tm * ((N + 255) / 256), pairs = sm_count / 2;
         if (pair_on && *bn >= 256 && pairs > 0 && double(t256) / double(((t256 + pairs - 1) / pairs) * pairs) >= 0.8) *bn = 1024;
     }
-    *workspace_floats = (s > 1 && !*swap) ? int64_t(s) * tiles * BM * (*bn) : 0;
-    *n_counters = (s > 1 && !*swap) ? tiles : 0;
+    *workspace_floats = (s > 1 && !*swap && !cluster) ? int64_t(s) * tiles * BM * (*bn) : 0;
+    *n_counters = (s > 1 && !*swap && !cluster) ? tiles : 0;
     return IB_OK;
 }
 
@@ -1113,8 +1123,8 @@ IB_EXPORT int ib_gemm_tc(const void* x, const void* w, const float* bias, const 
     p.kb_per_split = (p.kb_total + splits - 1) / splits;
     p.splits = (p.kb_total + p.kb_per_split - 1) / p.kb_per_split;
     p.cluster_split = (p.splits > 1 && !workspace) ? 1 : 0;
-    if (p.cluster_split && (!swap || p.splits > 8))
-        return ib::fail(IB_ERR_ARG, "gemm_tc: split-K without a workspace takes the swapped mapping and at most 8 slices");
+    if (p.cluster_split && (p.splits > 8 || (!swap && (BM % p.splits || (BM / p.splits) % 16))))
+        return ib::fail(IB_ERR_ARG, "gemm_tc: split-K without a workspace takes at most 8 slices, in the plain mapping 2, 4 or 8 (whole 16-column chunks per owner)");
     if (p.splits > 1 && !p.cluster_split && !counters) return ib::fail(IB_ERR_ARG, "gemm_tc: split-K through the workspace needs counters");
     p.bias = bias; p.residual = residual; p.out = out;
     p.workspace = workspace; p.counters = counters; p.status = status;

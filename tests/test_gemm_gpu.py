@@ -14,8 +14,14 @@ SIZES = [
     (17, 300, 520),        # swap, bn 32, ragged N, K tail (520 = 8*64 + 8)
     (64, 1536, 8960),      # swap, bn 64, long K, split-K
     (5, 301, 80),          # swap, odd N (scalar stores), K < 128
-    (65, 96, 224),         # plain, one ragged tile each way, K tail
-    (128, 128, 128),       # plain, exact tiles
+    (65, 96, 224),         # swap, bn 128, one ragged tile each way, K tail
+    (128, 128, 128),       # swap, bn 128, exact tiles
+    (100, 1536, 8960),     # swap, bn 128, long K in 8 slices that push 16 columns each to their owners
+    (128, 2048, 1536),     # swap, bn 128, three k-blocks per slice
+    (129, 128, 128),       # plain, the first size beyond the swapped mapping
+    (200, 300, 4096),      # plain, 6 tiles: 16 slices of K through the workspace, summed by the CTA that arrives last
+    (256, 1536, 8960),     # plain, 24 tiles: 4 slices of K as a cluster
+    (400, 2048, 1536),     # plain, 64 tiles: 2 slices of K as a cluster, three-stage ring wraps
     (300, 1000, 1536),     # plain, ragged M and N
     (2048, 2048, 1536),    # plain, prefill-sized
     (130, 301, 96),        # plain, odd N
@@ -176,11 +182,11 @@ def test_skinny_matches_plain(M, N, K, bulk):
     assert torch.equal(one, fast_ops.linear_skinny(x, w, bias, None, torch.float32)[:1])
 
 
-@pytest.mark.parametrize("M", [1, 8, 13, 40, 64, 200, 1500])
+@pytest.mark.parametrize("M", [1, 8, 13, 40, 64, 100, 128, 200, 1500])
 @pytest.mark.parametrize("I,H", [(8960, 1536), (224, 96), (176, 80)])
 def test_fused_swiglu_matches_the_two_kernels(M, I, H):
     """gate/up product with the SwiGLU epilogue (rows interleaved in blocks of 8) against plain product + plain SwiGLU,
-    through all three kernels: streaming (M <= 16), tcgen05 swapped (M <= 64), tcgen05 plain."""
+    through all three kernels: streaming (M <= 16), tcgen05 swapped (M <= 128), tcgen05 plain."""
     from infer_b200 import fast_ops, ops
     g = torch.Generator(device=DEV).manual_seed(M + I)
     x = torch.randn(M, H, device=DEV, generator=g).bfloat16()

@@ -57,9 +57,10 @@ def test_static_entry_point_refuses_what_does_not_fit():
     lib, f = _static_fn()
     from infer_b200 import fast_ops
     st = fast_ops.device_state(DEV)
-    # a GPU reported as huge asks for more slices than the array holds: 128 tiles x 8 slices x 128 x 128 floats = 67 MB
-    # (products of up to 64 rows need no scratch at all: their slices meet in the cluster's shared memory)
-    M, N, K = 1024, 2048, 16384
+    # a GPU reported as huge against few tiles: 12 tiles x 16 slices x 128 x 128 floats = 12.6 MB through the workspace
+    # (products of up to 128 rows, and larger ones whose slices fill the GPU in clusters of 2, 4 or 8, need no scratch
+    # at all: their slices meet in the cluster's shared memory)
+    M, N, K = 256, 768, 16384
     plan = fast_ops.gemm_plan(M, N, K, 1000)
     assert plan[2] > 1 and plan[3] * 4 > (8 << 20) - 16384
     x = torch.zeros(M, K, device=DEV, dtype=torch.bfloat16)
