@@ -96,6 +96,13 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+# The reference's own published decode throughput for the 1.5B model under continuous batching, by concurrent
+# sequences (bench/stage11_slots_15b_bf16_1.5B.json, README.md:68 of RyanXiaoo/infer): one RTX 5070 Ti, real weights,
+# prompts of 5-12 tokens. It publishes nothing on a B200, at 2,048-token contexts or at batch 64.
+PUBLISHED_TOK_S = {1: 178.4, 4: 554.5, 8: 891.6, 16: 1339.2, 32: 1360.8}
+PUBLISHED_NOTE = "reference's published tok/s at the same number of sequences on one RTX 5070 Ti with short contexts"
+
+
 def build_engine(n_layers, batch, context, steps_total, dtype="bfloat16"):
     import torch
     from infer_b200.config import parse_config
@@ -286,7 +293,9 @@ def main():
 
     out = {"metric": "decode tok/s at batch 8, 2048-token contexts (Qwen2.5-1.5B sizes)", "value": round(value, 1),
            "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_step, 4),
-           "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+           "higher_is_better": True, "scaling": "weak",
+           "vs_baseline": round(value / PUBLISHED_TOK_S[args.batch], 2) if args.batch in PUBLISHED_TOK_S else None,
+           "baseline": PUBLISHED_NOTE, "dtype": "bf16",
            "data": "synthetic: random weights N(0,0.02), random cache contents, fixed token ids",
            "config": {"model": "Qwen2.5-1.5B sizes", "layers": n_layers, "layers_of_model": CONFIG["num_hidden_layers"],
                       "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],

@@ -12,13 +12,15 @@
 //
 // Two ways to map the product onto a tile:
 //   plain   A = x (tokens on the 128-row side), B = w;  for many tokens (prefill)
-//   swap    A = w (output features on the 128-row side), B = x, tokens on the BN side padded to 16/32/64;
-//           for few tokens (decode), where the weights are streamed once and the tensor core's M is not wasted.
-// With few tiles the K range is cut into `splits` slices. In the swapped mapping the slices of a tile are the CTAs
-// of one thread-block cluster: each leaves its float tile in its shared memory and every CTA adds a share of the
-// columns over all slices, in ascending order, through distributed shared memory. Otherwise (grid.z) each CTA writes
-// its float tile to a workspace and the CTA that arrives last at the tile's counter adds the slices in ascending
-// order. Either way the sum does not depend on arrival order.
+//   swap    A = w (output features on the 128-row side), B = x, tokens on the BN side padded to 16/32/64/128;
+//           for up to 128 tokens (decode), where the weights are streamed once and the tensor core's M is not wasted.
+// With few tiles the K range is cut into `splits` slices. Up to 8 slices of a tile are the CTAs of one thread-block
+// cluster (always in the swapped mapping; 2, 4 or 8 in the plain one): every slice pushes each block of columns of
+// its float tile into the shared memory of the slice that owns the block, and after one cluster barrier the owner
+// adds the slices in ascending order and runs the epilogue. Otherwise (grid.z, up to 16 slices of very few tiles)
+// each CTA writes its float tile to a workspace and the CTA that arrives last at the tile's counter adds the slices
+// in ascending order. Either way the sum does not depend on arrival order.
+// For many tokens a persistent kernel (further down) walks over tiles with two accumulators in tensor memory.
 // In the swapped mapping the ring takes up to eight stages (the CTA has the SM to itself and all of its weights
 // should be in flight) and the weights' first stages are requested before the kernel waits for its predecessor.
 //
