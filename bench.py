@@ -27,6 +27,14 @@ sys.path.insert(0, ROOT)
 CONFIG = dict(architectures=["Qwen2ForCausalLM"], hidden_size=1536, num_hidden_layers=28, num_attention_heads=12,
               num_key_value_heads=2, intermediate_size=8960, vocab_size=151936, rope_theta=1000000.0, rms_norm_eps=1e-6,
               max_position_embeddings=32768, tie_word_embeddings=True, use_sliding_window=False)
+# Further layer sizes of the same architecture (--sizes): Qwen2.5-7B and 14B. The default stays the 1.5B sizes.
+SIZES = {
+    "1.5b": CONFIG,
+    "7b": dict(CONFIG, hidden_size=3584, num_attention_heads=28, num_key_value_heads=4, intermediate_size=18944,
+               vocab_size=152064, tie_word_embeddings=False),
+    "14b": dict(CONFIG, hidden_size=5120, num_hidden_layers=48, num_attention_heads=40, num_key_value_heads=8,
+                intermediate_size=13824, vocab_size=152064, rms_norm_eps=1e-5, tie_word_embeddings=False),
+}
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -251,7 +259,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=2048)
-    ap.add_argument("--layers", type=int, default=CONFIG["num_hidden_layers"])
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (0: all of them)")
+    ap.add_argument("--sizes", default="1.5b", choices=sorted(SIZES), help="layer sizes: Qwen2.5-1.5B (the default), 7B or 14B")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
     ap.add_argument("--mode", default="all", choices=["all", "decode", "prefill"],
@@ -265,10 +274,12 @@ def main():
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     args.warmup = max(3, args.warmup)
+    global CONFIG
+    CONFIG = SIZES[args.sizes]
     import torch
     from infer_b200 import ops
     pk = peaks()
-    n_layers = args.layers
+    n_layers = args.layers or CONFIG["num_hidden_layers"]
     total_steps = args.steps + args.warmup
     eng = build_engine(n_layers, max(64, args.batch), args.context, 2 * total_steps + 64)
     cfg = CONFIG
@@ -291,17 +302,19 @@ def main():
     achieved = nbytes / (ms_step * 1e-3) / 1e9
     e2e_value, h2d, d2h = time_e2e(eng, args.batch, args.context, args.steps, args.warmup)
 
-    out = {"metric": "decode tok/s at batch 8, 2048-token contexts (Qwen2.5-1.5B sizes)", "value": round(value, 1),
+    name = f"Qwen2.5-{args.sizes.upper()} sizes"
+    out = {"metric": f"decode tok/s at batch {args.batch}, {args.context}-token contexts ({name})", "value": round(value, 1),
            "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_step, 4),
            "higher_is_better": True, "scaling": "weak",
-           "vs_baseline": round(value / PUBLISHED_TOK_S[args.batch], 2) if args.batch in PUBLISHED_TOK_S else None,
+           "vs_baseline": round(value / PUBLISHED_TOK_S[args.batch], 2) if args.sizes == "1.5b" and args.batch in PUBLISHED_TOK_S else None,
            "baseline": PUBLISHED_NOTE, "dtype": "bf16",
            "data": "synthetic: random weights N(0,0.02), random cache contents, fixed token ids",
-           "config": {"model": "Qwen2.5-1.5B sizes", "layers": n_layers, "layers_of_model": CONFIG["num_hidden_layers"],
+           "config": {"model": name, "layers": n_layers, "layers_of_model": CONFIG["num_hidden_layers"],
                       "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
                       "head_dim": 128, "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
-                      "global_batch": args.batch, "seq_len": args.context, "page_size": 16, "tied_head": True,
-                      "parallelism": "single GPU", "l2": "inputs larger than L2 (3.1 GB weights per step)",
+                      "global_batch": args.batch, "seq_len": args.context, "page_size": 16,
+                      "tied_head": bool(cfg["tie_word_embeddings"]), "parallelism": "single GPU",
+                      "l2": f"inputs larger than L2 ({wbytes / 1e9:.1f} GB weights per step)",
                       "peaks": pk["source"]},
            "clocks": clk, "gpu_launches": launches,
            "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},

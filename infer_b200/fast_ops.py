@@ -203,10 +203,6 @@ def linear(x, weight, bias, residual, out_dtype, out, swiglu=False, prefetch=Non
     return gemm_tc(x, weight, bias, residual, out_dtype, out, swiglu=swiglu)
 
 
-def rope_kv_write(qkv, cos, sin, step, table, cache, n_heads, n_kv, head_dim, write_cache):
-    return None
-
-
 def attention_supported(n_heads: int, n_kv: int, head_dim: int, page_size: int) -> bool:
     return head_dim % 16 == 0 and 16 <= head_dim <= 128 and page_size == 16 and n_heads // n_kv <= 16
 

@@ -87,14 +87,8 @@ class Attention(Mixer):
                                                   step.max_ctx_len, write_cache, prefetch=self.prefetch_next)
             if ctx is not None:
                 return self.o(ctx, residual=residual)
-        if self.rt.fast("rope"):
-            from .. import fast_ops
-            q = fast_ops.rope_kv_write(qkv, cos, sin, step, table, cache, self.n_heads, self.n_kv, self.head_dim, write_cache)
-        else:
-            q = None
-        if q is None:
-            q = ops.rope_kv_write(qkv, cos, sin, step.positions, step.token_seg, table, cache.k, cache.v,
-                                  self.n_heads, self.n_kv, self.head_dim, write_cache, step.status)
+        q = ops.rope_kv_write(qkv, cos, sin, step.positions, step.token_seg, table, cache.k, cache.v,
+                              self.n_heads, self.n_kv, self.head_dim, write_cache, step.status)
         ctx = None
         if self.rt.fast("attention"):
             from .. import fast_ops
