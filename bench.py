@@ -23,7 +23,7 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# BASELINE.json configs[2]: Qwen2.5-1.5B layer sizes
+# The benchmark configuration: Qwen2.5-1.5B layer sizes, random weights
 CONFIG = dict(architectures=["Qwen2ForCausalLM"], hidden_size=1536, num_hidden_layers=28, num_attention_heads=12,
               num_key_value_heads=2, intermediate_size=8960, vocab_size=151936, rope_theta=1000000.0, rms_norm_eps=1e-6,
               max_position_embeddings=32768, tie_word_embeddings=True, use_sliding_window=False)
@@ -311,7 +311,7 @@ def main():
            "data": "synthetic: random weights N(0,0.02), random cache contents, fixed token ids",
            "config": {"model": name, "layers": n_layers, "layers_of_model": CONFIG["num_hidden_layers"],
                       "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
-                      "head_dim": 128, "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
+                      "head_dim": cfg["hidden_size"] // cfg["num_attention_heads"], "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
                       "global_batch": args.batch, "seq_len": args.context, "page_size": 16,
                       "tied_head": bool(cfg["tie_word_embeddings"]), "parallelism": "single GPU",
                       "l2": f"inputs larger than L2 ({wbytes / 1e9:.1f} GB weights per step)",

@@ -2,7 +2,7 @@
 (RyanXiaoo/infer src/forward.cpp, compiled here out of tree with g++, nothing copied) on two tiny random
 models of the architecture.  The plain implementation (tests/plain_model.py) is compared with these files.
 
-Run once:  python tests/golden/make_golden.py [path to the reference checkout]
+Run once:  python tests/golden/make_golden.py <path to a checkout of RyanXiaoo/infer>
 
 The reference reads bfloat16 tensors only (it never checks a tensor's dtype, src/model.cpp:18-29), so the
 models are written in bfloat16; tests regenerate the same weights from the same seeds.
@@ -60,7 +60,9 @@ N_NEW = 8
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        sys.exit("usage: make_golden.py <path to a checkout of RyanXiaoo/infer>")
+    ref = sys.argv[1]
     work = tempfile.mkdtemp(prefix="golden_")
     with open(os.path.join(work, "driver.cpp"), "w") as f:
         f.write(DRIVER)
