@@ -1,0 +1,65 @@
+"""Host-side decisions of the kernels' launchers, which need no GPU: how the tcgen05 matrix product maps a shape onto
+tiles and K slices (the planner is a host function of the compiled library) and how the decode attention cuts the key
+range into slices and clusters. The shapes are those of the 1.5B model's layer on a GPU of 148 SMs."""
+import types
+
+import pytest
+
+SMS = 148
+
+
+def _plan(M, N, K, sms=SMS):
+    from infer_b200 import fast_ops
+    from infer_b200.csrc.build import BuildError
+    try:
+        return fast_ops.gemm_plan(M, N, K, sms)
+    except BuildError as e:                                      # no nvcc on this machine: the planner cannot be built
+        pytest.skip(f"the library that holds the planner cannot be compiled here: {str(e)[:80]}")
+
+
+def test_few_tokens_take_the_swapped_mapping_with_cluster_slices():
+    for M, bn in ((1, 16), (16, 16), (17, 32), (33, 64), (64, 64), (65, 128), (128, 128)):
+        swap, got_bn, splits, ws, counters = _plan(M, 1536, 8960)
+        assert (swap, got_bn) == (1, bn)
+        assert splits == 8 and ws == 0 and counters == 0          # 12 tiles: 8 slices as a cluster, no scratch
+    # enough tiles to fill the GPU: no slices at all
+    assert _plan(64, 17920, 1536) == (1, 64, 1, 0, 0)
+    # a slice keeps at least two k-blocks
+    assert _plan(8, 1536, 320)[2] == 2
+
+
+def test_middling_token_counts_take_the_plain_mapping():
+    assert _plan(129, 1536, 8960)[:2] == (0, 128)
+    # 24 tiles: 4 slices of K as a cluster (8 would leave a third of the CTAs to a second round), no scratch
+    assert _plan(256, 1536, 8960) == (0, 128, 4, 0, 0)
+    assert _plan(512, 1536, 8960) == (0, 128, 2, 0, 0)
+    # very few tiles: up to 16 slices through the workspace, with one counter per tile
+    swap, bn, splits, ws, counters = _plan(200, 300, 4096)
+    assert (swap, bn, splits, counters) == (0, 128, 16, 6) and ws == 16 * 6 * 128 * 128
+
+
+def test_many_tokens_take_the_persistent_kernel_with_the_width_that_fills_the_sms():
+    assert _plan(2048, 17920, 1536) == (0, 512, 1, 0, 0)          # 128 x 256 tiles: 1120 of them
+    assert _plan(2048, 2048, 1536) == (0, 512, 1, 0, 0)           # 128 tiles in one round; narrower would need two
+    assert _plan(2048, 1536, 8960) == (0, 352, 1, 0, 0)           # 16 x 9 tiles of 176 columns = 144 CTAs
+    assert _plan(2048, 1536, 1536) == (0, 352, 1, 0, 0)
+    assert _plan(3000, 3584, 3584)[1] in (352, 384, 512)
+
+
+def test_refused_shapes():
+    assert _plan(8, 1536, 100) is None                            # K not a multiple of 8
+    assert _plan(0, 1536, 1536) is None
+
+
+def test_decode_attention_slices_and_clusters():
+    from infer_b200 import fast_ops
+    st = types.SimpleNamespace(sm_count=SMS)
+    assert fast_ops._decode_splits(st, 8, 2, 2048) == (8, 1)      # the serving shape: 128 CTAs, one cluster each
+    assert fast_ops._decode_splits(st, 64, 2, 2048) == (2, 1)     # enough requests: two slices
+    assert fast_ops._decode_splits(st, 1, 2, 100) == (1, 1)       # 7 pages: not worth cutting
+    assert fast_ops._decode_splits(st, 8, 2, 8192) == (8, 1)      # the second level does not pay yet
+    n, c = fast_ops._decode_splits(st, 1, 2, 30000)
+    assert n == 8 and 1 < c <= fast_ops.ATTENTION_MAX_CLUSTERS
+    assert 2 * 8 * c <= 2 * SMS and (30000 // 16) // (8 * c) >= fast_ops.ATTENTION_CLUSTER_PAGES
+    assert fast_ops._decode_splits(st, 8, 2, 30000) == (8, 2)     # 128 CTAs already: at most two per SM
+    assert fast_ops._decode_scratch(st, 8, 2, 128, 1) == (None, None)
