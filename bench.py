@@ -244,12 +244,79 @@ def time_e2e(eng, batch, context, steps, warmup):
     dt = time.perf_counter() - t0
     n_tokens = batch * steps                 # tokens generated on the device in the timed steps
     assert len(got) - n0 >= batch * (steps - 1), "the scheduler did not hand the tokens to the host"
-    h2d = eng.last_h2d_bytes + ge.sampler.last_h2d_bytes
+    h2d = eng.last_h2d_bytes                 # the one packed buffer: step integers and sampling inputs
     for rid in list(sch.active):
         sch.cancel(rid)
     sch.run_until_idle()
     release_all(eng)
     return n_tokens / dt, h2d, 4 * batch
+
+
+def reference_arm(args):
+    """The unmodified reference (built out of tree for sm_100 under baseline/_ref, see baseline/reference_arm.py)
+    through its own serving bench, main_serve_bench: as many requests as slots, contexts of `context` tokens (a
+    shared prefix plus 8 tokens each), CUDA graphs, continuous batching. The durations of its scheduler's decode
+    steps come from its own event log; W of them are dropped and the next K taken. Its scheduler step copies the
+    step's token ids to the device and reads the sampled ids back every step, so `value` and `e2e` are the same
+    number: the reference has no device-only timing on this path. It refuses more than 32 rows in a step, so there
+    is no batch-64 point."""
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    import reference_arm as ra
+    n_layers = args.layers or CONFIG["num_hidden_layers"]
+    cfg = dict(CONFIG, num_hidden_layers=n_layers)
+    name = f"qwen2.5-{args.sizes}-random-{n_layers}l"
+    try:
+        binary = ra.build()
+        ra.prepare_model(cfg, name)
+        clocks = ClockSampler()
+        clocks.start()
+        need = args.warmup + args.steps
+        main_run = ra.run_serve_bench(binary, name, args.batch, args.context, max_new=2 * need + 16)
+        clk = clocks.stop()
+        durs = main_run["step_ms"][args.warmup:args.warmup + args.steps]
+        if len(durs) < args.steps:
+            raise ra.Unavailable(f"only {len(durs)} timed decode steps, {args.steps} wanted")
+        ms_step = sum(durs) / len(durs)
+        points = {}
+        if not args.no_points:
+            one = ra.run_serve_bench(binary, name, 1, args.context, max_new=2 * need + 16)
+            d1 = one["step_ms"][args.warmup:args.warmup + args.steps]
+            points["decode_b1"] = round(1e3 * len(d1) / sum(d1), 1)
+    except ra.Unavailable as e:
+        print(json.dumps({"impl": "reference", "unavailable": str(e)}))
+        return 0
+    value = args.batch * 1e3 / ms_step
+    pk = peaks()
+    hd = cfg["hidden_size"] // cfg["num_attention_heads"]
+    # what the reference's step has to read: bfloat16 weights once, and its float32 cache of the live requests
+    w_bytes = 2 * (n_layers * (cfg["hidden_size"] * (cfg["num_attention_heads"] + 2 * cfg["num_key_value_heads"]) * hd
+                               + cfg["num_attention_heads"] * hd * cfg["hidden_size"] + 3 * cfg["hidden_size"] * cfg["intermediate_size"])
+                   + cfg["vocab_size"] * cfg["hidden_size"])
+    kv_bytes = args.batch * (args.context + args.warmup + args.steps // 2) * n_layers * 2 * cfg["num_key_value_heads"] * hd * 4
+    achieved = (w_bytes + kv_bytes) / (ms_step * 1e-3) / 1e9
+    out = {"impl": "reference", "metric": f"decode tok/s at batch {args.batch}, {args.context}-token contexts (Qwen2.5-{args.sizes.upper()} sizes)",
+           "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+           "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak",
+           "vs_baseline": round(value / PUBLISHED_TOK_S[args.batch], 2) if args.sizes == "1.5b" and args.batch in PUBLISHED_TOK_S else None,
+           "baseline": PUBLISHED_NOTE, "dtype": "bf16 weights, fp32 activations and cache (the reference's only mode)",
+           "data": "synthetic: random weights N(0,0.02), random token ids",
+           "config": {"model": f"Qwen2.5-{args.sizes.upper()} sizes", "layers": n_layers, "layers_of_model": CONFIG["num_hidden_layers"],
+                      "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+                      "head_dim": hd, "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
+                      "global_batch": args.batch, "seq_len": args.context, "page_size": 16,
+                      "tied_head": bool(cfg["tie_word_embeddings"]), "parallelism": "single GPU",
+                      "l2": "inputs larger than L2", "how": "main_serve_bench n=slots prefix=context-8 graphs=1, step durations from its event log"},
+           "clocks": clk, "gpu_launches": None,
+           "e2e": {"value": round(value, 1), "unit": "tokens/s", "h2d_bytes_per_step": None, "d2h_bytes_per_step": None},
+           "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                        "frac": round(achieved / pk["hbm_gbs"], 4)},
+           "points": points,
+           "prefill": {"value": round(main_run["prompt_tokens"] * 1e3 / max(main_run["prompt_ms"], 1e-9), 1),
+                       "tokens": main_run["prompt_tokens"], "ms": round(main_run["prompt_ms"], 3),
+                       "frac": round(prefill_flops(cfg, n_layers, main_run["prompt_tokens"]) / (max(main_run["prompt_ms"], 1e-9) * 1e-3)
+                                     / (pk["bf16_tflops"] * 1e12), 4)}}
+    print(json.dumps(out))
+    return 0
 
 
 def main():
@@ -266,16 +333,14 @@ def main():
     ap.add_argument("--mode", default="all", choices=["all", "decode", "prefill"],
                     help="decode / prefill: run only that part and print a short line (for profiling small cases)")
     args = ap.parse_args()
-    if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable": "RyanXiaoo/infer is a C++/CUDA CMake project built for sm_120 "
-                          "only, with no setup.py or pyproject.toml: pip reports 'not installable'"}))
-        return 0
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     args.warmup = max(3, args.warmup)
     global CONFIG
     CONFIG = SIZES[args.sizes]
+    if args.impl == "reference":
+        return reference_arm(args)
     import torch
     from infer_b200 import ops
     pk = peaks()

@@ -5,7 +5,7 @@ bytes the kernel has to read and TFLOP/s of its arithmetic.
     python -m infer_b200.cli.kernel_bench linear --M 8 --N 1536 --K 8960 [--kernel auto|skinny|tc|plain] [--epi none|residual|swiglu]
     python -m infer_b200.cli.kernel_bench attention --batch 8 --context 2048 --q-len 1 [--heads 12 --kv-heads 2 --head-dim 128]
     python -m infer_b200.cli.kernel_bench rmsnorm --M 8 --K 1536
-    python -m infer_b200.cli.kernel_bench chain --M 8 --hidden 1536 --intermediate 8960 --qkv 2048 [--separate]
+    python -m infer_b200.cli.kernel_bench layer --M 8 --hidden 1536 --intermediate 8960 --qkv 2048 [--phases 1..4]
 
 Inputs rotate over enough copies to exceed the 126 MB L2, as in the model where every layer brings its own weights;
 the launches (one per copy) are captured in a CUDA graph and the replay is timed, so the number is what the kernel
@@ -48,7 +48,7 @@ def _time(fn, n_variants, reps, warmup=3):
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("what", choices=["linear", "attention", "rmsnorm", "chain"])
+    ap.add_argument("what", choices=["linear", "attention", "rmsnorm", "layer"])
     ap.add_argument("--M", type=int, default=8)
     ap.add_argument("--N", type=int, default=1536)
     ap.add_argument("--K", type=int, default=1536)
@@ -63,14 +63,12 @@ def main(argv=None) -> int:
     ap.add_argument("--splits", type=int, default=0)
     ap.add_argument("--bn", type=int, default=0, help="tc: the tile code instead of the planner's (many tokens, no K slices)")
     ap.add_argument("--cluster", type=int, default=0)
-    ap.add_argument("--regs", action="store_true", help="skinny: the register-streaming kernel instead of the bulk-copy one")
     ap.add_argument("--fused", action="store_true", help="attention: the decode kernel that also rotates and stores k/v")
     ap.add_argument("--norm", action="store_true", help="skinny kernel with the fused RMSNorm prologue")
     ap.add_argument("--hidden", type=int, default=1536)
     ap.add_argument("--intermediate", type=int, default=8960)
     ap.add_argument("--qkv", type=int, default=2048)
-    ap.add_argument("--separate", action="store_true", help="chain: the same products as separate kernels")
-    ap.add_argument("--phases", type=int, default=4, help="chain: only the first n products")
+    ap.add_argument("--phases", type=int, default=4, help="layer: only the first n products")
     ap.add_argument("--reps", type=int, default=50)
     args = ap.parse_args(argv)
     import torch
@@ -102,7 +100,7 @@ def main(argv=None) -> int:
             if args.kernel == "skinny":
                 if args.norm:
                     return fast_ops.linear_skinny(hx, ws[i], None, r, odt, r, swiglu, args.cluster, nw, 1e-6)
-                return fast_ops.linear_skinny(x, ws[i], None, r, odt, r, swiglu, args.cluster, bulk=not args.regs)
+                return fast_ops.linear_skinny(x, ws[i], None, r, odt, r, swiglu, args.cluster)
             if args.kernel == "tc":
                 return fast_ops.gemm_tc(x, ws[i], None, r, odt, r, swiglu=swiglu, plan=plan)
             if args.kernel == "plain":
@@ -141,9 +139,11 @@ def main(argv=None) -> int:
         flops = 4 * B * nh * hd * (q_len * ctx + q_len * (q_len + 1) / 2)
         out.update(batch=B, context=ctx, q_len=q_len, us_median=round(med, 2), us_min=round(mn, 2),
                    gbs=round(nbytes / med / 1e3, 1), tflops=round(flops / med / 1e6, 2))
-    elif args.what == "chain":
-        # what a decode layer does between two attention kernels: o product + residual, norm, gate/up + SwiGLU,
-        # down + residual, the next layer's norm and q/k/v product with bias
+    elif args.what == "layer":
+        # what a decode layer does between two attention kernels: o product + residual, norm + gate/up + SwiGLU,
+        # down + residual, the next layer's norm + q/k/v product with bias (the norm inside the product where the
+        # streaming kernel takes it, as in the model)
+        from infer_b200.parts.base import DeferredNorm
         M, H, I, Q = args.M, args.hidden, args.intermediate, args.qkv
         F = fast_ops
         per_layer = (H * H + 3 * H * I + Q * H) * 2
@@ -153,28 +153,26 @@ def main(argv=None) -> int:
         g, bias = torch.ones(H, device=dev), torch.zeros(Q, device=dev)
         ctx = torch.randn(M, H, device=dev).bfloat16()
         h = torch.randn(M, H, device=dev)
-        act = torch.empty(M, I, dtype=torch.bfloat16, device=dev)
         qkv = torch.empty(M, Q, dtype=torch.bfloat16, device=dev)
-        chains = [[F.chain_phase(L["wo"], ctx, h, F.CHAIN_EPI_RESIDUAL),
-                   F.chain_phase(L["wgu"], h, act, F.CHAIN_EPI_SWIGLU, norm_weight=g, eps=1e-6),
-                   F.chain_phase(L["wd"], act, h, F.CHAIN_EPI_RESIDUAL),
-                   F.chain_phase(L["wqkv"], h, qkv, F.CHAIN_EPI_STORE, bias=bias, norm_weight=g, eps=1e-6)][:args.phases]
-                  for L in layers]
+
+        class _Norm:
+            weight, eps = g, 1e-6
+            @staticmethod
+            def forward(x):
+                return ops.rmsnorm(x, g, 1e-6, torch.bfloat16)
 
         def run(i):
             L = layers[i]
-            if not args.separate:
-                return F.linear_chain(chains[i], M, dev)
             F.linear(ctx, L["wo"], None, h, torch.float32, h)
             if args.phases > 1:
-                a = F.gate_up_swiglu(ops.rmsnorm(h, g, 1e-6, torch.bfloat16), L["wgu"])
+                a = F.gate_up_swiglu(DeferredNorm(_Norm, h), L["wgu"])
             if args.phases > 2:
                 F.linear(a, L["wd"], None, h, torch.float32, h)
             if args.phases > 3:
-                F.linear(ops.rmsnorm(h, g, 1e-6, torch.bfloat16), L["wqkv"], bias, None, torch.bfloat16, qkv)
+                F.linear(DeferredNorm(_Norm, h), L["wqkv"], bias, None, torch.bfloat16, qkv)
         med, mn = _time(run, copies, args.reps)
         nbytes = [H * H, H * H + 2 * I * H, H * H + 3 * I * H, per_layer // 2][args.phases - 1] * 2
-        out.update(M=M, hidden=H, intermediate=I, qkv=Q, phases=args.phases, separate=args.separate,
+        out.update(M=M, hidden=H, intermediate=I, qkv=Q, phases=args.phases,
                    us_median=round(med, 2), us_min=round(mn, 2), gbs=round(nbytes / med / 1e3, 1))
     else:
         M, K = args.M, args.K

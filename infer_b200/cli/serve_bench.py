@@ -2,11 +2,14 @@
 (src/main_serve_bench.cpp:1-27,74-239): a fixed request set goes through the scheduler once per slot count, with
 continuous and static batching.
 
-    bin/serve_bench --model DIR [key=value ...]
+    bin/serve_bench --model DIR | random=SPEC [key=value ...]
+      random=          a preset name, a config.json or a JSON object: seeded random weights instead of --model
       n=64             requests                 slots=1,2,4,8,16,32
       max_new=48       spread over max_new/2 .. 3*max_new/2 (src/main_serve_bench.cpp:137)
       max_seq=192      per-sequence cap         budget_mb=0 (0 = reserve slots x max_seq)
+      kv_blocks=0      size of the page pool in pages, instead of budget_mb
       prompt_len=12    prompts are seeded random ids of 5..prompt_len tokens (the reference cycles five fixed prompts)
+      prefix=0         that many shared random tokens in front of every prompt (the reference's long-context switch)
       chunk=512        token budget of one step
       modes=both|continuous|static
       gemm=mine|plain  attn=split|plain         dtype=bfloat16|float32
@@ -30,18 +33,27 @@ def main(argv=None) -> int:
     ap.add_argument("kv", nargs="*")
     args = ap.parse_args(argv)
     opt = dict(n="64", slots="1,2,4,8,16,32", max_new="48", max_seq="192", budget_mb="0", prompt_len="12", chunk="512",
-               modes="both", gemm="mine", attn="split", dtype="bfloat16", events="", tag="")
+               modes="both", gemm="mine", attn="split", dtype="bfloat16", events="", tag="", random="", kv_blocks="0",
+               prefix="0", weights_seed="0")
     for kv in args.kv:
         k, _, v = kv.partition("=")
         if k not in opt:
             ap.error(f"unknown option {k}")
         opt[k] = v
-    if not args.model:
-        ap.error("no model: give --model DIR or set LLM_MODEL")
+    if not args.model and not opt["random"]:
+        ap.error("no model: give --model DIR, random=SPEC, or set LLM_MODEL")
     import numpy as np
     import torch
     from infer_b200.engine.generation import LLM
     from infer_b200.engine.scheduler import Request, SampleParams
+    spec = weights = None
+    if opt["random"]:
+        from infer_b200.config import parse_config
+        from infer_b200.models import load_preset
+        from infer_b200.weights import random_weights
+        arch, typed = parse_config(load_preset(opt["random"]))
+        spec = arch.to_spec(typed)
+        weights = random_weights(spec, int(opt["weights_seed"]), torch.bfloat16, device="cuda")
     kernels = {}
     if opt["gemm"] == "plain":
         kernels["linear"] = "plain"
@@ -52,11 +64,13 @@ def main(argv=None) -> int:
           f"{'ttft p50':>8} {'steps':>6} {'pages':>7} {'peak':>7} {'preempt':>7}")
     records = []
     for slots in [int(s) for s in opt["slots"].split(",")]:
-        llm = LLM(args.model, dtype=opt["dtype"], slots=slots, max_seq=max_seq, budget_mb=int(opt["budget_mb"]),
-                  max_batch_tokens=int(opt["chunk"]), kernels=kernels)
+        llm = LLM(None if spec is not None else args.model, dtype=opt["dtype"], slots=slots, max_seq=max_seq,
+                  budget_mb=int(opt["budget_mb"]), kv_blocks=int(opt["kv_blocks"]), max_batch_tokens=int(opt["chunk"]),
+                  kernels=kernels, spec=spec, weights=weights)
         V = llm.engine.spec.vocab_size
         rng = np.random.default_rng(0)
-        prompts = [rng.integers(0, V, int(rng.integers(5, max(6, int(opt["prompt_len"]) + 1)))).tolist() for _ in range(5)]
+        prefix = rng.integers(0, V, int(opt["prefix"])).tolist()
+        prompts = [prefix + rng.integers(0, V, int(rng.integers(5, max(6, int(opt["prompt_len"]) + 1)))).tolist() for _ in range(5)]
         reqs = [(i, prompts[i % 5], max_new_base // 2 + (i * 7) % (max_new_base + 1)) for i in range(n)]
         for continuous in (True, False):
             if opt["modes"] == "continuous" and not continuous or opt["modes"] == "static" and continuous:

@@ -2,7 +2,7 @@
 
 It drives the framework's own model, step function, cache manager and kernels: the ones generation uses.
 
-    bin/trace_run --model DIR --dtype bfloat16|float32 --out DIR --max-tokens N
+    bin/trace_run --model DIR --dtype bfloat16|float32 --out DIR --max-tokens N [--format f32|npy|both]
 
 Steps come on standard input, one JSON object a line:
 
@@ -11,6 +11,8 @@ Steps come on standard input, one JSON object a line:
 All entries of a step run as one batch.  ``end`` names requests that are finished after the step; their
 pages and slot go back.  For a step in which something is wanted, ``<out>/<step>.f32`` holds the logits at
 the wanted places, in the order of the entries and of ``want``, little-endian float32 [wanted, vocab].
+With ``--format npy`` (or ``both``) the same rows are written as ``<out>/<step>.npy``, a NumPy array file of
+float32 [wanted, vocab] (the reference's tools exchange arrays in that format, src/npy.h).
 After every step a line ``done <step>`` is printed and flushed.
 """
 from __future__ import annotations
@@ -33,6 +35,8 @@ def main(argv=None) -> int:
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens live requests hold at any time (each request rounded up to 64)")
     ap.add_argument("--max-requests", type=int, default=MAX_LIVE, help="live requests at a time (default 4)")
+    ap.add_argument("--format", default="f32", choices=["f32", "npy", "both"],
+                    help="logit files: raw little-endian float32 (<step>.f32), NumPy (<step>.npy), or both")
     args = ap.parse_args(argv)
 
     print("[trace_run] loading the framework (kernels are compiled at first use) ...", file=sys.stderr, flush=True)
@@ -60,7 +64,10 @@ def main(argv=None) -> int:
         logits = engine.step(entries)
         if logits.shape[0] > 0:
             arr = logits.to("cpu", torch.float32).numpy().astype("<f4", copy=False)
-            arr.tofile(os.path.join(args.out, f"{step}.f32"))
+            if args.format in ("f32", "both"):
+                arr.tofile(os.path.join(args.out, f"{step}.f32"))
+            if args.format in ("npy", "both"):
+                np.save(os.path.join(args.out, f"{step}.npy"), arr)
         else:
             torch.cuda.synchronize()
         engine.check_status()

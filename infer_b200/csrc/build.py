@@ -29,9 +29,7 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", 
 # module name -> source file; headers that every module depends on
 MODULES: Dict[str, str] = {
     "plain": "plain_ops.cu",
-    "gemv": "gemv.cu",
     "gemvb": "gemv_bulk.cu",
-    "chain": "linear_chain.cu",
     "gemm": "gemm_tcgen05.cu",
     "attn": "attention_fast.cu",
     "attn_tc": "attention_tc.cu",

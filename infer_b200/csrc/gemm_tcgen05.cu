@@ -1207,7 +1207,10 @@ IB_EXPORT int ib_gemm_tc_static(const void* x, const void* w, const float* bias,
     if (rc) return rc;
     float* workspace = nullptr;
     unsigned int* counters = nullptr;
-    if (splits > 1) {
+    // Only a plan that sums its K slices through global memory (ws_floats > 0) gets the array. The other split plans
+    // (up to 128 rows, and clusters of 2, 4 or 8 slices) add their slices in the cluster's shared memory and must be
+    // given no workspace: with one, ib_gemm_tc would take the global-memory path, whose need the plan did not state.
+    if (splits > 1 && ws_floats > 0) {
         const int64_t room = (int64_t(IB_GEMM_STATIC_SCRATCH_BYTES) - IB_STATIC_COUNTERS * 4) / 4;
         if (ws_floats > room || n_counters > IB_STATIC_COUNTERS)
             return ib::fail(IB_ERR_ARG, "gemm_tc_static: M=%lld N=%lld K=%lld needs %lld bytes of split-K scratch and %lld counters; "

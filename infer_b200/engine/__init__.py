@@ -1,2 +1,2 @@
-from .engine import Engine, OutOfPages, StepContext, StepEntry  # noqa: F401
+from .engine import Engine, OutOfPages, SamplingInputs, StepContext, StepEntry, StepResult  # noqa: F401
 from .model import Model  # noqa: F401

@@ -64,6 +64,29 @@ class StepContext:
     max_ctx_len: int = 0
     decode_only: bool = False
     extras: Dict[str, object] = field(default_factory=dict)   # per-step scratch that fast kernels share
+    # sampling at the wanted rows inside the step (None: the step returns logits)
+    sampling: Optional["SamplingInputs"] = None
+
+
+@dataclass
+class SamplingInputs:
+    """Per wanted row, on the device: what the sampling kernel reads. ``filtered`` selects the top-k / top-p kernel."""
+    temperature: torch.Tensor        # float32 [n_want]
+    seed: torch.Tensor               # int64 [n_want]
+    position: torch.Tensor           # int64 [n_want] position of the token fed: the noise stream's key
+    top_k: torch.Tensor              # int64 [n_want]
+    top_p: torch.Tensor              # float32 [n_want]
+    slot: torch.Tensor               # int64 [n_want] state slot of the row's request (where its token is left)
+    filtered: bool = False
+
+
+@dataclass
+class StepResult:
+    """What ``Engine.try_step`` returns. ``ran[i]`` is False for an entry that was left out because it could not get
+    its pages or would pass the sequence limit; such an entry's request is exactly as it was before the call.
+    ``output`` holds the rows of the entries that ran (logits, or token ids when sampling), in their order."""
+    output: torch.Tensor
+    ran: List[bool]
 
 
 def _round_up(x: int, m: int) -> int:
@@ -87,6 +110,7 @@ class _GraphEntry:
     def __init__(self, static: torch.Tensor):
         self.static, self.graphs, self.turn, self.warm, self.n_launches = static, [], 0, 0, 0
         self.pinned, self.flip = None, 0
+        self.copied = None                 # per pinned buffer: the event recorded after the copy that read it last
         self.copies = GRAPH_COPIES
 
 
@@ -153,10 +177,12 @@ class Engine:
 
     # ------------------------------------------------------------------ the step
 
-    def _build_context(self, entries: Sequence[StepEntry], graphs: bool = False):
+    def _build_context(self, entries: Sequence[StepEntry], graphs: bool = False, sample=None):
         """Packs the step's integers on the host and places them on the device. With ``graphs`` and a decode-only
         step, the integers go into the static buffer of the step's shape (tokens, wanted rows, table widths), whose
-        tensors a captured CUDA graph reads; returns (context, graph entry or None)."""
+        tensors a captured CUDA graph reads; returns (context, graph entry or None). ``sample``: one
+        (SampleParams, position) per wanted row, in the order of the entries and their ``want`` lists; the sampling
+        kernel's inputs then travel in the same buffer."""
         V, cache = self.spec.vocab_size, self.cache
         S = len(entries)
         T = sum(len(e.tokens) for e in entries)
@@ -169,8 +195,11 @@ class Engine:
             w = max(-(-(p + n) // cache.page_size) for p, n in zip(pos0, seg_lens))
             # decode-only steps round the table width up further, so that one captured graph serves many steps
             widths.append(_round_up(max(w, 1), GRAPH_WIDTH_PAGES if (graphs and T == S) else 8))
-        # layout of the packed buffer
-        sizes = [T, T, T, S + 1, S, S, max(n_want, 1)] + [S * w for w in widths]
+        if sample is not None and len(sample) != n_want:
+            raise ValueError(f"sampling needs one (params, position) per wanted row: {len(sample)} given, {n_want} wanted")
+        n_s = n_want if sample is not None else 0
+        # layout of the packed buffer (int32 words; 64-bit fields take two, and every section starts on 16 bytes)
+        sizes = [T, T, T, S + 1, S, S, max(n_want, 1)] + [S * w for w in widths] + [n_s, 2 * n_s, 2 * n_s, 2 * n_s, n_s, 2 * n_s]
         offs = np.concatenate([[0], np.cumsum([_round_up(s, 4) for s in sizes])])
         buf = np.zeros(int(offs[-1]), dtype=np.int32)
         ids, pos, seg = (buf[offs[i]:offs[i] + T] for i in range(3))
@@ -178,9 +207,11 @@ class Engine:
         seg_pos0 = buf[offs[4]:offs[4] + S]
         seg_slot = buf[offs[5]:offs[5] + S]
         want = buf[offs[6]:offs[6] + n_want]
+        want_slot = []
         r = w_i = 0
         for s, e in enumerate(entries):
             n = seg_lens[s]
+            slot = cache.slot(e.rid)
             if n == 1:
                 # a decoded token: the common case, kept free of array work
                 tok = int(e.tokens[0])
@@ -195,11 +226,12 @@ class Engine:
                 seg[r] = s
                 seg_start[s] = r
                 seg_pos0[s] = pos0[s]
-                seg_slot[s] = cache.slot(e.rid)
+                seg_slot[s] = slot
                 for wi in e.want:
                     if int(wi) != 0:
                         raise ValueError(f"request {e.rid!r}: wanted place {wi} is outside its 1 tokens")
                     want[w_i] = r
+                    want_slot.append(slot)
                     w_i += 1
                 r += 1
                 continue
@@ -216,11 +248,12 @@ class Engine:
             seg[r:r + n] = s
             seg_start[s] = r
             seg_pos0[s] = pos0[s]
-            seg_slot[s] = cache.slot(e.rid)
+            seg_slot[s] = slot
             for wi in e.want:
                 if not 0 <= int(wi) < n:
                     raise ValueError(f"request {e.rid!r}: wanted place {wi} is outside its {n} tokens")
                 want[w_i] = r + int(wi)
+                want_slot.append(slot)
                 w_i += 1
             r += n
         seg_start[S] = T
@@ -230,12 +263,31 @@ class Engine:
             for s, e in enumerate(entries):
                 t = cache.block_table(e.rid, gi)
                 tab[s, :len(t)] = t
+        o_s = 7 + n_groups                                  # first of the six sampling sections
+        filtered = False
+        if n_s:
+            temp = buf[offs[o_s]:offs[o_s] + n_s].view(np.float32)
+            seed = buf[offs[o_s + 1]:offs[o_s + 1] + 2 * n_s].view(np.int64)
+            spos = buf[offs[o_s + 2]:offs[o_s + 2] + 2 * n_s].view(np.int64)
+            topk = buf[offs[o_s + 3]:offs[o_s + 3] + 2 * n_s].view(np.int64)
+            topp = buf[offs[o_s + 4]:offs[o_s + 4] + n_s].view(np.float32)
+            sslot = buf[offs[o_s + 5]:offs[o_s + 5] + 2 * n_s].view(np.int64)
+            for i, (p, position) in enumerate(sample):
+                temp[i] = max(0.0, float(p.temperature))
+                seed[i] = int(p.seed) & 0x7FFFFFFFFFFFFFFF
+                spos[i] = int(position)
+                topk[i] = int(getattr(p, "top_k", 0) or 0)
+                topp[i] = float(getattr(p, "top_p", 1.0))
+                sslot[i] = want_slot[i]
+                if temp[i] > 0 and (topk[i] > 0 or topp[i] < 1.0):
+                    filtered = True
+        mode = 0 if sample is None else (2 if filtered else 1)
         entry = None
         key = None
         if graphs and T == S:
-            key = (S, n_want, tuple(widths))
+            key = (S, n_want, tuple(widths), mode)
         elif graphs and T <= PORTION_GRAPH_MAX_TOKENS:
-            pkey = ("portions", tuple(seg_lens), n_want, tuple(widths))
+            pkey = ("portions", tuple(seg_lens), n_want, tuple(widths), mode)
             if pkey in self._graphs:
                 key = pkey
             else:
@@ -256,44 +308,102 @@ class Engine:
                     self._graphs.pop(next(k for k in self._graphs if k[0] != "portions"))
                 entry = self._graphs[key] = _GraphEntry(torch.empty(buf.size, dtype=torch.int32, device=self.rt.device))
                 entry.pinned = [torch.empty(buf.size, dtype=torch.int32).pin_memory() for _ in range(2)]
+                entry.copied = [torch.cuda.Event() for _ in range(2)]
                 if portion:
                     entry.copies, entry.warm = 1, GRAPH_WARMUP_STEPS - 1      # the shape has run eagerly before
-            # two pinned staging buffers alternate, so that one is free while the other's copy may still be in flight
+            # Two pinned staging buffers alternate. The copy out of a buffer is asynchronous: before the buffer is
+            # written again, the copy that read it last (two steps ago) must have run, or a caller that issues steps
+            # without ever waiting for the device would overwrite integers that an earlier step has not yet taken.
             entry.flip ^= 1
+            entry.copied[entry.flip].synchronize()
             host = entry.pinned[entry.flip]
             host.numpy()[:] = buf
             dev = entry.static
             dev.copy_(host, non_blocking=True)
+            entry.copied[entry.flip].record()
         else:
             dev = torch.from_numpy(buf).pin_memory().to(self.rt.device, non_blocking=True)
         self.last_h2d_bytes = buf.nbytes
 
         def cut(i, n):
             return dev[int(offs[i]):int(offs[i]) + n]
+        sampling = None
+        if n_s:
+            sampling = SamplingInputs(
+                temperature=cut(o_s, n_s).view(torch.float32), seed=cut(o_s + 1, 2 * n_s).view(torch.int64),
+                position=cut(o_s + 2, 2 * n_s).view(torch.int64), top_k=cut(o_s + 3, 2 * n_s).view(torch.int64),
+                top_p=cut(o_s + 4, n_s).view(torch.float32), slot=cut(o_s + 5, 2 * n_s).view(torch.int64), filtered=filtered)
         ctx = StepContext(
             n_tokens=T, n_segments=S, n_want=n_want,
             token_ids=cut(0, T), positions=cut(1, T), token_seg=cut(2, T), seg_start=cut(3, S + 1),
             seg_pos0=cut(4, S), seg_slot=cut(5, S), want_rows=cut(6, n_want),
             block_tables=[cut(7 + gi, S * widths[gi]).view(S, widths[gi]) for gi in range(n_groups)],
             feedback=self.next_tokens, status=self.status, seg_lens=seg_lens, seg_pos0_host=pos0, max_q_len=max(seg_lens),
-            max_ctx_len=max(p + n for p, n in zip(pos0, seg_lens)), decode_only=all(n == 1 for n in seg_lens))
+            max_ctx_len=max(p + n for p, n in zip(pos0, seg_lens)), decode_only=all(n == 1 for n in seg_lens),
+            sampling=sampling)
         if entry is not None:
             # a graph's launch shapes must not depend on the step: bound the context by the table width
             ctx.max_ctx_len = max(widths) * cache.page_size if widths else ctx.max_ctx_len
         return ctx, entry
 
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
-        """Runs one batch; returns float32 logits [wanted places, vocab] on the device. With CUDA graphs on, the
-        tensor returned by a decode-only step is reused by the next step of the same shape: read it before."""
+    def _run_model(self, ctx: StepContext) -> torch.Tensor:
+        """The model on the step's tokens; with sampling inputs, the sampling kernel on the logits as well (each
+        token is also left at next_tokens[slot] for a later FEEDBACK_TOKEN)."""
+        logits = self.model.forward(ctx, self.cache_views)
+        sp = ctx.sampling
+        if sp is None or ctx.n_want == 0:
+            return logits
+        if sp.filtered:
+            return ops.sample_filtered(logits, sp.temperature, sp.seed, sp.position, sp.top_k, sp.top_p,
+                                       self.next_tokens, sp.slot)
+        return ops.sample(logits, sp.temperature, sp.seed, sp.position, self.next_tokens, sp.slot)
+
+    def step(self, entries: Sequence[StepEntry], sample=None) -> torch.Tensor:
+        """Runs one batch; returns float32 logits [wanted places, vocab] on the device. With ``sample`` (one
+        (SampleParams, position) per wanted place, in order) the step samples on the device as well and returns
+        int32 token ids [wanted places] instead; each id also stays on the device for its request (FEEDBACK_TOKEN).
+        With CUDA graphs on, the tensor returned by a captured step is reused by the next step of the same shape:
+        read it, or enqueue its copy, before that. Steps may be issued back to back without waiting for the device.
+        Raises OutOfPages (nothing changed) if the pages for all entries together are not free."""
+        return self._step(entries, sample, False).output
+
+    def try_step(self, entries: Sequence[StepEntry], sample=None) -> StepResult:
+        """As ``step``, but an entry that cannot get its pages (after the entries before it have taken theirs) or
+        that would pass the sequence limit is left out instead of failing the call: the others run, the result says
+        which (``ran``), and a request that was left out is untouched (the reference's per-row -1,
+        kernels/batch_gpu.cu:386-410). ``sample`` still has one item per wanted place of ALL entries."""
+        return self._step(entries, sample, True)
+
+    def _step(self, entries, sample, partial: bool) -> StepResult:
         entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
+        empty_dtype = torch.int32 if sample is not None else torch.float32
+        empty_shape = (0,) if sample is not None else (0, self.spec.vocab_size)
         if not entries:
-            return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.rt.device)
+            return StepResult(torch.empty(empty_shape, dtype=empty_dtype, device=self.rt.device), [])
         rids = [e.rid for e in entries]
         if len(set(rids)) != len(rids):
             raise ValueError("a request may appear once in a step")
         for e in entries:
             if e.rid not in self.cache.requests:
                 raise KeyError(f"request {e.rid!r} is not admitted (add_request first)")
+        ran = [True] * len(entries)
+        if partial:
+            taken = []
+            for i, e in enumerate(entries):
+                fits = self.cache.length(e.rid) + len(e.tokens) <= self.max_seq_len
+                if fits and self.cache.can_reserve(taken + [(e.rid, len(e.tokens))]):
+                    taken.append((e.rid, len(e.tokens)))
+                else:
+                    ran[i] = False
+            if sample is not None:
+                keep, w = [], 0
+                for e, ok in zip(entries, ran):
+                    keep += list(sample[w:w + len(e.want)]) if ok else []
+                    w += len(e.want)
+                sample = keep
+            entries = [e for e, ok in zip(entries, ran) if ok]
+            if not entries:
+                return StepResult(torch.empty(empty_shape, dtype=empty_dtype, device=self.rt.device), ran)
         wanted = [(e.rid, len(e.tokens)) for e in entries]
         if not self.cache.can_reserve(wanted):
             raise OutOfPages(f"step needs more pages than are free (free per group: {self.cache.pages_free()})")
@@ -301,39 +411,41 @@ class Engine:
             if not self.cache.reserve(rid, n):
                 raise AssertionError("reserve failed after can_reserve succeeded")
         try:
-            ctx, entry = self._build_context(entries, self.use_graphs)
+            ctx, entry = self._build_context(entries, self.use_graphs, sample)
         except Exception:
-            for rid in rids:
+            for rid, _ in wanted:
                 self.cache.unreserve(rid)
             raise
         with torch.cuda.device(self.rt.device):
             if entry is None:
-                logits = self.model.forward(ctx, self.cache_views)
+                out = self._run_model(ctx)
             elif len(entry.graphs) == entry.copies:
                 # Copies of the graph take turns: launching an executable graph again while its previous launch is
                 # still running is serialised by the driver, which would put the launch cost between two steps.
                 entry.turn = (entry.turn + 1) % entry.copies
-                graph, logits = entry.graphs[entry.turn]
+                graph, out = entry.graphs[entry.turn]
                 graph.replay()
                 ops._LAUNCHES[0] += entry.n_launches
             elif entry.warm < GRAPH_WARMUP_STEPS:
                 # The first steps of a shape run eagerly: they build libraries, size workspaces, set attributes.
                 entry.warm += 1
-                logits = self.model.forward(ctx, self.cache_views)
+                out = self._run_model(ctx)
             else:
                 graph = torch.cuda.CUDAGraph()
                 n0 = ops.kernel_launches()
                 with torch.cuda.graph(graph, pool=self._graph_pool):
-                    logits = self.model.forward(ctx, self.cache_views)
+                    out = self._run_model(ctx)
                 entry.n_launches = ops.kernel_launches() - n0        # kernels of this package inside the graph
                 ops._LAUNCHES[0] = n0
-                entry.graphs.append((graph, logits))
+                entry.graphs.append((graph, out))
                 graph.replay()
                 ops._LAUNCHES[0] += entry.n_launches
         for rid, n in wanted:
             self.cache.advance(rid, n)
         self.steps_run += 1
-        return logits
+        if sample is not None and ctx.n_want == 0:
+            out = torch.empty((0,), dtype=torch.int32, device=self.rt.device)
+        return StepResult(out, ran)
 
     def check_status(self) -> None:
         """Synchronises and raises if a kernel met a page index or token id out of range."""

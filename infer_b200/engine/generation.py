@@ -34,7 +34,7 @@ class GenerationEngine(BatchEngine):
 
     def __init__(self, engine: Engine):
         self.engine = engine
-        self.sampler = Sampler(engine.rt.device)
+        self.sampler = Sampler(engine.rt.device)       # for callers that sample from logits themselves
         self.max_seq_len = engine.max_seq_len
         self.max_requests = engine.cache.n_slots
         self._pinned, self._flip = {}, 0
@@ -71,20 +71,22 @@ class GenerationEngine(BatchEngine):
         once. Every sampled token also stays on the device (engine.next_tokens[slot]); a later decode item may pass
         FEEDBACK_TOKEN instead of the id."""
         entries = [StepEntry(b.rid, b.tokens, [len(b.tokens) - 1] if b.sample is not None else []) for b in batch]
-        slots = {b.rid: self.engine.cache.slot(b.rid) for b in batch if b.sample is not None}
-        logits = self.engine.step(entries)
         rows = [b for b in batch if b.sample is not None]
+        # the sampling kernel's inputs travel in the step's one packed buffer and the kernel runs inside the step
+        # (inside its CUDA graph when the shape is captured): one copy in, one launch, one copy out per step
+        ids = self.engine.step(entries, sample=[(b.sample, b.position) for b in rows])
         if not rows:
             return PendingTokens([], None, None)
-        ids = self.sampler.sample(logits, [b.sample for b in rows], [b.position for b in rows],
-                                  self.engine.next_tokens, [slots[b.rid] for b in rows])
-        self._flip ^= 1
+        # Pinned buffers for the ids take turns (four per batch size): a buffer comes round again only after the
+        # result of the step that used it last has been read, which waits on that step's event.
+        self._flip = (self._flip + 1) % 4
         key = (len(rows), self._flip)
-        host = self._pinned.get(key)
-        if host is None:
-            host = self._pinned[key] = torch.empty(len(rows), dtype=torch.int32).pin_memory()
+        slot = self._pinned.get(key)
+        if slot is None:
+            slot = self._pinned[key] = (torch.empty(len(rows), dtype=torch.int32).pin_memory(), torch.cuda.Event())
+        host, event = slot
+        event.synchronize()                     # the copy that wrote this buffer last has landed (no-op if never used)
         host.copy_(ids, non_blocking=True)
-        event = torch.cuda.Event()
         event.record()
         return PendingTokens([b.rid for b in rows], host, event)
 
@@ -108,16 +110,20 @@ class LLM:
 
     def __init__(self, model: str, dtype="bfloat16", device: str = "cuda:0", slots: int = 8, max_seq: int = 4096,
                  budget_mb: int = 0, max_batch_tokens: int = 512, page_size: int = 16, eos_id: Optional[int] = None,
-                 kernels: Optional[Dict[str, str]] = None, weights=None, spec=None, overlap: bool = True):
-        """slots: live requests; max_seq: per-sequence cap; budget_mb: size of the page pool (0 = reserve
-        slots x max_seq, as the reference does). ``spec`` + ``weights`` may replace the folder."""
+                 kernels: Optional[Dict[str, str]] = None, weights=None, spec=None, overlap: bool = True,
+                 kv_blocks: int = 0):
+        """slots: live requests; max_seq: per-sequence cap; budget_mb: size of the page pool in MiB, or kv_blocks: its
+        size in pages (both 0 = reserve slots x max_seq, as the reference does, kernels/batch_gpu.cu:92-95);
+        max_batch_tokens: the token budget of a step, which is also the largest prompt portion. ``spec`` + ``weights``
+        may replace the folder."""
         from ..config.registry import load_config
         from ..weights.binder import load_weights
         if spec is None:
             arch, typed = load_config(model)
             spec = arch.to_spec(typed)
             weights = load_weights(model, spec)
-        self.engine = Engine(spec, weights, dtype=dtype, device=device, max_tokens=slots * max_seq,
+        self.engine = Engine(spec, weights, dtype=dtype, device=device,
+                             max_tokens=int(kv_blocks) * page_size if kv_blocks else slots * max_seq,
                              max_requests=slots, page_size=page_size, max_seq_len=max_seq, kernels=kernels,
                              cache_budget_bytes=int(budget_mb) << 20)
         self.batch_engine = GenerationEngine(self.engine)

@@ -28,7 +28,6 @@ class DeviceState:
         self._workspace = torch.empty(0, dtype=torch.float32, device=device)
         self._counters = torch.zeros(4096, dtype=torch.int32, device=device)
         self._retired = []
-        self.grid_barrier = torch.zeros(4, dtype=torch.int32, device=device)    # words of linear_chain's grid barrier
 
     def workspace(self, n_floats: int) -> torch.Tensor:
         if self._workspace.numel() < n_floats:
@@ -109,6 +108,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = Non
     f = _fn("gemm", "ib_gemm_tc", [c_void_p] * 5 + [c_int64] * 3 + [c_int] * 5 + [c_void_p] * 4)
     _call(f, x.data_ptr(), w.data_ptr(), _ptr(bias), _ptr(residual), out.data_ptr(), M, N, K, dtype_code(out_dtype),
           2 if swiglu else 0, swap, bn, splits, _ptr(ws), _ptr(cnt), st.status.data_ptr(), _stream())
+    ops.note("gemm_tc:persistent" if bn >= 256 else ("gemm_tc:swapped" if swap else "gemm_tc:one_tile"))
     return out
 
 
@@ -122,9 +122,6 @@ def _prefetch_args(t: Optional[torch.Tensor]):
         return None, 0
     return t.data_ptr(), min(t.numel() * t.element_size(), PREFETCH_MAX_BYTES)
 
-# Which streaming kernel serves up to 16 rows: the one fed by bulk asynchronous copies (gemv_bulk.cu) or the one
-# that loads weights straight into registers (gemv.cu). INFER_B200_GEMV=regs selects the latter.
-GEMV_BULK = os.environ.get("INFER_B200_GEMV", "bulk") != "regs"
 # Decode kernels can ask L2 to fetch the weights of a product that runs two kernels later. Measured on B200 at the
 # 1.5B sizes it does not pay (batch 8: 1.56 ms against 1.55 ms per step, batch 1: 1.76 against 1.42), so it is off;
 # INFER_B200_PREFETCH=1 turns it on.
@@ -135,10 +132,10 @@ def linear_skinny(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor]
                   residual: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16,
                   out: Optional[torch.Tensor] = None, swiglu: bool = False, cluster: int = 0,
                   norm_weight: Optional[torch.Tensor] = None, norm_eps: float = 0.0,
-                  bulk: Optional[bool] = None, prefetch: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+                  prefetch: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
     """The decode kernel: x [M <= 16, K] against w [N, K], weights streamed once; same epilogues as gemm_tc.
-    With ``norm_weight`` x is the float32 residual stream and is RMS-normalised inside the kernel (K <= 1536 in the
-    copy-ring kernel, <= 4096 in the register-streaming one).
+    With ``norm_weight`` x is the float32 residual stream and is RMS-normalised inside the kernel (see
+    ``skinny_fused_norm_max_k``).
     cluster: CTAs sharing one tile's K range (0 = chosen by the kernel). prefetch: a tensor (the weights of a
     product that runs later) that the kernel asks L2 to fetch while it works."""
     fused = norm_weight is not None
@@ -150,11 +147,9 @@ def linear_skinny(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor]
         raise KernelError(f"linear_skinny: x is [{M},{K}] but w is {tuple(w.shape)}")
     if M > SKINNY_MAX_ROWS or K % 8 or (x.data_ptr() & 15) or (w.data_ptr() & 15) or (swiglu and N % 16):
         return None
-    if bulk is None:
-        bulk = GEMV_BULK
     if fused:
         _check(norm_weight, "norm_weight", torch.float32, (K,))
-        if K > (SKINNY_FUSED_NORM_MAX_K if bulk else 4096) or (norm_weight.data_ptr() & 15):
+        if K > SKINNY_FUSED_NORM_MAX_K or (norm_weight.data_ptr() & 15):
             return None
     if bias is not None:
         _check(bias, "bias", torch.float32, (N,))
@@ -169,16 +164,10 @@ def linear_skinny(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor]
     st = device_state(x.device)
     epi = 2 if swiglu else (1 if residual is not None else 0)
     pf_ptr, pf_bytes = _prefetch_args(prefetch)
-    if bulk:
-        f = _fn("gemvb", "ib_linear_skinny_bulk", [c_void_p, c_void_p, c_float] + [c_void_p] * 4 + [c_int64] * 3 + [c_int] * 4 +
-                [c_void_p] * 2 + [c_int64, c_void_p])
-        _call(f, x.data_ptr(), _ptr(norm_weight), float(norm_eps), w.data_ptr(), _ptr(bias), _ptr(residual), out.data_ptr(),
-              M, N, K, dtype_code(out_dtype), epi, int(cluster), st.sm_count, st.status.data_ptr(), pf_ptr, pf_bytes, _stream())
-        return out
-    f = _fn("gemv", "ib_linear_skinny", [c_void_p, c_void_p, c_float] + [c_void_p] * 4 + [c_int64] * 3 + [c_int] * 4 +
-            [c_void_p, c_int64, c_void_p])
+    f = _fn("gemvb", "ib_linear_skinny_bulk", [c_void_p, c_void_p, c_float] + [c_void_p] * 4 + [c_int64] * 3 + [c_int] * 4 +
+            [c_void_p] * 2 + [c_int64, c_void_p])
     _call(f, x.data_ptr(), _ptr(norm_weight), float(norm_eps), w.data_ptr(), _ptr(bias), _ptr(residual), out.data_ptr(),
-          M, N, K, dtype_code(out_dtype), epi, int(cluster), st.sm_count, pf_ptr, pf_bytes, _stream())
+          M, N, K, dtype_code(out_dtype), epi, int(cluster), st.sm_count, st.status.data_ptr(), pf_ptr, pf_bytes, _stream())
     return out
 
 
@@ -277,6 +266,8 @@ def attention_fast(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor
         _call(g, q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), block_table.data_ptr(),
               block_table.shape[1], seg_start.data_ptr(), seg_pos0.data_ptr(), S, T, n_heads, n_kv, head_dim, page_size,
               int(window or 0), float(scale), n_pages, int(max_q_len), st.status.data_ptr(), _stream())
+        if max_q_len > 128:
+            ops.note("attention_prefill_tc:several_query_tiles")
         if not has_decode:
             return out
     f = _fn("attn", "ib_attention_fast", [c_void_p] * 5 + [c_int] + [c_void_p] * 2 + [c_int] * 6 + [c_float, c_int64] +
@@ -341,57 +332,3 @@ def attention(q, cache, table, step, n_heads, n_kv, head_dim, window, scale):
 def gate_up_swiglu(x, gate_up_weight, prefetch=None):
     """silu(x Wg^T) * (x Wu^T) in one kernel; gate_up_weight rows interleaved in blocks of 8."""
     return linear(x, gate_up_weight, None, None, torch.bfloat16, None, swiglu=True, prefetch=prefetch)
-
-
-# ----------------------------------------------------------------------------- chains of skinny products
-
-class _ChainPhase(ctypes.Structure):
-    _fields_ = [("w", c_void_p), ("N", c_int64), ("K", c_int64), ("x_kind", c_int), ("x", c_void_p),
-                ("norm_w", c_void_p), ("eps", c_float), ("epi", c_int), ("bias", c_void_p), ("out", c_void_p)]
-
-
-CHAIN_MAX_PHASES = 4
-CHAIN_MAX_NORM_K = 1536          # a normalised input is held in registers: one stage of K
-CHAIN_X_PLAIN, CHAIN_X_NORM = 0, 1
-CHAIN_EPI_STORE, CHAIN_EPI_RESIDUAL, CHAIN_EPI_SWIGLU = 0, 1, 2
-CHAIN = os.environ.get("INFER_B200_CHAIN", "1") == "1"
-
-
-def chain_phase(w: torch.Tensor, x: torch.Tensor, out: torch.Tensor, epi: int, bias: Optional[torch.Tensor] = None,
-                norm_weight: Optional[torch.Tensor] = None, eps: float = 0.0):
-    """One product of a chain (see linear_chain): ``out = epilogue(f(x) @ w.T)``. x bfloat16 [M, K], or, with
-    ``norm_weight``, the float32 residual stream that is RMS-normalised first. epi: CHAIN_EPI_STORE (+ bias,
-    bfloat16 out), CHAIN_EPI_RESIDUAL (out is the float32 stream, added to in place), CHAIN_EPI_SWIGLU (w's rows
-    are gate/up features interleaved by 8; out bfloat16 [M, N/2]). None if the kernel refuses the sizes."""
-    N, K = w.shape
-    M = x.shape[0]
-    _check(w, "w", torch.bfloat16)
-    if norm_weight is not None:
-        _check(x, "x", torch.float32, (M, K))
-        _check(norm_weight, "norm_weight", torch.float32, (K,))
-        kind = CHAIN_X_NORM
-    else:
-        _check(x, "x", torch.bfloat16, (M, K))
-        kind = CHAIN_X_PLAIN
-    if K % 8 or (kind == CHAIN_X_NORM and K > CHAIN_MAX_NORM_K) or (epi == CHAIN_EPI_SWIGLU and N % 16):
-        return None
-    if (w.data_ptr() & 15) or (x.data_ptr() & 15):
-        return None
-    if epi == CHAIN_EPI_RESIDUAL:
-        _check(out, "out", torch.float32, (M, N))
-    else:
-        _check(out, "out", torch.bfloat16, (M, N // 2 if epi == CHAIN_EPI_SWIGLU else N))
-    if bias is not None:
-        _check(bias, "bias", torch.float32, (N,))
-    return _ChainPhase(w.data_ptr(), N, K, kind, x.data_ptr(), _ptr(norm_weight), float(eps), epi, _ptr(bias), out.data_ptr())
-
-
-def linear_chain(phases, M: int, device) -> None:
-    """Runs up to four skinny products (M <= 16), each reading what the one before wrote, as ONE cooperative kernel
-    with grid barriers between them; the weights of a later product stream in while an earlier one finishes."""
-    if not 0 < len(phases) <= CHAIN_MAX_PHASES or M > SKINNY_MAX_ROWS:
-        raise KernelError(f"linear_chain takes 1..{CHAIN_MAX_PHASES} products of at most {SKINNY_MAX_ROWS} rows")
-    st = device_state(device)
-    arr = (_ChainPhase * len(phases))(*phases)
-    f = _fn("chain", "ib_linear_chain", [c_void_p, c_int, c_int64, c_int, c_void_p, c_void_p, c_void_p])
-    _call(f, ctypes.addressof(arr), len(phases), M, st.sm_count, st.grid_barrier.data_ptr(), st.status.data_ptr(), _stream())

@@ -6,6 +6,7 @@ a library's model code.
 """
 from __future__ import annotations
 
+import collections
 import ctypes
 from typing import Optional
 
@@ -65,6 +66,13 @@ def _fn(module: str, name: str, argtypes, defines=None, restype=c_int):
 
 
 _LAUNCHES = [0]
+# How often each kind of launch was made from the host (a replayed CUDA graph does not pass here): tests read it to
+# assert that the kernel they mean to cover is the one that ran. Launchers add kinds of their own with ``note``.
+LAUNCH_KINDS = collections.Counter()
+
+
+def note(kind: str) -> None:
+    LAUNCH_KINDS[kind] += 1
 
 
 def kernel_launches() -> int:
@@ -74,6 +82,7 @@ def kernel_launches() -> int:
 
 def _call(f, *args) -> None:
     _LAUNCHES[0] += 1
+    LAUNCH_KINDS[f.__name__] += 1
     rc = f(*args)
     if rc != 0:
         msg = f._lib.ib_last_error()

@@ -43,17 +43,20 @@ class Sampler:
             top_p[i] = float(getattr(p, "top_p", 1.0))
             if temp[i] > 0 and (host[i, 2] > 0 or top_p[i] < 1.0):
                 filtered = True
-        # one pinned staging buffer per batch size and parity, reused step after step
+        # two pinned staging buffers per batch size take turns; the event says when the copies out of one have run,
+        # and is waited for before the buffer is written again
         self._flip ^= 1
         key = (B, self._flip)
         stage = self._pinned.get(key)
         if stage is None:
             stage = self._pinned[key] = (torch.empty((B, 4), dtype=torch.int64).pin_memory(),
-                                         torch.empty(B, dtype=torch.float32).pin_memory())
+                                         torch.empty(B, dtype=torch.float32).pin_memory(), torch.cuda.Event())
+        stage[2].synchronize()
         stage[0].numpy()[:] = host
         stage[1].numpy()[:] = temp
         ints = stage[0].to(self.device, non_blocking=True)
         t = stage[1].to(self.device, non_blocking=True)
+        stage[2].record()
         self.last_h2d_bytes = host.nbytes + temp.nbytes
         seed, step = ints[:, 0].contiguous(), ints[:, 1].contiguous()
         fb = feedback if slots is not None else None

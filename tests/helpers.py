@@ -13,11 +13,11 @@ import plain_model as pm
 
 # Three tiny configurations of the architecture that differ in every size and option.
 TINY: Dict[str, dict] = {
-    # BASELINE "tiny A": tied head, 2:1 grouping, float32 weights
+    # tiny A: tied head, 2:1 grouping, float32 weights
     "a": dict(architectures=["Qwen2ForCausalLM"], hidden_size=64, num_hidden_layers=2, num_attention_heads=4,
               num_key_value_heads=2, intermediate_size=128, vocab_size=256, rope_theta=10000.0, rms_norm_eps=1e-6,
               max_position_embeddings=1024, tie_word_embeddings=True, use_sliding_window=False),
-    # BASELINE "tiny B": untied head, 3:1 grouping, one kv head, sizes that are no power of two
+    # tiny B: untied head, 3:1 grouping, one kv head, sizes that are no power of two
     "b": dict(architectures=["Qwen2ForCausalLM"], hidden_size=96, num_hidden_layers=3, num_attention_heads=3,
               num_key_value_heads=1, intermediate_size=224, vocab_size=320, rope_theta=1000000.0, rms_norm_eps=1e-5,
               max_position_embeddings=2048, tie_word_embeddings=False, use_sliding_window=False),

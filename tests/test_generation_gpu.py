@@ -112,3 +112,29 @@ def test_overlap_and_plain_scheduling_generate_the_same(dtype):
     stop = full[1][5]
     assert a.generate(prompts[:2], max_new=16, eos_id=stop) == b.generate(prompts[:2], max_new=16, eos_id=stop)
     assert b.engine.cache.pages_in_use() == [0]
+
+
+def test_overlap_with_few_pages_preempts_while_a_token_is_in_flight():
+    """Overlap scheduling on a pool of 9 pages for four requests that need 16: requests are preempted while the last
+    step's tokens are still on their way to the host (they are read before the victim's new prompt is made), and a
+    decode item after that reads its token from the device. In float32 the streams are those of the one-step-at-a-time
+    scheduler with room for everything; in bfloat16 every request still ends with all its tokens and no page is lost."""
+    name = "a"
+    cfg = H.TINY[name]
+    prompts = [H.random_ids(cfg, 20, 400 + i) for i in range(4)]
+    for kw in (dict(max_new=30, temperature=0.7, seed=5), dict(max_new=30)):
+        free = _llm(name, torch.float32, max_seq=64, overlap=False).generate(prompts, **kw)
+        tight = _llm(name, torch.float32, max_seq=64, kv_blocks=9, overlap=True)
+        assert tight.engine.cache.pages_total() == [9]
+        got = tight.generate(prompts, **kw)
+        sch = tight.last_scheduler
+        assert sch.preemptions > 0
+        assert got == free
+        assert tight.engine.cache.pages_in_use() == [0]
+        tight.engine.cache.check_invariants()
+        tight.engine.check_status()
+    fast = _llm(name, torch.bfloat16, max_seq=64, kv_blocks=9, overlap=True)
+    outs = fast.generate(prompts, max_new=30)
+    assert fast.last_scheduler.preemptions > 0 and [len(o) for o in outs] == [30] * 4
+    assert fast.engine.cache.pages_in_use() == [0]
+    fast.engine.check_status()

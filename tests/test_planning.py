@@ -63,3 +63,34 @@ def test_decode_attention_slices_and_clusters():
     assert 2 * 8 * c <= 2 * SMS and (30000 // 16) // (8 * c) >= fast_ops.ATTENTION_CLUSTER_PAGES
     assert fast_ops._decode_splits(st, 8, 2, 30000) == (8, 2)     # 128 CTAs already: at most two per SM
     assert fast_ops._decode_scratch(st, 8, 2, 128, 1) == (None, None)
+
+
+def test_every_plan_that_the_no_alloc_entry_point_accepts_fits_its_array():
+    """ib_gemm_tc_static hands its built-in array (8 MiB: 4096 counters, then partial tiles) to the kernel exactly
+    when the plan sums K slices through global memory, and refuses when the plan's figures exceed the array. So for
+    every shape the plan's figures must be the kernel's true need (slices x tiles x 128 x bn floats, one counter per
+    tile), and the plans that add their slices in shared memory must state no need at all. Swept over the products
+    of the 1.5B, 7B and 14B layer sizes for 17..4096 rows, and a few odd shapes."""
+    room_floats = ((8 << 20) - 4096 * 4) // 4
+    widths = [(1536, 2048), (1536, 1536), (1536, 17920), (8960, 1536),            # (K, N) of q/k/v, o, gate/up, down
+              (3584, 4608), (3584, 3584), (3584, 37888), (18944, 3584),
+              (5120, 7168), (5120, 5120), (5120, 27648), (13824, 5120),
+              (4096, 136), (1536, 300), (1024, 256), (16384, 768)]
+    rows = list(range(17, 130)) + list(range(130, 1025, 37)) + [1024, 2048, 3000, 4096]
+    reached = 0
+    for K, N in widths:
+        for M in rows:
+            plan = _plan(M, N, K)
+            assert plan is not None
+            swap, bn, splits, ws, counters = plan
+            if ws == 0:
+                assert counters == 0
+                # no scratch: one slice, or slices that form a cluster (at most 8; plain mapping 2, 4 or 8)
+                assert splits == 1 or (splits <= 8 and (swap or splits in (2, 4, 8)))
+                continue
+            assert not swap and bn == 128 and splits > 1
+            tiles = -(-M // 128) * -(-N // bn)
+            assert ws == splits * tiles * 128 * bn and counters == tiles
+            if ws <= room_floats and counters <= 4096:
+                reached += 1                                          # accepted: it fits by the same comparison
+    assert reached > 0

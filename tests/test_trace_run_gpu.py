@@ -14,14 +14,14 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 SEED = 9
 
 
-def _replay(tmp_path, name, dtype, steps, max_tokens):
+def _replay(tmp_path, name, dtype, steps, max_tokens, fmt=None):
     from infer_b200.weights import write_random_model
     model = tmp_path / "model"
     write_random_model(str(model), H.TINY[name], SEED, H.STORED_DTYPE[name])
     out = tmp_path / f"out_{dtype}"
     proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", str(model), "--dtype", dtype,
-                           "--out", str(out), "--max-tokens", str(max_tokens)], input=H.trace_to_jsonl(steps),
-                          capture_output=True, text=True, timeout=600)
+                           "--out", str(out), "--max-tokens", str(max_tokens)] + (["--format", fmt] if fmt else []),
+                          input=H.trace_to_jsonl(steps), capture_output=True, text=True, timeout=600)
     assert proc.returncode == 0, proc.stderr[-2000:]
     assert [l for l in proc.stdout.splitlines() if l.startswith("done ")] == [f"done {i}" for i in range(len(steps))]
     V = H.TINY[name]["vocab_size"]
@@ -35,6 +35,9 @@ def _replay(tmp_path, name, dtype, steps, max_tokens):
                 pos[rid] = pos.get(rid, 0) + len(toks)
             continue
         arr = np.fromfile(path, dtype="<f4").reshape(n_want, V)
+        if fmt == "both":
+            saved = np.load(out / f"{i}.npy")
+            assert saved.dtype == np.float32 and saved.shape == (n_want, V) and np.array_equal(saved, arr)
         r = 0
         for rid, toks, want in st["entries"]:
             for w in want:
@@ -70,7 +73,7 @@ def test_whole_and_tail_agree_through_the_program(tmp_path):
     name = "c"
     ids = {"x": H.random_ids(H.TINY[name], 90, 700)}
     a = _replay(tmp_path, name, "float32", H.trace_whole(ids), 128)["x"]
-    b = _replay(tmp_path, name, "float32", H.trace_tail(ids, 32), 128)["x"]
+    b = _replay(tmp_path, name, "float32", H.trace_tail(ids, 32), 128, fmt="both")["x"]
     ref = H.oracle(H.TINY[name], SEED, H.STORED_DTYPE[name], torch.float32, ids["x"])
     for p in b:
         assert np.array_equal(a[p], b[p])

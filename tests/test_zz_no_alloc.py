@@ -24,33 +24,67 @@ def _static_fn():
     return lib, f
 
 
-# shapes whose plan cuts K into slices (they use the built-in scratch) and one that does not
-@pytest.mark.parametrize("M,N,K", [(8, 1536, 1536), (64, 1536, 8960), (40, 300, 2048), (300, 512, 1536), (1024, 2048, 256)])
-def test_static_entry_point_matches_the_regular_one(M, N, K):
-    from infer_b200 import fast_ops
-    lib, f = _static_fn()
-    st = fast_ops.device_state(DEV)
+# Shapes whose K slices are summed through global memory: these are the ones that read and write the built-in array
+# (the plan states how many floats). Both calls are compared with a float64 product, so a wrong address, size or
+# counter offset shows; the second call meets the partial tiles and counters that the first one left.
+SCRATCH_SHAPES = [(300, 300, 1536), (200, 136, 4096), (300, 256, 1024)]
+# Shapes that need none of it: up to 128 rows and clusters of slices meet in shared memory, large ones are not cut.
+OTHER_SHAPES = [(8, 1536, 1536), (64, 1536, 8960), (40, 300, 2048), (300, 512, 1536), (1024, 2048, 256)]
+
+
+def _inputs(M, N, K):
     g = torch.Generator(device=DEV).manual_seed(M + N + K)
     x = torch.randn(M, K, device=DEV, generator=g).bfloat16()
     w = (torch.randn(N, K, device=DEV, generator=g) * 0.05).bfloat16()
     bias = torch.randn(N, device=DEV, generator=g)
     res = torch.randn(M, N, device=DEV, generator=g)
-    want = fast_ops.gemm_tc(x, w, bias, res.clone(), torch.float32)
+    return x, w, bias, res
+
+
+def _call_static(lib, f, st, x, w, bias, out):
+    M, K = x.shape
+    base = torch.cuda.memory_allocated()
+    rc = f(x.data_ptr(), w.data_ptr(), bias.data_ptr(), out.data_ptr(), out.data_ptr(), M, w.shape[0], K, 0, st.sm_count,
+           st.status.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert rc == 0, lib.ib_last_error().decode()
+    torch.cuda.synchronize()
+    assert torch.cuda.memory_allocated() == base, "the call allocated through torch"
+    assert st.status.item() == 0
+
+
+@pytest.mark.parametrize("M,N,K", SCRATCH_SHAPES)
+def test_static_entry_point_sums_its_slices_in_the_built_in_array(M, N, K):
+    from infer_b200 import fast_ops
+    lib, f = _static_fn()
+    st = fast_ops.device_state(DEV)
+    plan = fast_ops.gemm_plan(M, N, K, st.sm_count)
+    assert plan is not None and plan[2] > 1 and plan[3] > 0, f"this shape no longer reaches the scratch array: plan {plan}"
+    assert plan[3] * 4 <= (8 << 20) - 16384
+    x, w, bias, res = _inputs(M, N, K)
+    exact = x.double() @ w.double().T + bias.double() + res.double()
     cond = x.float().abs() @ w.float().abs().T + 1.0
-    stream = torch.cuda.current_stream().cuda_stream
-    before = torch.cuda.memory_allocated()
+    regular = fast_ops.gemm_tc(x, w, bias, res.clone(), torch.float32)
     for call in range(2):
         out = res.clone()                       # the residual is added in place, as the engine does
-        base = torch.cuda.memory_allocated()
-        rc = f(x.data_ptr(), w.data_ptr(), bias.data_ptr(), out.data_ptr(), out.data_ptr(), M, N, K, 0, st.sm_count,
-               st.status.data_ptr(), stream)
-        assert rc == 0, lib.ib_last_error().decode()
-        torch.cuda.synchronize()
-        assert torch.cuda.memory_allocated() == base, "the call allocated through torch"
-        assert st.status.item() == 0
-        assert ((out - want).abs() / cond).max().item() < 2e-6, f"call {call}"
-    del out
-    assert torch.cuda.memory_allocated() <= before + res.numel() * 4
+        _call_static(lib, f, st, x, w, bias, out)
+        assert ((out.double() - exact).abs() / cond).max().item() < 2e-6, f"call {call} against float64"
+        assert ((out - regular).abs() / cond).max().item() < 2e-6, f"call {call} against the regular entry point"
+
+
+@pytest.mark.parametrize("M,N,K", OTHER_SHAPES)
+def test_static_entry_point_matches_the_regular_one(M, N, K):
+    from infer_b200 import fast_ops
+    lib, f = _static_fn()
+    st = fast_ops.device_state(DEV)
+    plan = fast_ops.gemm_plan(M, N, K, st.sm_count)
+    assert plan is not None and plan[3] == 0
+    x, w, bias, res = _inputs(M, N, K)
+    want = fast_ops.gemm_tc(x, w, bias, res.clone(), torch.float32)
+    for call in range(2):
+        out = res.clone()
+        _call_static(lib, f, st, x, w, bias, out)
+        # without a workspace both entry points add the slices in the same fixed order: the same bits
+        assert torch.equal(out, want), f"call {call}"
 
 
 def test_static_entry_point_refuses_what_does_not_fit():
@@ -58,8 +92,6 @@ def test_static_entry_point_refuses_what_does_not_fit():
     from infer_b200 import fast_ops
     st = fast_ops.device_state(DEV)
     # a GPU reported as huge against few tiles: 12 tiles x 16 slices x 128 x 128 floats = 12.6 MB through the workspace
-    # (products of up to 128 rows, and larger ones whose slices fill the GPU in clusters of 2, 4 or 8, need no scratch
-    # at all: their slices meet in the cluster's shared memory)
     M, N, K = 256, 768, 16384
     plan = fast_ops.gemm_plan(M, N, K, 1000)
     assert plan[2] > 1 and plan[3] * 4 > (8 << 20) - 16384
