@@ -23,18 +23,15 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# The benchmark configuration: Qwen2.5-1.5B layer sizes, random weights
-CONFIG = dict(architectures=["Qwen2ForCausalLM"], hidden_size=1536, num_hidden_layers=28, num_attention_heads=12,
-              num_key_value_heads=2, intermediate_size=8960, vocab_size=151936, rope_theta=1000000.0, rms_norm_eps=1e-6,
-              max_position_embeddings=32768, tie_word_embeddings=True, use_sliding_window=False)
-# Further layer sizes of the same architecture (--sizes): Qwen2.5-7B and 14B. The default stays the 1.5B sizes.
-SIZES = {
-    "1.5b": CONFIG,
-    "7b": dict(CONFIG, hidden_size=3584, num_attention_heads=28, num_key_value_heads=4, intermediate_size=18944,
-               vocab_size=152064, tie_word_embeddings=False),
-    "14b": dict(CONFIG, hidden_size=5120, num_hidden_layers=48, num_attention_heads=40, num_key_value_heads=8,
-                intermediate_size=13824, vocab_size=152064, rms_norm_eps=1e-5, tie_word_embeddings=False),
-}
+# The benchmark configurations are the config.json presets of the package (no weights): Qwen2.5-1.5B layer sizes by
+# default, 7B and 14B with --sizes.
+def _preset(name):
+    with open(os.path.join(ROOT, "infer_b200", "models", "presets", name + ".json")) as f:
+        return json.load(f)
+
+
+SIZES = {"1.5b": _preset("qwen2.5-1.5b"), "7b": _preset("qwen2.5-7b"), "14b": _preset("qwen2.5-14b")}
+CONFIG = SIZES["1.5b"]
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -152,8 +149,10 @@ def decode_bytes(eng, batch, context_mid):
     spec = eng.spec
     w = eng.model.weight_bytes()
     item = 2 if str(eng.rt.dtype).endswith("bfloat16") else 4
-    if spec.head_name is not None:
-        w -= spec.vocab_size * spec.hidden_size * item - batch * spec.hidden_size * item
+    table = eng.model.embedding.table()
+    head_w = getattr(getattr(eng.model.head, "linear", None), "weight", None)
+    if table is not None and (head_w is None or head_w.data_ptr() != table.data_ptr()):
+        w -= table.numel() * item - batch * spec.hidden_size * item         # an untied table is read row by row only
     kv = sum(2 * len(g.cache_ids) * g.need.num_kv_heads * g.need.head_dim * item for g in eng.cache.groups)
     return w + batch * context_mid * kv, w, kv
 
@@ -206,6 +205,43 @@ def time_prefill(eng, tokens, reps, warmup):
     return times[len(times) // 2]
 
 
+def serve_workload(eng, n_requests, len_lo, len_hi, max_new, chunk, seed=0):
+    """Continuous batching through the scheduler of the Python entry point: `n_requests` requests, all submitted at
+    once, with seeded random prompt lengths in [len_lo, len_hi] and `max_new` generated tokens each, prompts cut into
+    portions of at most `chunk` tokens beside the decode tokens of the running requests. Host token ids in, sampled
+    host token ids out. Wall clock around the whole run, synchronised on both sides."""
+    import numpy as np
+    import torch
+    from infer_b200.engine.generation import GenerationEngine
+    from infer_b200.engine.scheduler import Request, SampleParams, Scheduler, SchedulerConfig
+    ge = GenerationEngine(eng)
+    rng = np.random.default_rng(seed)
+    V = eng.spec.vocab_size
+    warm = Scheduler(ge, SchedulerConfig(eos_id=-1, max_batch_tokens=chunk, overlap=True))
+    for r in range(2):
+        warm.submit(Request(("warm", r), rng.integers(0, V, 3 * chunk // 2 + r).tolist(), 8, 0, SampleParams()))
+    warm.run_until_idle()
+    lengths = rng.integers(len_lo, len_hi + 1, n_requests)
+    sch = Scheduler(ge, SchedulerConfig(eos_id=-1, max_batch_tokens=chunk, overlap=True))
+    for r, n in enumerate(lengths):
+        sch.submit(Request(r, rng.integers(0, V, int(n)).tolist(), max_new, 0, SampleParams()))
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    sch.run_until_idle()
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    eng.check_status()
+    generated = sum(len(c.tokens) for c in sch.completed)
+    lat = sorted(c.finished_ms for c in sch.completed)
+    ttft = sorted(c.first_token_ms for c in sch.completed)
+    return {"requests": n_requests, "prompt_tokens": int(lengths.sum()), "generated_tokens": generated,
+            "wall_s": round(wall, 3), "generated_tok_s": round(generated / wall, 1),
+            "total_tok_s": round((int(lengths.sum()) + generated) / wall, 1), "steps": sch.steps,
+            "ms_per_step": round(wall * 1e3 / max(1, sch.steps), 3), "preemptions": sch.preemptions,
+            "request_p50_ms": round(lat[len(lat) // 2], 1), "ttft_p50_ms": round(ttft[len(ttft) // 2], 1),
+            "chunk": chunk, "prompt_lengths": [int(len_lo), int(len_hi)], "max_new": max_new}
+
+
 def prefill_flops(cfg, n_layers, T):
     H, nh, nkv, hd, I, V = (cfg["hidden_size"], cfg["num_attention_heads"], cfg["num_key_value_heads"],
                             cfg["hidden_size"] // cfg["num_attention_heads"], cfg["intermediate_size"], cfg["vocab_size"])
@@ -229,8 +265,10 @@ def time_e2e(eng, batch, context, steps, warmup):
     sch = Scheduler(ge, SchedulerConfig(eos_id=-1, max_batch_tokens=2048, overlap=True,
                                         on_token=lambda rid, tok: got.append(tok)))
     rng = np.random.default_rng(1)
+    # requests whose prompts end early decode while the others' prompts still run: room for those tokens too
+    prompt_steps = -(-batch * context // 2048) + batch
     for r in range(batch):
-        sch.submit(Request(r, rng.integers(0, eng.spec.vocab_size, context).tolist(), warmup + steps + 8, 0, SampleParams()))
+        sch.submit(Request(r, rng.integers(0, eng.spec.vocab_size, context).tolist(), warmup + steps + 8 + prompt_steps, 0, SampleParams()))
     while sch.queue or any(not a.decoding for a in sch.active.values()):
         sch.step()
     for _ in range(warmup):
@@ -330,6 +368,12 @@ def main():
     ap.add_argument("--sizes", default="1.5b", choices=sorted(SIZES), help="layer sizes: Qwen2.5-1.5B (the default), 7B or 14B")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
+    ap.add_argument("--points", default="1,64", help="batch sizes of the further decode points (default 1,64)")
+    ap.add_argument("--workload", default="decode", choices=["decode", "serve"],
+                    help="serve: 64 requests with prompts of 128..4096 tokens and 128 new tokens each under continuous "
+                         "batching with prompt portions of 512 (the 7B measurement workload); prints its own line")
+    ap.add_argument("--requests", type=int, default=64, help="serve: number of requests")
+    ap.add_argument("--chunk", type=int, default=512, help="serve: token budget of a step")
     ap.add_argument("--mode", default="all", choices=["all", "decode", "prefill"],
                     help="decode / prefill: run only that part and print a short line (for profiling small cases)")
     args = ap.parse_args()
@@ -346,8 +390,18 @@ def main():
     pk = peaks()
     n_layers = args.layers or CONFIG["num_hidden_layers"]
     total_steps = args.steps + args.warmup
-    eng = build_engine(n_layers, max(64, args.batch), args.context, 2 * total_steps + 64)
     cfg = CONFIG
+    if args.workload == "serve":
+        lo, hi, max_new = 128, 4096, 128
+        # the pool holds every request at once (the 7B sizes take 57 KB per position: 15 GB for 64 requests)
+        eng = build_engine(n_layers, args.requests, hi, max_new + 64)
+        rec = serve_workload(eng, args.requests, lo, hi, max_new, args.chunk)
+        rec.update(workload="serve", model=f"Qwen2.5-{args.sizes.upper()} sizes", layers=n_layers,
+                   layers_of_model=CONFIG["num_hidden_layers"], slots=args.requests, dtype="bf16")
+        print(json.dumps(rec))
+        return 0
+    point_batches = [] if args.no_points else [int(b) for b in args.points.split(",") if b]
+    eng = build_engine(n_layers, max([args.batch] + point_batches), args.context, 2 * total_steps + 64)
 
     if args.mode == "decode":
         ms_step, launches = time_decode(eng, args.batch, args.context, args.steps, args.warmup, ops.kernel_launches)
@@ -387,10 +441,14 @@ def main():
                         "frac": round(achieved / pk["hbm_gbs"], 4)}}
     if not args.no_points:
         points = {}
-        for b in (1, 64):
-            ms_b, _ = time_decode(eng, b, args.context, max(16, args.steps // 2), args.warmup, ops.kernel_launches)
+        fracs = {}
+        for b in point_batches:
+            n_b = max(16, args.steps // 2)
+            ms_b, _ = time_decode(eng, b, args.context, n_b, args.warmup, ops.kernel_launches)
             points[f"decode_b{b}"] = round(b * 1e3 / ms_b, 1)
+            fracs[f"decode_b{b}"] = round(decode_bytes(eng, b, args.context + args.warmup + n_b // 2)[0] / (ms_b * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
         out["points"] = points
+        out["points_roofline_frac"] = fracs
         T = 2048
         ms_p = time_prefill(eng, T, 5, 3)
         fl = prefill_flops(cfg, n_layers, T)

@@ -85,8 +85,7 @@ def main(argv=None) -> int:
         spec = arch.to_spec(typed)
         # the values of write_random_model (drawn on the CPU from (seed, tensor name)); models beyond two billion
         # parameters are drawn on the device instead, which is faster and gives another stream of numbers
-        n_params = spec.vocab_size * spec.hidden_size * (1 if spec.head_name is None else 2) + \
-            sum(int(torch.Size(shape).numel()) for shape, *_ in expected_tensors(spec).values() if len(shape) == 2 and shape[0] != spec.vocab_size)
+        n_params = sum(int(torch.Size(shape).numel()) for shape, *_ in expected_tensors(spec).values())
         weights = random_weights(spec, args.weights_seed, torch.bfloat16, device="cuda" if n_params > 2e9 else "cpu")
         args.max_seq = min(args.max_seq, spec.max_positions)
         args.model = f"random:{args.random} (weights seed {args.weights_seed})"

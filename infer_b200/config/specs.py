@@ -9,7 +9,7 @@ checkpoint stores the part's parameters.
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Any, Mapping, Optional, Sequence
+from typing import Any, Iterator, Mapping, Optional, Sequence, Tuple
 
 
 @dataclass(frozen=True)
@@ -31,14 +31,35 @@ class PartSpec:
         return self.params.get(key, default)
 
 
+# The families a part can belong to; each has its own registry of kinds (``parts.base``).
+FAMILIES = ("mixer", "feed_forward", "norm", "position", "block", "embedding", "head")
+
+
 @dataclass(frozen=True)
 class LayerSpec:
-    """One layer: which parts it is made of and how they are arranged (``block`` kind)."""
-    block: str                       # registered block arrangement, e.g. "prenorm"
-    mixer: PartSpec
-    feed_forward: PartSpec
-    mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
+    """One layer: a block arrangement (``block`` kind) and the parts it arranges.
+
+    parts maps a slot name, which the block class defines, to (family, PartSpec), in the order in which the block
+    runs them. The framework does not know the slot names: it builds, loads and binds whatever the mapping holds,
+    and hands the built parts to the block class by slot name. A block with a third norm, without a feed-forward,
+    or with two mixers is another block class and another mapping, not another framework."""
+    block: str
+    parts: Mapping[str, Tuple[str, PartSpec]]
+
+    def __post_init__(self):
+        for slot, fp in self.parts.items():
+            if not (isinstance(fp, tuple) and len(fp) == 2 and fp[0] in FAMILIES and isinstance(fp[1], PartSpec)):
+                raise ValueError(f"layer slot {slot!r} must map to (family, PartSpec), got {fp!r}")
+
+    @classmethod
+    def standard(cls, block: str, mixer: PartSpec, feed_forward: PartSpec, mixer_norm: PartSpec,
+                 feed_forward_norm: PartSpec) -> "LayerSpec":
+        """The usual four slots: a norm before the mixer, the mixer, a norm before the feed-forward, the feed-forward."""
+        return cls(block, {"mixer_norm": ("norm", mixer_norm), "mixer": ("mixer", mixer),
+                           "feed_forward_norm": ("norm", feed_forward_norm), "feed_forward": ("feed_forward", feed_forward)})
+
+    def part(self, slot: str) -> PartSpec:
+        return self.parts[slot][1]
 
 
 @dataclass(frozen=True)
@@ -65,9 +86,17 @@ class ModelSpec:
     layers: Sequence[LayerSpec]
     schedule: Sequence[LayerCall]
     final_norm: PartSpec
-    embedding_name: str              # checkpoint name of the token table [vocab, hidden]
-    head_name: Optional[str]         # checkpoint name of the output matrix; None = tied to the table
+    embedding: PartSpec              # family "embedding": token ids -> float32 rows of the residual stream
+    head: PartSpec                   # family "head": normalised rows -> float32 logits; may be tied to the embedding
     eos_token_id: Optional[int] = None
+
+    def part_specs(self) -> Iterator[Tuple[str, PartSpec]]:
+        """Every (family, PartSpec) of the model: embedding, head, final norm, then the layers' parts in order."""
+        yield "embedding", self.embedding
+        yield "head", self.head
+        yield "norm", self.final_norm
+        for layer in self.layers:
+            yield from layer.parts.values()
 
     def validate(self) -> None:
         if self.hidden_size <= 0 or self.vocab_size <= 0 or self.max_positions <= 0:

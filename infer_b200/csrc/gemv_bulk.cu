@@ -477,6 +477,14 @@ int launch(const GemvParams& p, int out_dtype, int epi, int grid_ctas, cudaStrea
 // each CTA once for all its tiles (K <= 1536). epi: 0 = (+ bias), 1 = (+ bias) + residual -> float, 2 = SwiGLU over rows interleaved by 8 ->
 // bfloat16 [M, N/2]. cluster: CTAs that share a tile's K range (1, 2, 4 or 8); 0 lets the kernel choose from N, K and
 // sm_count. status: one int in device memory, raised if a bounded wait runs out.
+// What this kernel takes: the most rows of activations, and the longest row that the fused RMSNorm prologue
+// normalises in registers. Callers plan with these figures instead of carrying copies of them.
+IB_EXPORT int ib_linear_skinny_bulk_limits(int* max_rows, int* max_fused_norm_k) {
+    if (max_rows) *max_rows = ROWS;
+    if (max_fused_norm_k) *max_fused_norm_k = KC_MAX;
+    return IB_OK;
+}
+
 IB_EXPORT int ib_linear_skinny_bulk(const void* x, const float* norm_w, float norm_eps, const void* w, const float* bias, const float* residual, void* out,
                                     int64_t M, int64_t N, int64_t K, int out_dtype, int epi, int cluster, int sm_count,
                                     int* status, const void* prefetch, int64_t prefetch_bytes, cudaStream_t stream) {

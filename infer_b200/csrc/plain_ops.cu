@@ -14,6 +14,7 @@
 // cache write), kernels/ops/batch.cu:250-316 (attention over a block table),
 // kernels/ops/elementwise.cu:6-16, kernels/ops/batch.cu:450-478 (sampling).
 #include "common.cuh"
+#include <cooperative_groups.h>
 
 IB_DEFINE_LAST_ERROR()
 
@@ -29,14 +30,14 @@ namespace {
 using bf16 = __nv_bfloat16;
 
 // ------------------------------------------------------------------------------------------------
-// Embedding: out[t, :] = float(table[ids[t], :]). Ids are validated on the host; an id outside the
+// Embedding: out[t, :] = float(table[ids[t], :]) * scale (scale 1 for architectures without one). Ids are validated on the host; an id outside the
 // table writes zeros and raises the status word rather than reading out of bounds. An id of -1 stands for "the
 // token sampled last for this request", which the sampling kernel left in feedback[slot of the request].
 template <typename T>
 __global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids, int64_t n_tokens,
                                  int64_t hidden, int64_t vocab, float* __restrict__ out, int* status,
                                  const int* __restrict__ feedback, const int* __restrict__ token_seg,
-                                 const int* __restrict__ seg_slot) {
+                                 const int* __restrict__ seg_slot, float scale) {
     ib::pdl_wait();
     const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
     if (i >= n_tokens * hidden) return;
@@ -49,7 +50,8 @@ __global__ void embedding_kernel(const T* __restrict__ table, const int* __restr
         if (status) atomicExch(status, 1);
         return;
     }
-    out[i] = ib::to_f32(table[int64_t(id) * hidden + c]);
+    const float v = ib::to_f32(table[int64_t(id) * hidden + c]);
+    out[i] = scale == 1.0f ? v : v * scale;
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -410,13 +412,25 @@ __device__ __forceinline__ float hash_uniform(uint64_t seed, uint64_t step, uint
     return (float((x >> 40) & 0xFFFFFF) + 0.5f) / 16777216.0f;
 }
 
-__global__ void sample_kernel(const float* __restrict__ logits, int64_t vocab, const float* __restrict__ temperature,
-                              const int64_t* __restrict__ seed, const int64_t* __restrict__ step,
-                              int* __restrict__ out, int* feedback, const int64_t* __restrict__ slots) {
+// A row is shared by a thread-block cluster of SAMPLE_CLUSTER CTAs (each takes a contiguous slice of the vocabulary);
+// every CTA leaves its best (value, index) in the first CTA's shared memory, which picks among them. The maximum
+// with ties to the lowest index is the same in whatever order the candidates meet.
+constexpr int SAMPLE_CLUSTER = 8;
+constexpr int SAMPLE_THREADS = 512;
+
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+sample_kernel(const float* __restrict__ logits, int64_t vocab, const float* __restrict__ temperature,
+              const int64_t* __restrict__ seed, const int64_t* __restrict__ step,
+              int* __restrict__ out, int* feedback, const int64_t* __restrict__ slots) {
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    __shared__ float sv[SAMPLE_THREADS / 32];
+    __shared__ int si[SAMPLE_THREADS / 32];
+    __shared__ float cv[SAMPLE_CLUSTER];                    // candidates of the cluster's CTAs (used in the first CTA)
+    __shared__ int ci[SAMPLE_CLUSTER];
+    const int rank = int(cluster.block_rank());
+    const int b = blockIdx.x / SAMPLE_CLUSTER;
     ib::pdl_wait();
-    __shared__ float sv[1024];
-    __shared__ int si[1024];
-    const int b = blockIdx.x;
     const float* row = logits + int64_t(b) * vocab;
     const float T = temperature[b];
     const uint64_t sd = uint64_t(seed[b]), stp = uint64_t(step[b]);
@@ -429,37 +443,54 @@ __global__ void sample_kernel(const float* __restrict__ logits, int64_t vocab, c
     if ((vocab & 3) == 0) {
         // rows are 16-byte aligned: four logits per load, two loads in flight per thread
         const float4* row4 = reinterpret_cast<const float4*>(row);
-        const int64_t n4 = vocab >> 2;
-        int64_t i = threadIdx.x;
-        for (; i + blockDim.x < n4; i += 2 * blockDim.x) {
+        const int64_t n4 = vocab >> 2, per = (n4 + SAMPLE_CLUSTER - 1) / SAMPLE_CLUSTER;
+        const int64_t lo = per * rank, hi = lo + per < n4 ? lo + per : n4;
+        int64_t i = lo + threadIdx.x;
+        for (; i + blockDim.x < hi; i += 2 * blockDim.x) {
             const float4 a = row4[i], c = row4[i + blockDim.x];
             take(a.x, 4 * i); take(a.y, 4 * i + 1); take(a.z, 4 * i + 2); take(a.w, 4 * i + 3);
             const int64_t j = i + blockDim.x;
             take(c.x, 4 * j); take(c.y, 4 * j + 1); take(c.z, 4 * j + 2); take(c.w, 4 * j + 3);
         }
-        if (i < n4) {
+        if (i < hi) {
             const float4 a = row4[i];
             take(a.x, 4 * i); take(a.y, 4 * i + 1); take(a.z, 4 * i + 2); take(a.w, 4 * i + 3);
         }
     } else {
-        for (int64_t v = threadIdx.x; v < vocab; v += blockDim.x) take(row[v], v);
+        const int64_t per = (vocab + SAMPLE_CLUSTER - 1) / SAMPLE_CLUSTER;
+        const int64_t lo = per * rank, hi = lo + per < vocab ? lo + per : vocab;
+        for (int64_t v = lo + threadIdx.x; v < hi; v += blockDim.x) take(row[v], v);
     }
-    sv[threadIdx.x] = best;
-    si[threadIdx.x] = besti;
+    auto better = [](float ov, int oi, float v, int i) { return ov > v || (ov == v && oi < i); };
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, besti, o);
+        if (better(ov, oi, best, besti)) { best = ov; besti = oi; }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) { sv[warp] = best; si[warp] = besti; }
     __syncthreads();
-    for (int s = blockDim.x / 2; s > 0; s >>= 1) {
-        if (threadIdx.x < s) {
-            const float ov = sv[threadIdx.x + s];
-            const int oi = si[threadIdx.x + s];
-            if (ov > sv[threadIdx.x] || (ov == sv[threadIdx.x] && oi < si[threadIdx.x])) {
-                sv[threadIdx.x] = ov;
-                si[threadIdx.x] = oi;
-            }
+    if (warp == 0) {
+        best = lane < SAMPLE_THREADS / 32 ? sv[lane] : -INFINITY;
+        besti = lane < SAMPLE_THREADS / 32 ? si[lane] : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, besti, o);
+            if (better(ov, oi, best, besti)) { best = ov; besti = oi; }
         }
-        __syncthreads();
+        if (lane == 0) {
+            *cluster.map_shared_rank(&cv[rank], 0) = best;
+            *cluster.map_shared_rank(&ci[rank], 0) = besti;
+        }
     }
-    if (threadIdx.x == 0) {
-        const int tok = si[0] == 0x7fffffff ? 0 : si[0];
+    cluster.sync();                                          // every CTA's candidate has arrived in the first CTA
+    if (rank == 0 && threadIdx.x == 0) {
+        best = cv[0]; besti = ci[0];
+        for (int r = 1; r < SAMPLE_CLUSTER; r++)
+            if (better(cv[r], ci[r], best, besti)) { best = cv[r]; besti = ci[r]; }
+        const int tok = besti == 0x7fffffff ? 0 : besti;
         out[b] = tok;
         if (feedback) feedback[slots[b]] = tok;          // stays on the device for the request's next step
     }
@@ -569,13 +600,13 @@ inline unsigned blocks_for(int64_t n, int threads) { return unsigned((n + thread
 
 IB_EXPORT int ib_embedding(const void* table, int table_dtype, const int* ids, int64_t n_tokens, int64_t hidden,
                            int64_t vocab, float* out, int* status, const int* feedback, const int* token_seg,
-                           const int* seg_slot, cudaStream_t stream) {
+                           const int* seg_slot, float scale, cudaStream_t stream) {
     if (n_tokens <= 0) return IB_OK;
     const int64_t n = n_tokens * hidden;
     if (table_dtype == IB_F32)
-        IB_LAUNCH(embedding_kernel<float>, blocks_for(n, 256), 256, 0, (const float*)table, ids, n_tokens, hidden, vocab, out, status, feedback, token_seg, seg_slot);
+        IB_LAUNCH(embedding_kernel<float>, blocks_for(n, 256), 256, 0, (const float*)table, ids, n_tokens, hidden, vocab, out, status, feedback, token_seg, seg_slot, scale);
     else if (table_dtype == IB_BF16)
-        IB_LAUNCH(embedding_kernel<bf16>, blocks_for(n, 256), 256, 0, (const bf16*)table, ids, n_tokens, hidden, vocab, out, status, feedback, token_seg, seg_slot);
+        IB_LAUNCH(embedding_kernel<bf16>, blocks_for(n, 256), 256, 0, (const bf16*)table, ids, n_tokens, hidden, vocab, out, status, feedback, token_seg, seg_slot, scale);
     else
         return ib::fail(IB_ERR_ARG, "ib_embedding: unknown table dtype %d", table_dtype);
     return ib::check_launch("ib_embedding");
@@ -648,6 +679,10 @@ IB_EXPORT int ib_rope_kv_write(const void* qkv, const float* cos_t, const float*
     return ib::check_launch("ib_rope_kv_write");
 }
 
+// The largest head size the plain attention kernel takes (parts ask at construction, so that a configuration the
+// kernels cannot serve is refused when the model is built, not at its first step).
+IB_EXPORT int ib_attention_plain_max_head_dim() { return 2 * AT; }
+
 IB_EXPORT int ib_attention_plain(const void* q, const void* k_cache, const void* v_cache, const int* block_table,
                                  int64_t max_blocks, const int* token_seg, const int* positions, void* out,
                                  int64_t n_tokens, int n_heads, int n_kv, int head_dim, int page_size, int window,
@@ -689,7 +724,9 @@ IB_EXPORT int ib_sample(const float* logits, int64_t n_rows, int64_t vocab, cons
                         cudaStream_t stream) {
     if (n_rows <= 0) return IB_OK;
     if (vocab <= 0 || vocab >= 0x7fffffff) return ib::fail(IB_ERR_ARG, "ib_sample: vocabulary %lld out of range", (long long)vocab);
-    IB_LAUNCH(sample_kernel, unsigned(n_rows), 1024, 0, logits, vocab, temperature, seed, step, out, feedback, slots);
+    const int rc = ib::launch("sample_kernel", sample_kernel, dim3(unsigned(n_rows) * SAMPLE_CLUSTER), dim3(SAMPLE_THREADS), 0, stream,
+                              unsigned(SAMPLE_CLUSTER), logits, vocab, temperature, seed, step, out, feedback, slots);
+    if (rc) return rc;
     return ib::check_launch("ib_sample");
 }
 

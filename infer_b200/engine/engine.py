@@ -150,7 +150,7 @@ class Engine:
         self.next_tokens = torch.zeros(max(1, max_requests), dtype=torch.int32, device=self.rt.device)
         # Decode-only steps of the bfloat16 path are captured into CUDA graphs, one per (batch, wanted rows, table widths);
         # steps with prompt portions once their exact shape has repeated.
-        self.use_graphs = bool(cuda_graphs) and dtype == torch.bfloat16
+        self.use_graphs = bool(cuda_graphs) and dtype == torch.bfloat16 and self.model.graph_safe()
         self._graphs: Dict[tuple, _GraphEntry] = {}
         self._portion_seen: Dict[tuple, int] = {}         # how often a shape with prompt portions has come
         self._graph_pool = torch.cuda.graph_pool_handle() if self.use_graphs else None

@@ -112,32 +112,28 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = Non
     return out
 
 
-SKINNY_MAX_ROWS = 16
-SKINNY_FUSED_NORM_MAX_K = 1536    # the copy-ring kernel normalises rows of up to one stage of K in registers
-PREFETCH_MAX_BYTES = 64 << 20     # at most this much of a later product's weights is pulled into L2 ahead of time
+_SKINNY_LIMITS = None
 
 
-def _prefetch_args(t: Optional[torch.Tensor]):
-    if t is None or not PREFETCH:
-        return None, 0
-    return t.data_ptr(), min(t.numel() * t.element_size(), PREFETCH_MAX_BYTES)
-
-# Decode kernels can ask L2 to fetch the weights of a product that runs two kernels later. Measured on B200 at the
-# 1.5B sizes it does not pay (batch 8: 1.56 ms against 1.55 ms per step, batch 1: 1.76 against 1.42), so it is off;
-# INFER_B200_PREFETCH=1 turns it on.
-PREFETCH = os.environ.get("INFER_B200_PREFETCH", "0") == "1"
+def skinny_limits():
+    """(most rows, longest row the fused norm takes) of the streaming kernel, as its library states them."""
+    global _SKINNY_LIMITS
+    if _SKINNY_LIMITS is None:
+        f = _fn("gemvb", "ib_linear_skinny_bulk_limits", [c_void_p, c_void_p])
+        rows, k = ctypes.c_int(), ctypes.c_int()
+        f(ctypes.byref(rows), ctypes.byref(k))
+        _SKINNY_LIMITS = (rows.value, k.value)
+    return _SKINNY_LIMITS
 
 
 def linear_skinny(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
                   residual: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16,
                   out: Optional[torch.Tensor] = None, swiglu: bool = False, cluster: int = 0,
-                  norm_weight: Optional[torch.Tensor] = None, norm_eps: float = 0.0,
-                  prefetch: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+                  norm_weight: Optional[torch.Tensor] = None, norm_eps: float = 0.0) -> Optional[torch.Tensor]:
     """The decode kernel: x [M <= 16, K] against w [N, K], weights streamed once; same epilogues as gemm_tc.
-    With ``norm_weight`` x is the float32 residual stream and is RMS-normalised inside the kernel (see
-    ``skinny_fused_norm_max_k``).
-    cluster: CTAs sharing one tile's K range (0 = chosen by the kernel). prefetch: a tensor (the weights of a
-    product that runs later) that the kernel asks L2 to fetch while it works."""
+    With ``norm_weight`` x is the float32 residual stream and is RMS-normalised inside the kernel (rows up to
+    ``skinny_limits()[1]`` long).
+    cluster: CTAs sharing one tile's K range (0 = chosen by the kernel)."""
     fused = norm_weight is not None
     _check(x, "x", torch.float32 if fused else torch.bfloat16)
     _check(w, "w", torch.bfloat16)
@@ -145,11 +141,12 @@ def linear_skinny(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor]
     N = w.shape[0]
     if w.shape[1] != K:
         raise KernelError(f"linear_skinny: x is [{M},{K}] but w is {tuple(w.shape)}")
-    if M > SKINNY_MAX_ROWS or K % 8 or (x.data_ptr() & 15) or (w.data_ptr() & 15) or (swiglu and N % 16):
+    max_rows, max_norm_k = skinny_limits()
+    if M > max_rows or K % 8 or (x.data_ptr() & 15) or (w.data_ptr() & 15) or (swiglu and N % 16):
         return None
     if fused:
         _check(norm_weight, "norm_weight", torch.float32, (K,))
-        if K > SKINNY_FUSED_NORM_MAX_K or (norm_weight.data_ptr() & 15):
+        if K > max_norm_k or (norm_weight.data_ptr() & 15):
             return None
     if bias is not None:
         _check(bias, "bias", torch.float32, (N,))
@@ -163,30 +160,28 @@ def linear_skinny(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor]
         _check(out, "out", out_dtype, (M, n_out))
     st = device_state(x.device)
     epi = 2 if swiglu else (1 if residual is not None else 0)
-    pf_ptr, pf_bytes = _prefetch_args(prefetch)
     f = _fn("gemvb", "ib_linear_skinny_bulk", [c_void_p, c_void_p, c_float] + [c_void_p] * 4 + [c_int64] * 3 + [c_int] * 4 +
             [c_void_p] * 2 + [c_int64, c_void_p])
     _call(f, x.data_ptr(), _ptr(norm_weight), float(norm_eps), w.data_ptr(), _ptr(bias), _ptr(residual), out.data_ptr(),
-          M, N, K, dtype_code(out_dtype), epi, int(cluster), st.sm_count, st.status.data_ptr(), pf_ptr, pf_bytes, _stream())
+          M, N, K, dtype_code(out_dtype), epi, int(cluster), st.sm_count, st.status.data_ptr(), None, 0, _stream())
     return out
 
 
-def linear(x, weight, bias, residual, out_dtype, out, swiglu=False, prefetch=None):
+def linear(x, weight, bias, residual, out_dtype, out, swiglu=False):
     """The bfloat16 matrix product of the serving path: the streaming kernel for up to 16 rows, the tcgen05 kernel
     above that; None if neither takes the shape. x may be a DeferredNorm (the float32 residual stream plus the norm
     that is still to be applied): the streaming kernel then normalises inside, anything else materialises it."""
     from .parts.base import DeferredNorm
     if isinstance(x, DeferredNorm):
-        if weight.dtype == torch.bfloat16 and x.h.shape[0] <= SKINNY_MAX_ROWS:
-            y = linear_skinny(x.h, weight, bias, residual, out_dtype, out, swiglu, 0, x.norm.weight, x.norm.eps,
-                              prefetch=prefetch)
+        if weight.dtype == torch.bfloat16 and x.h.shape[0] <= skinny_limits()[0]:
+            y = linear_skinny(x.h, weight, bias, residual, out_dtype, out, swiglu, 0, x.norm.weight, x.norm.eps)
             if y is not None:
                 return y
         x = x.materialize()
     if x.dtype != torch.bfloat16:
         return None
-    if x.shape[0] <= SKINNY_MAX_ROWS:
-        y = linear_skinny(x, weight, bias, residual, out_dtype, out, swiglu, prefetch=prefetch)
+    if x.shape[0] <= skinny_limits()[0]:
+        y = linear_skinny(x, weight, bias, residual, out_dtype, out, swiglu)
         if y is not None:
             return y
     return gemm_tc(x, weight, bias, residual, out_dtype, out, swiglu=swiglu)
@@ -287,8 +282,7 @@ def attention_decode_fused(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tens
                            v_cache: torch.Tensor, block_table: torch.Tensor, seg_start: torch.Tensor,
                            seg_pos0: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, window: Optional[int],
                            scale: float, max_ctx_len: int, write_cache: bool = True,
-                           n_splits: Optional[int] = None, prefetch: Optional[torch.Tensor] = None,
-                           n_clusters: int = 1) -> Optional[torch.Tensor]:
+                           n_splits: Optional[int] = None, n_clusters: int = 1) -> Optional[torch.Tensor]:
     """Decode-only steps: rotation of q and k, the cache write of the new positions and attention in ONE kernel.
     qkv [S, (heads + 2 kv) * head_dim] packed rows with the bias added. Returns [S, heads * head_dim]."""
     n_pages, ckv, page_size, chd = k_cache.shape
@@ -313,13 +307,12 @@ def attention_decode_fused(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tens
         n_splits, n_clusters = _decode_splits(st, S, n_kv, visible)
     ws, cnt = _decode_scratch(st, S, n_kv, head_dim, n_clusters)
     out = torch.empty((S, n_heads * head_dim), dtype=torch.bfloat16, device=qkv.device)
-    pf_ptr, pf_bytes = _prefetch_args(prefetch)
     f = _fn("attn", "ib_attention_decode_fused", [c_void_p] * 7 + [c_int] + [c_void_p] * 2 + [c_int] * 6 + [c_float, c_int64] +
             [c_int] * 2 + [c_void_p] * 2 + [c_int64, c_void_p] + [c_int] + [c_void_p] * 2, {"IB_HEAD_DIM": head_dim})
     _call(f, qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
           block_table.data_ptr(), block_table.shape[1], seg_start.data_ptr(), seg_pos0.data_ptr(), S, n_heads, n_kv,
           head_dim, page_size, int(window or 0), float(scale), n_pages, int(write_cache), int(n_splits),
-          st.status.data_ptr(), pf_ptr, pf_bytes, _stream(), int(n_clusters), _ptr(ws), _ptr(cnt))
+          st.status.data_ptr(), None, 0, _stream(), int(n_clusters), _ptr(ws), _ptr(cnt))
     return out
 
 
@@ -329,6 +322,6 @@ def attention(q, cache, table, step, n_heads, n_kv, head_dim, window, scale):
                           scale, n_decode > 0, step.max_q_len, step.max_ctx_len, n_decode)
 
 
-def gate_up_swiglu(x, gate_up_weight, prefetch=None):
+def gate_up_swiglu(x, gate_up_weight):
     """silu(x Wg^T) * (x Wu^T) in one kernel; gate_up_weight rows interleaved in blocks of 8."""
-    return linear(x, gate_up_weight, None, None, torch.bfloat16, None, swiglu=True, prefetch=prefetch)
+    return linear(x, gate_up_weight, None, None, torch.bfloat16, None, swiglu=True)

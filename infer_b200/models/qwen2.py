@@ -136,14 +136,16 @@ def to_spec(cfg: Qwen2Config) -> ModelSpec:
                                   "intermediate_size": cfg.intermediate_size}, p + "mlp.")
         n1 = PartSpec("rmsnorm", {"size": cfg.hidden_size, "eps": cfg.rms_norm_eps}, p + "input_layernorm.")
         n2 = PartSpec("rmsnorm", {"size": cfg.hidden_size, "eps": cfg.rms_norm_eps}, p + "post_attention_layernorm.")
-        layers.append(LayerSpec("prenorm", mixer, ffn, n1, n2))
+        layers.append(LayerSpec.standard("prenorm", mixer, ffn, n1, n2))
     spec = ModelSpec(
         architecture=NAME, hidden_size=cfg.hidden_size, vocab_size=cfg.vocab_size,
         max_positions=cfg.max_position_embeddings, layers=tuple(layers),
         schedule=tuple(LayerCall(i, i) for i in range(cfg.num_hidden_layers)),
         final_norm=PartSpec("rmsnorm", {"size": cfg.hidden_size, "eps": cfg.rms_norm_eps}, "model.norm."),
-        embedding_name="model.embed_tokens.weight",
-        head_name=None if cfg.tie_word_embeddings else "lm_head.weight",
+        embedding=PartSpec("token_table", {"vocab_size": cfg.vocab_size, "hidden_size": cfg.hidden_size, "scale": None},
+                           "model.embed_tokens."),
+        head=PartSpec("linear_head", {"vocab_size": cfg.vocab_size, "hidden_size": cfg.hidden_size,
+                                      "tied": cfg.tie_word_embeddings}, "lm_head."),
         eos_token_id=cfg.eos_token_id)
     spec.validate()
     return spec

@@ -35,7 +35,9 @@ def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
 
 
 def _stream() -> int:
-    return torch.cuda.current_stream().cuda_stream
+    """The raw handle of torch's current stream on the current device (asked of torch's C layer directly: the Python
+    wrapper costs several microseconds, which counts when a step launches two hundred kernels)."""
+    return torch._C._cuda_getCurrentRawStream(torch._C._cuda_getDevice())
 
 
 def _check(t: torch.Tensor, name: str, dtype=None, shape=None) -> None:
@@ -93,9 +95,9 @@ def _call(f, *args) -> None:
 
 def embedding(table: torch.Tensor, ids: torch.Tensor, status: Optional[torch.Tensor] = None,
               feedback: Optional[torch.Tensor] = None, token_seg: Optional[torch.Tensor] = None,
-              seg_slot: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """float32 rows of ``table`` ([vocab, hidden], float32 or bfloat16) for int32 ``ids``. An id of -1 is replaced by
-    ``feedback[seg_slot[token_seg[t]]]``: the token the sampler left on the device for that request."""
+              seg_slot: Optional[torch.Tensor] = None, scale: float = 1.0) -> torch.Tensor:
+    """float32 rows of ``table`` ([vocab, hidden], float32 or bfloat16) for int32 ``ids``, times ``scale``. An id of
+    -1 is replaced by ``feedback[seg_slot[token_seg[t]]]``: the token the sampler left on the device for that request."""
     _check(table, "table")
     _check(ids, "ids", torch.int32)
     T, (V, H) = ids.numel(), table.shape
@@ -104,9 +106,9 @@ def embedding(table: torch.Tensor, ids: torch.Tensor, status: Optional[torch.Ten
         _check(feedback, "feedback", torch.int32)
         _check(token_seg, "token_seg", torch.int32, (T,))
         _check(seg_slot, "seg_slot", torch.int32)
-    f = _fn("plain", "ib_embedding", [c_void_p, c_int, c_void_p, c_int64, c_int64, c_int64] + [c_void_p] * 6)
+    f = _fn("plain", "ib_embedding", [c_void_p, c_int, c_void_p, c_int64, c_int64, c_int64] + [c_void_p] * 5 + [c_float, c_void_p])
     _call(f, table.data_ptr(), dtype_code(table.dtype), ids.data_ptr(), T, H, V, out.data_ptr(), _ptr(status),
-          _ptr(feedback), _ptr(token_seg), _ptr(seg_slot), _stream())
+          _ptr(feedback), _ptr(token_seg), _ptr(seg_slot), float(scale), _stream())
     return out
 
 
@@ -204,6 +206,11 @@ def attention_plain(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
           token_seg.data_ptr(), positions.data_ptr(), out.data_ptr(), T, n_heads, n_kv, head_dim, page_size,
           int(window or 0), float(scale), n_pages, dtype_code(q.dtype), _ptr(status), _stream())
     return out
+
+
+def attention_max_head_dim() -> int:
+    """The largest head size the attention kernels of this package take."""
+    return int(_fn("plain", "ib_attention_plain_max_head_dim", [])())
 
 
 def swiglu(gate_up: torch.Tensor, interleave8: bool = False) -> torch.Tensor:

@@ -38,13 +38,14 @@ class Attention(Mixer):
             raise ValueError(f"heads ({self.n_heads}) must be a multiple of kv heads ({self.n_kv})")
         if self.head_dim <= 0 or self.head_dim % 2:
             raise ValueError(f"head_dim must be positive and even, got {self.head_dim}")
+        if self.head_dim > ops.attention_max_head_dim():
+            raise ValueError(f"head_dim {self.head_dim} is beyond what the attention kernels take ({ops.attention_max_head_dim()})")
         scale = spec.get("softmax_scale")
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(float(self.head_dim))
         pos = spec.get("position")
         self.position = build_part("position", pos, runtime) if pos is not None else None
         self.qkv: Optional[Linear] = None
         self.o: Optional[Linear] = None
-        self.prefetch_next = None      # hint for the attention kernel itself (see Part.stations)
 
     @classmethod
     def param_shapes(cls, spec):
@@ -66,9 +67,6 @@ class Attention(Mixer):
     def cache_need(self):
         return PagedKVNeed(self.n_kv, self.head_dim, self.window)
 
-    def stations(self):
-        return [(self.qkv, self.qkv.weight), (self, None), (self.o, self.o.weight)]
-
     def forward(self, x, step, cache, residual, write_cache=True):
         qkv = self.qkv(x)                                              # [T, (heads + 2 kv) * head_dim]
         table = step.block_tables[cache.group]
@@ -84,7 +82,7 @@ class Attention(Mixer):
             from .. import fast_ops
             ctx = fast_ops.attention_decode_fused(qkv, cos, sin, cache.k, cache.v, table, step.seg_start, step.seg_pos0,
                                                   self.n_heads, self.n_kv, self.head_dim, self.window, self.scale,
-                                                  step.max_ctx_len, write_cache, prefetch=self.prefetch_next)
+                                                  step.max_ctx_len, write_cache)
             if ctx is not None:
                 return self.o(ctx, residual=residual)
         q = ops.rope_kv_write(qkv, cos, sin, step.positions, step.token_seg, table, cache.k, cache.v,

@@ -5,8 +5,8 @@ names and shapes of its parameters, and what it needs from the cache manager.  I
 which architecture, which layer index or which model it is in.
 
 To add a part: subclass the matching interface below, decorate it with
-``@register_mixer("name")`` (or the feed-forward / norm / position / block variant), and let an
-architecture's ``to_spec`` name that kind.  No framework file changes.
+``@register_mixer("name")`` (or the feed-forward / norm / position / block / embedding / head
+variant), and let an architecture's ``to_spec`` name that kind.  No framework file changes.
 """
 from __future__ import annotations
 
@@ -56,15 +56,13 @@ class Part:
         biases N(0, 0.02).  Parts whose parameters want another distribution override this."""
         return torch.randn(shape, generator=gen, dtype=torch.float32, device=gen.device) * 0.02
 
+    # False: the part's forward() cannot be captured into a CUDA graph (it reads device memory on the host, allocates
+    # outside the stream's pool, or launches by data). The engine then runs every step of the model eagerly.
+    graph_safe = True
+
     def load(self, params: Mapping[str, torch.Tensor]) -> None:
         """Receives the part's parameters (CPU tensors in their stored dtype) and moves what it
         needs to the device, in the layout its kernels want."""
-
-    def stations(self):
-        """The part's kernels in run order, for prefetch hints: a list of (holder, weight) where ``weight`` is the big
-        tensor the kernel streams (or None) and ``holder.prefetch_next`` may be set to a tensor that the kernel
-        should pull into L2 while it runs. Parts that do not care return nothing."""
-        return []
 
 
 class DeferredNorm:
@@ -128,12 +126,45 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
-class Block:
-    """An arrangement of a mixer, a feed-forward and their norms."""
+class Embedding(Part):
+    """Token ids -> float32 rows of the residual stream."""
 
-    def __init__(self, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm, feed_forward_norm: Norm):
-        self.mixer, self.feed_forward = mixer, feed_forward
-        self.mixer_norm, self.feed_forward_norm = mixer_norm, feed_forward_norm
+    def forward(self, step: "StepContext") -> torch.Tensor:
+        """float32 [T, hidden] for ``step.token_ids`` (an id of -1 stands for the request's last sampled token, kept
+        on the device in ``step.feedback[step.seg_slot[step.token_seg[t]]]``)."""
+        raise NotImplementedError
+
+    def table(self) -> Optional[torch.Tensor]:
+        """The [vocab, hidden] matrix on the device, for a head that is tied to it; None if there is none."""
+        return None
+
+
+class Head(Part):
+    """Normalised rows -> float32 logits [rows, vocab]."""
+
+    def tie(self, embedding: Embedding) -> None:
+        """Called once after loading, with the model's embedding part; a tied head takes its matrix from there."""
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Block:
+    """An arrangement of parts into a layer. ``parts`` maps the slot names of the layer's spec to the built and
+    loaded parts, in the spec's order; each is also an attribute of the block under its slot name. A block class
+    defines which slots it wants and how ``forward`` runs them."""
+
+    def __init__(self, **parts: Part):
+        self.parts: Dict[str, Part] = dict(parts)
+        for slot, part in parts.items():
+            setattr(self, slot, part)
+
+    def cache_need(self):
+        """What the layer needs from the cache manager per run-order entry: the need of its one part that has one."""
+        needs = [n for n in (p.cache_need() for p in self.parts.values() if hasattr(p, "cache_need")) if n is not None]
+        if len(needs) > 1:
+            raise ValueError("a block with more than one stateful part must define cache_need() itself")
+        return needs[0] if needs else None
 
     def forward(self, h: torch.Tensor, step: "StepContext", cache: Any, write_cache: bool) -> torch.Tensor:
         raise NotImplementedError
@@ -141,7 +172,8 @@ class Block:
 
 # ----------------------------------------------------------------------------- registries
 
-_REGISTRIES: Dict[str, Dict[str, type]] = {"mixer": {}, "feed_forward": {}, "norm": {}, "position": {}, "block": {}}
+_REGISTRIES: Dict[str, Dict[str, type]] = {"mixer": {}, "feed_forward": {}, "norm": {}, "position": {}, "block": {},
+                                           "embedding": {}, "head": {}}
 
 
 def _register(family: str, name: str) -> Callable[[type], type]:
@@ -158,6 +190,8 @@ def register_feed_forward(name: str): return _register("feed_forward", name)
 def register_norm(name: str): return _register("norm", name)
 def register_position(name: str): return _register("position", name)
 def register_block(name: str): return _register("block", name)
+def register_embedding(name: str): return _register("embedding", name)
+def register_head(name: str): return _register("head", name)
 
 
 def unregister(family: str, name: str) -> None:

@@ -20,7 +20,16 @@ class Linear:
         self.weight = weight.to(device=rt.device, dtype=rt.dtype).contiguous()
         self.bias = None if bias is None else bias.to(device=rt.device, dtype=torch.float32).contiguous()
         self.out_features, self.in_features = self.weight.shape
-        self.prefetch_next = None      # weights of a product that runs later; decode kernels fetch them into L2
+
+    @classmethod
+    def share(cls, rt: Runtime, weight: torch.Tensor) -> "Linear":
+        """A product by a matrix that already lies on the device in the compute dtype (no copy is made)."""
+        if weight.device != rt.device or weight.dtype != rt.dtype or not weight.is_contiguous():
+            raise ValueError("a shared matrix must lie on the device, contiguous, in the compute dtype")
+        self = cls.__new__(cls)
+        self.rt, self.weight, self.bias = rt, weight, None
+        self.out_features, self.in_features = weight.shape
+        return self
 
     def __call__(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None,
                  out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
@@ -33,8 +42,7 @@ class Linear:
             out_dtype = torch.float32
         if self.rt.fast("linear"):
             from .. import fast_ops
-            y = fast_ops.linear(x, self.weight, self.bias, residual, out_dtype or self.rt.dtype, out,
-                                prefetch=self.prefetch_next)
+            y = fast_ops.linear(x, self.weight, self.bias, residual, out_dtype or self.rt.dtype, out)
             if y is not None:
                 return y
         if isinstance(x, DeferredNorm):

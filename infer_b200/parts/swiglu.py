@@ -40,14 +40,11 @@ class SwiGLU(FeedForward):
         self.gate_up = Linear(self.rt, w)
         self.down = Linear(self.rt, params["down_proj.weight"])
 
-    def stations(self):
-        return [(self.gate_up, self.gate_up.weight), (self.down, self.down.weight)]
-
     def forward(self, x, residual):
         act = None
         if self.interleaved and self.rt.fast("swiglu") and self.rt.fast("linear"):
             from .. import fast_ops
-            act = fast_ops.gate_up_swiglu(x, self.gate_up.weight, self.gate_up.prefetch_next)
+            act = fast_ops.gate_up_swiglu(x, self.gate_up.weight)
         if act is None:
             act = ops.swiglu(self.gate_up(x), self.interleaved)      # Linear materialises a deferred norm
         return self.down(act, residual=residual)

@@ -1,8 +1,8 @@
 """Binds checkpoint tensors to a ModelSpec by tensor name, and makes seeded random checkpoints.
 
-Which tensors a model has follows from its spec alone: the token table, the output matrix
-unless tied, the final norm, and for every layer the parameters each part class declares
-(``Part.param_shapes``) under the part's prefix.  The reference resolves the same names one by
+Which tensors a model has follows from its spec alone: the parameters that each part class
+declares (``Part.param_shapes``) under the part's prefix, for the embedding, the head (none when
+it is tied), the final norm and every part of every layer.  The reference resolves the same names one by
 one and stops at the first problem (src/model.cpp:13-29,54-76); here every problem of a
 checkpoint is collected into one error.
 """
@@ -44,20 +44,13 @@ def _part_entries(family: str, spec: PartSpec):
 
 
 def expected_tensors(spec: ModelSpec) -> Dict[str, Tuple[Tuple[int, ...], type, PartSpec, str]]:
-    """Full tensor name -> (shape, owning part class or None, its spec, local name)."""
+    """Full tensor name -> (shape, owning part class, its spec, local name), over every part the spec lists."""
     out: Dict[str, Tuple] = {}
-    out[spec.embedding_name] = ((spec.vocab_size, spec.hidden_size), None, None, "embedding")
-    if spec.head_name is not None:
-        out[spec.head_name] = ((spec.vocab_size, spec.hidden_size), None, None, "head")
-    for name, shape, cls, ps, local in _part_entries("norm", spec.final_norm):
-        out[name] = (shape, cls, ps, local)
-    for layer in spec.layers:
-        for family, ps in (("mixer", layer.mixer), ("feed_forward", layer.feed_forward),
-                           ("norm", layer.mixer_norm), ("norm", layer.feed_forward_norm)):
-            for name, shape, cls, pspec, local in _part_entries(family, ps):
-                if name in out and out[name][0] != shape:
-                    raise ValueError(f"two parts declare tensor {name} with different shapes")
-                out[name] = (shape, cls, pspec, local)
+    for family, ps in spec.part_specs():
+        for name, shape, cls, pspec, local in _part_entries(family, ps):
+            if name in out and out[name][0] != shape:
+                raise ValueError(f"two parts declare tensor {name} with different shapes")
+            out[name] = (shape, cls, pspec, local)
     return out
 
 
@@ -103,11 +96,7 @@ def random_weights(spec: ModelSpec, seed: int, dtype: torch.dtype = torch.bfloat
     for name, (shape, cls, ps, local) in expected_tensors(spec).items():
         gen = torch.Generator(device=device)
         gen.manual_seed((int(seed) * 1000003 + zlib.crc32(name.encode())) & 0x7FFFFFFFFFFFFFFF)
-        if cls is None:
-            t = torch.randn(shape, generator=gen, dtype=torch.float32, device=device) * 0.02
-        else:
-            t = cls.init_params(ps, local, shape, gen)
-        out[name] = t.to(dtype)
+        out[name] = cls.init_params(ps, local, shape, gen).to(dtype)
     return out
 
 

@@ -19,11 +19,11 @@ def test_parse_and_spec(name):
     spec = arch.to_spec(typed)
     assert len(spec.layers) == cfg["num_hidden_layers"] == len(spec.schedule)
     assert spec.vocab_size == cfg["vocab_size"] and spec.hidden_size == cfg["hidden_size"]
-    m = spec.layers[0].mixer
+    m = spec.layers[0].part("mixer")
     assert m.kind == "attention" and m["num_heads"] == cfg["num_attention_heads"]
     assert m["head_dim"] == cfg.get("head_dim", cfg["hidden_size"] // cfg["num_attention_heads"])
-    assert (spec.head_name is None) == cfg["tie_word_embeddings"]
-    assert spec.layers[0].mixer_norm["eps"] == cfg["rms_norm_eps"]
+    assert spec.head["tied"] == cfg["tie_word_embeddings"] and spec.embedding.prefix == "model.embed_tokens."
+    assert spec.layers[0].part("mixer_norm")["eps"] == cfg["rms_norm_eps"]
     assert m["position"]["theta"] == cfg["rope_theta"]
     # the dictionary written back parses to the same typed configuration
     assert parse_config(arch.to_dict(typed))[1] == typed
@@ -31,7 +31,7 @@ def test_parse_and_spec(name):
 
 def test_window_is_chosen_layer_by_layer():
     spec = H.spec_of(H.TINY["c"])
-    assert [l.mixer["window"] for l in spec.layers] == [None, None, 40, 40]
+    assert [l.part("mixer")["window"] for l in spec.layers] == [None, None, 40, 40]
 
 
 def test_defaults_follow_the_reference():

@@ -208,13 +208,14 @@ def test_toy_mixer_with_state_registers_builds_and_steps():
         Hd, V = 32, 50
         attn = H.spec_of(dict(H.TINY["a"], hidden_size=Hd, num_attention_heads=2, num_key_value_heads=1, vocab_size=V,
                               intermediate_size=48)).layers[0]
-        toy = LayerSpec("prenorm", PartSpec("toy_decay", {"size": Hd, "decay": 0.9}, "toy.1."), attn.feed_forward,
-                        attn.mixer_norm, attn.feed_forward_norm)
-        toy = LayerSpec("prenorm", toy.mixer, PartSpec("swiglu", dict(attn.feed_forward.params), "toy.1.mlp."),
-                        PartSpec("rmsnorm", dict(attn.mixer_norm.params), "toy.1.n1."),
-                        PartSpec("rmsnorm", dict(attn.feed_forward_norm.params), "toy.1.n2."))
+        toy = LayerSpec.standard("prenorm", PartSpec("toy_decay", {"size": Hd, "decay": 0.9}, "toy.1."),
+                                 PartSpec("swiglu", dict(attn.part("feed_forward").params), "toy.1.mlp."),
+                                 PartSpec("rmsnorm", dict(attn.part("mixer_norm").params), "toy.1.n1."),
+                                 PartSpec("rmsnorm", dict(attn.part("feed_forward_norm").params), "toy.1.n2."))
         spec = ModelSpec("ToyForTests", Hd, V, 256, (attn, toy), (LayerCall(0, 0), LayerCall(1, 1)),
-                         PartSpec("rmsnorm", {"size": Hd, "eps": 1e-6}, "model.norm."), "model.embed_tokens.weight", None)
+                         PartSpec("rmsnorm", {"size": Hd, "eps": 1e-6}, "model.norm."),
+                         PartSpec("token_table", {"vocab_size": V, "hidden_size": Hd}, "model.embed_tokens."),
+                         PartSpec("linear_head", {"vocab_size": V, "hidden_size": Hd, "tied": True}, "lm_head."))
         register_architecture(Architecture("ToyForTests", lambda raw: raw, lambda typed: spec, lambda typed: dict(typed)))
         W = random_weights(spec, 4, torch.float32)
         assert "toy.1.mix.weight" in W
@@ -253,3 +254,130 @@ def test_toy_mixer_with_state_registers_builds_and_steps():
     finally:
         unregister("mixer", "toy_decay")
         unregister_architecture("ToyForTests")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+def test_toy_block_with_three_norms_toy_positions_and_scaled_embedding(dtype):
+    """Parts that this engine's architecture does not have, defined and registered here, with no change to a
+    framework file: a block arrangement with five slots, three of them norms ("sandwich": h += mixer(norm_in(h));
+    h += norm_out(ffn(norm_mid(h)))), a position encoding that is not a rotation and goes through ``apply()`` (so the
+    attention part stores keys as it gets them), an
+    embedding with a scale, an untied head of its own kind with a soft cap, and a part that says it cannot be
+    captured into a CUDA graph, which the engine must honour in bfloat16. Compared with a plain computation."""
+    from infer_b200.config import (Architecture, LayerCall, LayerSpec, ModelSpec, PartSpec, register_architecture,
+                                   unregister_architecture)
+    from infer_b200.engine import Engine
+    from infer_b200.parts import (Block, Head, PositionEncoding, register_block, register_head, register_position, unregister)
+    from infer_b200.parts.linear import Linear
+    from infer_b200.weights import random_weights
+
+    @register_position("toy_additive")
+    class ToyAdditive(PositionEncoding):
+        """q and k get a learned-free additive code: x[..., j] += amp * sin(pos * (j + 1) * rate)."""
+        def __init__(self, spec, runtime):
+            super().__init__(spec, runtime)
+            self.amp, self.rate = float(spec["amp"]), float(spec["rate"])
+
+        def rotary_tables(self, n_positions=None):
+            return None
+
+        def apply(self, q, k, positions):
+            for x in (q, k):
+                j = torch.arange(1, x.shape[-1] + 1, device=x.device, dtype=torch.float32)
+                code = self.amp * torch.sin(positions.float()[:, None] * j[None, :] * self.rate)      # [T, head_dim]
+                x.copy_((x.float() + code[:, None, :]).to(x.dtype))
+
+    @register_block("toy_sandwich")
+    class Sandwich(Block):
+        def __init__(self, norm_in, mixer, norm_mid, feed_forward, norm_out):
+            super().__init__(norm_in=norm_in, mixer=mixer, norm_mid=norm_mid, feed_forward=feed_forward, norm_out=norm_out)
+
+        def forward(self, h, step, cache, write_cache=True):
+            h = self.mixer.forward(self.norm_in.forward(h), step, cache, h, write_cache)
+            delta = self.feed_forward.forward(self.norm_mid.forward(h), torch.zeros_like(h))
+            return h + self.norm_out.forward(delta, torch.float32)
+
+    @register_head("toy_capped")
+    class Capped(Head):
+        graph_safe = False                     # pretend: this part must never be captured
+
+        def __init__(self, spec, runtime):
+            super().__init__(spec, runtime)
+            self.cap = float(spec["cap"])
+
+        @classmethod
+        def param_shapes(cls, spec):
+            return {"weight": (int(spec["vocab_size"]), int(spec["hidden_size"]))}
+
+        def load(self, params):
+            self.linear = Linear(self.rt, params["weight"])
+
+        def forward(self, x):
+            assert not torch.cuda.is_current_stream_capturing(), "a part that is not graph-safe was captured"
+            return self.cap * torch.tanh(self.linear(x, out_dtype=torch.float32) / self.cap)
+
+    try:
+        Hd, V, nh, nkv, hd, I = 48, 61, 3, 1, 16, 80
+        pos = PartSpec("toy_additive", {"amp": 0.3, "rate": 0.05})
+        layers = []
+        for i in range(2):
+            p = f"t.{i}."
+            layers.append(LayerSpec("toy_sandwich", {
+                "norm_in": ("norm", PartSpec("rmsnorm", {"size": Hd, "eps": 1e-5}, p + "n1.")),
+                "mixer": ("mixer", PartSpec("attention", {"hidden_size": Hd, "num_heads": nh, "num_kv_heads": nkv, "head_dim": hd,
+                                                          "qkv_bias": False, "window": None, "softmax_scale": 0.2, "position": pos},
+                                            p + "attn.")),
+                "norm_mid": ("norm", PartSpec("rmsnorm", {"size": Hd, "eps": 1e-5}, p + "n2.")),
+                "feed_forward": ("feed_forward", PartSpec("swiglu", {"hidden_size": Hd, "intermediate_size": I}, p + "mlp.")),
+                "norm_out": ("norm", PartSpec("rmsnorm", {"size": Hd, "eps": 1e-5}, p + "n3."))}))
+        spec = ModelSpec("ToySandwich", Hd, V, 256, tuple(layers), (LayerCall(0, 0), LayerCall(1, 1)),
+                         PartSpec("rmsnorm", {"size": Hd, "eps": 1e-5}, "final."),
+                         PartSpec("token_table", {"vocab_size": V, "hidden_size": Hd, "scale": 3.0}, "emb."),
+                         PartSpec("toy_capped", {"vocab_size": V, "hidden_size": Hd, "cap": 2.0}, "out."))
+        register_architecture(Architecture("ToySandwich", lambda raw: raw, lambda typed: spec, lambda typed: dict(typed)))
+        W = random_weights(spec, 6, torch.bfloat16)
+        assert {"t.0.n3.weight", "t.1.attn.q_proj.weight", "out.weight", "emb.weight"} <= set(W) and "t.0.attn.q_proj.bias" not in W
+        eng = Engine(spec, W, dtype=dtype, max_tokens=256, max_requests=3)
+        assert not eng.use_graphs                                  # the head said so
+        ids = {"p": H.random_ids({"vocab_size": V}, 50, 1), "q": H.random_ids({"vocab_size": V}, 33, 2)}
+        reqs = {k: (v, len(v) - 10) for k, v in ids.items()}
+        got = H.run_trace(eng, H.trace_mixed(reqs, 192, seed=2, max_live=2))
+        Wd = {k: v.double() for k, v in W.items()}
+
+        def plain(seq):
+            T = len(seq)
+            h = pm.embedding(Wd["emb.weight"], seq) * 3.0
+            j = torch.arange(1, hd + 1, dtype=torch.float64)
+            code = 0.3 * torch.sin(torch.arange(T, dtype=torch.float32).double()[:, None] * j[None, :] * 0.05)
+            for i in range(2):
+                p = f"t.{i}."
+                n = pm.rmsnorm(h, Wd[p + "n1.weight"], 1e-5)
+                q = pm.linear(n, Wd[p + "attn.q_proj.weight"]).view(T, nh, hd) + code[:, None, :]
+                k = pm.linear(n, Wd[p + "attn.k_proj.weight"]).view(T, nkv, hd) + code[:, None, :]
+                v = pm.linear(n, Wd[p + "attn.v_proj.weight"]).view(T, nkv, hd)
+                h = h + pm.linear(pm.attention(q, k, v, None, 0.2).reshape(T, nh * hd), Wd[p + "attn.o_proj.weight"])
+                n = pm.rmsnorm(h, Wd[p + "n2.weight"], 1e-5)
+                d = pm.swiglu_mlp(n, Wd[p + "mlp.gate_proj.weight"], Wd[p + "mlp.up_proj.weight"], Wd[p + "mlp.down_proj.weight"])
+                h = h + pm.rmsnorm(d, Wd[p + "n3.weight"], 1e-5)
+            return (2.0 * torch.tanh(pm.linear(pm.rmsnorm(h, Wd["final.weight"], 1e-5), Wd["out.weight"]) / 2.0)).numpy()
+        for rid, seq in ids.items():
+            ref = plain(seq)
+            g = np.stack([got[rid][p] for p in sorted(got[rid])])
+            if dtype == torch.float32:
+                assert np.abs(g - ref).max() < 5e-5, rid
+            else:
+                assert np.sqrt(np.mean((g - ref) ** 2)) < 0.03 * np.sqrt(np.mean(ref ** 2)) + 3e-3, rid
+    finally:
+        unregister("position", "toy_additive"), unregister("block", "toy_sandwich"), unregister("head", "toy_capped")
+        unregister_architecture("ToySandwich")
+
+
+def test_a_head_size_beyond_the_kernels_is_refused_when_the_part_is_built():
+    from infer_b200 import ops
+    from infer_b200.config import PartSpec
+    from infer_b200.parts import build_part
+    from infer_b200.runtime import Runtime
+    too_big = ops.attention_max_head_dim() + 2
+    spec = PartSpec("attention", {"hidden_size": 64, "num_heads": 1, "num_kv_heads": 1, "head_dim": too_big, "qkv_bias": False}, "a.")
+    with pytest.raises(ValueError, match="beyond what the attention kernels take"):
+        build_part("mixer", spec, Runtime(dtype=torch.float32))
