@@ -4,10 +4,18 @@
 // Two kernels share one launch call; each segment (a request's tokens in this step) goes to one of them:
 //
 //  decode  (segments of ONE token)   grid (slices, kv heads, segments). The query heads that share a kv head are
-//          the rows of one 16-row tile, so a key or value is read once for the whole group. The key range is cut
-//          into slices (flash-decoding); inside a CTA each of the 4 warps walks its own pages (a page is a
-//          contiguous 16 x head_dim block per kv head) through a 3-stage cp.async ring, with its own running
-//          maximum, sum and output, merged in shared memory at the end. Up to 8 slices form a thread-block cluster
+//          the 8 columns of one MMA tile and a page's 16 keys its rows (S^T = K Q^T, then O^T = V^T P^T with P^T
+//          turned into the B operand by movmatrix), so a key or value is read once for the whole group and a page
+//          costs 16 MMAs, not 32: the legacy tensor path issues about one m16n8k16 per 32 cycles and scheduler on
+//          sm_100, and that, not bytes, bounds this kernel at short contexts. The key range is cut
+//          into slices (flash-decoding); inside a CTA each of the 6 warps walks its own pages (a page is a
+//          contiguous 16 x head_dim block per kv head) through a ring of 2 stages that is requested whole before
+//          the kernel waits for its predecessor, with its own running maximum, sum and output, merged in shared
+//          memory at the end. For head sizes 64 and 128 a page arrives by TMA (cp.async.bulk.tensor, 128-byte
+//          swizzle, completion on an mbarrier per stage), otherwise by 16-byte cp.async into padded rows. Six warps
+//          and two stages are what measured best inside a decode step at 2,048-token contexts (0.94-0.96 ms at
+//          batch 1, 1.04-1.05 at batch 8; four warps and three stages 1.00 / 1.08; anything above about 100 KB of
+//          shared memory no longer fits beside a neighbouring product's CTA and loses 15 %). Up to 8 slices form a thread-block cluster
 //          and meet through distributed shared memory; for long contexts at small batches several clusters share a
 //          (segment, kv head): each leaves (max, sum, unnormalised output) in the workspace and the CTA that arrives
 //          last at the (segment, kv head) counter adds the clusters in ascending order and writes the result.
@@ -20,6 +28,7 @@
 // Rows of keys or values that are not visible and not yet written are zero-filled in shared memory, so stale
 // cache contents can never reach a sum. Page ids outside the pool raise the status word and read as zeros.
 #include "common.cuh"
+#include "tma_map.cuh"
 
 #include <cooperative_groups.h>
 
@@ -42,15 +51,30 @@ constexpr int CHUNKS = HD / 8;                  // 16-byte chunks per row
 constexpr int KS = HD / 16;                     // k-steps over the head dimension
 constexpr float LOG2E = 1.4426950408889634f;
 
-constexpr int DEC_WARPS = 4, DEC_STAGES = 3;
+#ifndef IB_DEC_WARPS
+#define IB_DEC_WARPS 6
+#endif
+#ifndef IB_DEC_STAGES
+#define IB_DEC_STAGES 2
+#endif
+constexpr int DEC_WARPS = IB_DEC_WARPS, DEC_STAGES = IB_DEC_STAGES;
 constexpr int MAX_SPLITS = 8;                   // slices of the key range per cluster
 constexpr int MAX_SUPER = 32;                   // clusters per (segment, kv head)
 constexpr int WS_STRIDE = 16 * HD + 32;         // floats a cluster leaves in the workspace: [16][HD] output, [16][2] max and sum
-constexpr int DEC_STAGE_BYTES = 2 * PAGE * ROW_BYTES;                       // K page + V page
-constexpr int DEC_SMEM = DEC_WARPS * DEC_STAGES * DEC_STAGE_BYTES;
+// The decode kernel's pages arrive by TMA where a row is whole 128-byte swizzle lines (head sizes 64 and 128): one
+// tensor copy per 16 rows x 64 elements, 128-byte swizzle, no padding. Other head sizes use 16-byte cp.async into
+// padded rows.
+#ifndef IB_DEC_TMA
+#define IB_DEC_TMA 1
+#endif
+constexpr bool TMA_PAGES = IB_DEC_TMA && HD % 64 == 0;
+constexpr int PAGE_TILE_BYTES = TMA_PAGES ? PAGE * HD * 2 : PAGE * ROW_BYTES;   // K (or V) rows of one page in shared memory
+constexpr int DEC_STAGE_BYTES = 2 * PAGE_TILE_BYTES;                        // K page + V page
+constexpr int DEC_RING_BYTES = DEC_WARPS * DEC_STAGES * DEC_STAGE_BYTES;
+constexpr int DEC_SMEM = DEC_RING_BYTES + (TMA_PAGES ? 1024 : 0);           // swizzled tiles start on 1024-byte boundaries
 constexpr int MO_PITCH = HD + 8;                // floats between rows of a warp's partial output: 8-byte stores of a half-warp hit 32 banks
 constexpr int DEC_MERGE_BYTES = DEC_WARPS * (16 * MO_PITCH + 32) * 4;
-static_assert(DEC_MERGE_BYTES <= DEC_SMEM, "merge area must fit the stage area");
+static_assert(DEC_MERGE_BYTES <= DEC_RING_BYTES, "merge area must fit the stage area");
 
 constexpr int PF_BM = 64, PF_BN = 64, PF_WARPS = 4;
 constexpr int PF_TILE_BYTES = PF_BN * ROW_BYTES;
@@ -75,6 +99,42 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) { return uint32_t(__
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
 }
+// Bulk asynchronous copies of whole cache rows, counted on an mbarrier (the decode kernel's page ring).
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait (about a second): false if the phase did not complete.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < (1u << 22); i++) {
+        if (mbar_test(bar, parity)) return true;
+        if (i > 2048) __nanosleep(64);
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+// Byte offset of the 16-byte chunk c of row r inside a page tile of the decode ring: swizzled 128-byte lines in tiles
+// of 64 elements (what the tensor copy writes), or padded rows.
+__device__ __forceinline__ uint32_t page_chunk(int r, int c) {
+    if constexpr (TMA_PAGES) return uint32_t((c >> 3) * (PAGE * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4));
+    else return uint32_t(r * ROW_BYTES + c * 16);
+}
+constexpr int STATUS_PAGE_TIMEOUT = 105;        // a decode warp's wait for a page ran out
+
 __device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
@@ -182,6 +242,94 @@ __device__ __forceinline__ void pv_tile(float (*o)[4], const float (*s)[4], uint
     }
 }
 
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+    return d;
+}
+
+// Decode tiles, keys on the rows: S^T[16 keys x 8 NH heads] = K[16 x HD] . Q^T, K rows at k_smem (a page tile);
+// qf[nh][ks] = B fragments of Q^T (heads nh*8 .. nh*8+7). Even and odd k-steps go to two accumulators, so the chain of
+// dependent MMAs is half as long.
+template <int NH>
+__device__ __forceinline__ void qk_page(float (*s)[4], const uint32_t (*qf)[KS][2], uint32_t k_smem) {
+    const int lane = threadIdx.x & 31;
+    const int row = (lane & 7) + ((lane >> 3) & 1) * 8, c0 = lane >> 4;
+    float s2[NH][4];
+#pragma unroll
+    for (int nh = 0; nh < NH; nh++) s2[nh][0] = s2[nh][1] = s2[nh][2] = s2[nh][3] = 0.0f;
+#pragma unroll
+    for (int ks = 0; ks < KS; ks++) {
+        uint32_t a[4];
+        ldsm_x4(k_smem + page_chunk(row, ks * 2 + c0), a[0], a[1], a[2], a[3]);
+#pragma unroll
+        for (int nh = 0; nh < NH; nh++) mma_bf16((ks & 1) ? s2[nh] : s[nh], a, qf[nh][ks][0], qf[nh][ks][1]);
+    }
+#pragma unroll
+    for (int nh = 0; nh < NH; nh++)
+#pragma unroll
+        for (int e = 0; e < 4; e++) s[nh][e] += s2[nh][e];
+}
+
+// O^T[HD x 8 NH heads] += V^T[HD x 16 keys] . P^T: V rows (keys) at v_smem are read transposed as the A operand; the
+// probabilities in s (C layout: keys on rows, heads on columns) become the B operand through movmatrix.
+template <int NH>
+__device__ __forceinline__ void pv_page(float (*o)[HD / 16][4], const float (*s)[4], uint32_t v_smem) {
+    const int lane = threadIdx.x & 31;
+    uint32_t b[NH][2];
+#pragma unroll
+    for (int nh = 0; nh < NH; nh++) {
+        b[nh][0] = movmatrix_trans(pack_bf16(s[nh][0], s[nh][1]));
+        b[nh][1] = movmatrix_trans(pack_bf16(s[nh][2], s[nh][3]));
+    }
+    const int row = (lane & 7) + (lane >> 4) * 8, c0 = (lane >> 3) & 1;
+#pragma unroll
+    for (int mt = 0; mt < HD / 16; mt++) {
+        uint32_t a[4];
+        ldsm_x4_trans(v_smem + page_chunk(row, mt * 2 + c0), a[0], a[1], a[2], a[3]);
+#pragma unroll
+        for (int nh = 0; nh < NH; nh++) mma_bf16(o[nh][mt], a, b[nh][0], b[nh][1]);
+    }
+}
+
+// Online softmax of one page in that layout. A thread holds, per group of 8 heads, heads 2 t4 and 2 t4 + 1 of keys g
+// and g + 8: s[nh] = {(g, h0), (g, h1), (g+8, h0), (g+8, h1)}. The maximum of a head runs over the lanes that share
+// t4; l stays a per-thread share of the sum (the shares are added at the end).
+template <int NH>
+__device__ __forceinline__ void softmax_page(float (*s)[4], float (*m)[2], float (*l)[2], float (*o)[HD / 16][4], float scale_log2,
+                                             bool vis0, bool vis1) {
+    bool rescale = false;
+    float corr[NH][2];
+#pragma unroll
+    for (int nh = 0; nh < NH; nh++)
+#pragma unroll
+        for (int c = 0; c < 2; c++) {
+            const float v0 = vis0 ? s[nh][c] * scale_log2 : -INFINITY, v1 = vis1 ? s[nh][2 + c] * scale_log2 : -INFINITY;
+            float mx = fmaxf(v0, v1);
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+            const float m_new = fmaxf(m[nh][c], mx);
+            const float msafe = m_new == -INFINITY ? 0.0f : m_new;
+            corr[nh][c] = exp2f(m[nh][c] - msafe);             // m = -inf gives 0
+            m[nh][c] = m_new;
+            const float p0 = exp2f(v0 - msafe), p1 = exp2f(v1 - msafe);
+            s[nh][c] = p0; s[nh][2 + c] = p1;
+            l[nh][c] = l[nh][c] * corr[nh][c] + p0 + p1;
+            rescale |= corr[nh][c] != 1.0f;
+        }
+    // once the running maximum has settled the factors are exactly 1 for every head of the warp: skip the multiplies
+    if (__any_sync(0xffffffffu, rescale)) {
+#pragma unroll
+        for (int nh = 0; nh < NH; nh++)
+#pragma unroll
+            for (int mt = 0; mt < HD / 16; mt++) {
+                o[nh][mt][0] *= corr[nh][0]; o[nh][mt][1] *= corr[nh][1];
+                o[nh][mt][2] *= corr[nh][0]; o[nh][mt][3] *= corr[nh][1];
+            }
+    }
+}
+
 // ================================================================================================ decode
 //
 // Grid (slices, kv heads, segments); the slices of one (segment, kv head) form a thread-block cluster, and their
@@ -201,10 +349,11 @@ __device__ long long ib_dec_trace[32];
 #define IB_DT(k) do {} while (0)
 #endif
 
-template <bool FUSED>
+template <bool FUSED, int NH>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
-attn_decode_kernel(const AttnParams p) {
-    extern __shared__ __align__(128) uint8_t smem[];
+attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    uint8_t* smem = TMA_PAGES ? smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u) : smem_raw;
     // This kernel is a chain of latencies and leaves HBM nearly idle: a good time to fetch a later product's weights.
     ib::l2_prefetch_share(p.prefetch, p.prefetch_bytes, (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x,
                           gridDim.x * gridDim.y * gridDim.z);
@@ -243,33 +392,68 @@ attn_decode_kernel(const AttnParams p) {
     // a round trip to L2 in front of every copy.
     int lane_page = -1;
     if (lane < my_pages) lane_page = table[pg_begin + warp + lane * DEC_WARPS];
+    // A warp's ring of pages. With TMA_PAGES a page is two tensor copies per 64 elements of the head size (K and V,
+    // 16 rows x 128 bytes each, 128-byte swizzle) issued by one lane and counted on the stage's mbarrier: sixteen-byte
+    // cp.async took sixteen instructions per lane and page, about 900 cycles of a warp that has 600 of arithmetic per
+    // page. Rows that are not written yet (beyond the new position; with FUSED the new position itself, which comes
+    // from the projections) are zeroed before use, so that what a page held before can never reach a sum: by the
+    // copy's zero fill with cp.async, by stores after the tensor copy has landed.
+    __shared__ __align__(8) uint64_t page_bar[DEC_WARPS][DEC_STAGES];
+    const int copy_limit = (FUSED && p.write_cache) ? pos : pos + 1;       // keys below this are in the cache
+    if constexpr (TMA_PAGES) {
+        if (lane < DEC_STAGES) mbar_init(smem_u32(&page_bar[warp][lane]), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_k) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_v) : "memory");
+        }
+        __syncwarp();
+    }
     auto issue = [&](int i) {
         if (i < my_pages) {
             const int pg = pg_begin + warp + i * DEC_WARPS;
             int page = i < 32 ? __shfl_sync(0xffffffffu, lane_page, i) : table[pg];
             if (page < 0 || page >= p.n_pages) { atomicExch(p.status, 3); page = -1; }
             const uint32_t dst = my_smem + (i % DEC_STAGES) * DEC_STAGE_BYTES;
-            const int64_t base = page < 0 ? 0 : ((int64_t(page) * p.n_kv + kvh) * PAGE) * HD;
+            if constexpr (TMA_PAGES) {
+                // one lane states the bytes to come; the copies (K and V of every 64-element tile) go out from as many
+                // lanes at once, since a tensor copy holds up the lane that issues it for about 150 cycles
+                const uint32_t bar = smem_u32(&page_bar[warp][i % DEC_STAGES]);
+                if (lane == 0) mbar_expect_tx(bar, page < 0 ? 0u : uint32_t(2 * PAGE_TILE_BYTES));
+                __syncwarp();
+                if (page >= 0 && lane < 2 * (HD / 64)) {
+                    const int bx = lane >> 1, is_v = lane & 1;
+                    const int y = (page * p.n_kv + kvh) * PAGE;              // row of the [pages * kv heads * 16, HD] view
+                    tma_load_2d(dst + is_v * PAGE_TILE_BYTES + bx * (PAGE * 128), is_v ? &tm_v : &tm_k, bar, bx * 64, y);
+                }
+            } else {
+                const int64_t base = page < 0 ? 0 : ((int64_t(page) * p.n_kv + kvh) * PAGE) * HD;
 #pragma unroll
-            for (int c = lane; c < PAGE * CHUNKS; c += 32) {
-                const int row = c / CHUNKS, col = c % CHUNKS;
-                const int key = pg * PAGE + row;
-                // rows not written yet read as zeros (with FUSED the row of `pos` itself comes from the projections)
-                const int bytes = (page >= 0 && (FUSED && p.write_cache ? key < pos : key <= pos)) ? 16 : 0;
-                cp_async16(dst + row * ROW_BYTES + col * 16, p.k_cache + base + row * HD + col * 8, bytes);
-                cp_async16(dst + PAGE * ROW_BYTES + row * ROW_BYTES + col * 16, p.v_cache + base + row * HD + col * 8, bytes);
+                for (int c = lane; c < PAGE * CHUNKS; c += 32) {
+                    const int row = c / CHUNKS, col = c % CHUNKS;
+                    const int bytes = (page >= 0 && pg * PAGE + row < copy_limit) ? 16 : 0;
+                    cp_async16(dst + row * ROW_BYTES + col * 16, p.k_cache + base + row * HD + col * 8, bytes);
+                    cp_async16(dst + PAGE * ROW_BYTES + row * ROW_BYTES + col * 16, p.v_cache + base + row * HD + col * 8, bytes);
+                }
             }
         }
-        cp_commit();
+        if constexpr (!TMA_PAGES) cp_commit();
     };
 
-    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
-    float o[HD / 8][4];
+    float m[NH][2], l[NH][2];
+    float o[NH][HD / 16][4];
 #pragma unroll
-    for (int n = 0; n < HD / 8; n++) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f;
+    for (int nh = 0; nh < NH; nh++) {
+        m[nh][0] = m[nh][1] = -INFINITY;
+        l[nh][0] = l[nh][1] = 0.0f;
+#pragma unroll
+        for (int mt = 0; mt < HD / 16; mt++) o[nh][mt][0] = o[nh][mt][1] = o[nh][mt][2] = o[nh][mt][3] = 0.0f;
+    }
 
+    // The whole ring is requested now, before the wait for the predecessor: a copy costs its issuer hundreds of cycles
+    // (about 150 per tensor copy), which are free here and would sit in the chain of dependent work later.
 #pragma unroll
-    for (int i = 0; i < DEC_STAGES - 1; i++) issue(i);
+    for (int i = 0; i < DEC_STAGES; i++) issue(i);
     if constexpr (FUSED) {                               // the rotation's table rows, on their way meanwhile
         if (lane * 32 < HD / 2) {
             asm volatile("prefetch.global.L1 [%0];" ::"l"(p.cos + int64_t(pos) * (HD / 2) + lane * 32));
@@ -280,69 +464,107 @@ attn_decode_kernel(const AttnParams p) {
     if (early) ib::pdl_wait();                           // q, k and v of this step come from the predecessor
     IB_DT(2);
 
-    // Query fragments straight from global memory: tile row = head within the group, zero beyond it.
-    uint32_t qf[KS][4];
+    // Query fragments (the B operand: Q^T) straight from global memory: column g of group nh is head nh * 8 + g of
+    // this kv head's group, zero beyond it; a thread holds elements 2 t4, 2 t4 + 1 and those 8 further of every k-step.
+    uint32_t qf[NH][KS][2];
     if constexpr (FUSED) {
         const bf16* qb = p.qkv + qkv_row + int64_t(kvh) * G * HD;
         const float* cs = p.cos + int64_t(pos) * (HD / 2);
         const float* sn = p.sin + int64_t(pos) * (HD / 2);
 #pragma unroll
-        for (int ks = 0; ks < KS / 2; ks++)
+        for (int nh = 0; nh < NH; nh++)
 #pragma unroll
-            for (int e = 0; e < 4; e++) {
-                const int row = g + (e & 1) * 8, d = ks * 16 + t4 * 2 + (e >> 1) * 8;      // d < HD/2
-                if (row < G) {
-                    const float2 x1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(qb + row * HD + d));
-                    const float2 x2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(qb + row * HD + d + HD / 2));
-                    const float2 c = *reinterpret_cast<const float2*>(cs + d), sv = *reinterpret_cast<const float2*>(sn + d);
-                    qf[ks][e] = pack_bf16(x1.x * c.x - x2.x * sv.x, x1.y * c.y - x2.y * sv.y);
-                    qf[ks + KS / 2][e] = pack_bf16(x2.x * c.x + x1.x * sv.x, x2.y * c.y + x1.y * sv.y);
-                } else {
-                    qf[ks][e] = 0u;
-                    qf[ks + KS / 2][e] = 0u;
+            for (int ks = 0; ks < KS / 2; ks++)
+#pragma unroll
+                for (int e = 0; e < 2; e++) {
+                    const int head = nh * 8 + g, d = ks * 16 + t4 * 2 + e * 8;             // d < HD/2
+                    if (head < G) {
+                        const float2 x1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(qb + head * HD + d));
+                        const float2 x2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(qb + head * HD + d + HD / 2));
+                        const float2 c = *reinterpret_cast<const float2*>(cs + d), sv = *reinterpret_cast<const float2*>(sn + d);
+                        qf[nh][ks][e] = pack_bf16(x1.x * c.x - x2.x * sv.x, x1.y * c.y - x2.y * sv.y);
+                        qf[nh][ks + KS / 2][e] = pack_bf16(x2.x * c.x + x1.x * sv.x, x2.y * c.y + x1.y * sv.y);
+                    } else {
+                        qf[nh][ks][e] = 0u;
+                        qf[nh][ks + KS / 2][e] = 0u;
+                    }
                 }
-            }
     } else {
         const bf16* qb = p.q + (int64_t(t) * p.n_heads + int64_t(kvh) * G) * HD;
 #pragma unroll
-        for (int ks = 0; ks < KS; ks++) {
-            const int d = ks * 16 + t4 * 2;
-            qf[ks][0] = g < G ? *reinterpret_cast<const uint32_t*>(qb + g * HD + d) : 0u;
-            qf[ks][1] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(qb + (g + 8) * HD + d) : 0u;
-            qf[ks][2] = g < G ? *reinterpret_cast<const uint32_t*>(qb + g * HD + d + 8) : 0u;
-            qf[ks][3] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(qb + (g + 8) * HD + d + 8) : 0u;
-        }
+        for (int nh = 0; nh < NH; nh++)
+#pragma unroll
+            for (int ks = 0; ks < KS; ks++)
+#pragma unroll
+                for (int e = 0; e < 2; e++) {
+                    const int head = nh * 8 + g;
+                    qf[nh][ks][e] = head < G ? *reinterpret_cast<const uint32_t*>(qb + head * HD + ks * 16 + t4 * 2 + e * 8) : 0u;
+                }
     }
     IB_DT(3);
-    // Prepares page i of this warp (its stage has landed): for the page of the new position, rotates k and puts k and v
-    // into the shared-memory copy and into the cache. Returns the first key of the page.
+    // The warp whose page holds the new position rotates k and puts k and v into its shared-memory copy of the page and
+    // into the cache. Their values are requested now, so that they have arrived when the warp gets to that page.
+    constexpr int NP = (HD / 2 + 31) / 32;
+    const bool owns_new = FUSED && p.write_cache && last_page >= pg_begin && last_page < pg_end &&
+                          (last_page - pg_begin) % DEC_WARPS == warp;
+    float nk1[NP], nk2[NP], ncs[NP], nsn[NP];
+    bf16 nv1[NP], nv2[NP];
+    if constexpr (FUSED) {
+        if (owns_new) {
+            const bf16* kb = p.qkv + qkv_row + (int64_t(p.n_heads) + kvh) * HD;
+            const bf16* vb = p.qkv + qkv_row + (int64_t(p.n_heads) + p.n_kv + kvh) * HD;
+            const float* cs = p.cos + int64_t(pos) * (HD / 2);
+            const float* sn = p.sin + int64_t(pos) * (HD / 2);
+#pragma unroll
+            for (int u = 0; u < NP; u++) {
+                const int j = lane + u * 32;
+                if (j < HD / 2) {
+                    nk1[u] = __bfloat162float(kb[j]); nk2[u] = __bfloat162float(kb[j + HD / 2]);
+                    nv1[u] = vb[j]; nv2[u] = vb[j + HD / 2];
+                    ncs[u] = cs[j]; nsn[u] = sn[j];
+                }
+            }
+        }
+    }
+    // Prepares page i of this warp (its stage has landed): zeroes the rows that the tensor copy brought but that are
+    // not written yet, and puts the new position's k and v into the page. Returns the first key of the page.
     auto prepare = [&](int i, uint8_t* stage) -> int {
         const int pg = pg_begin + warp + i * DEC_WARPS;
         const int key0 = pg * PAGE;
+        if constexpr (TMA_PAGES) {
+            const int n_ok = (i < 32 ? __shfl_sync(0xffffffffu, lane_page, i) : table[pg]) < 0 ? 0 : copy_limit - key0;   // rows that hold cache contents
+            if (n_ok < PAGE) {
+                // a row is whole 128-byte lines of every 64-element tile, wherever the swizzle puts its chunks
+                for (int idx = lane; idx < (PAGE - max(n_ok, 0)) * CHUNKS; idx += 32) {
+                    const int row = max(n_ok, 0) + idx / CHUNKS, c = idx % CHUNKS;
+                    *reinterpret_cast<uint4*>(stage + page_chunk(row, c)) = make_uint4(0u, 0u, 0u, 0u);
+                    *reinterpret_cast<uint4*>(stage + PAGE_TILE_BYTES + page_chunk(row, c)) = make_uint4(0u, 0u, 0u, 0u);
+                }
+                __syncwarp();
+            }
+        }
         if constexpr (FUSED) {
-            if (p.write_cache && pg == last_page) {
-                // The new position: rotate k, store k and v into this page's shared-memory copy and into the cache.
+            if (owns_new && pg == last_page) {
                 const int page = table[pg];
                 const int row = pos - key0;
-                const bf16* kb = p.qkv + qkv_row + (int64_t(p.n_heads) + kvh) * HD;
-                const bf16* vb = p.qkv + qkv_row + (int64_t(p.n_heads) + p.n_kv + kvh) * HD;
-                const float* cs = p.cos + int64_t(pos) * (HD / 2);
-                const float* sn = p.sin + int64_t(pos) * (HD / 2);
-                bf16* ks_row = reinterpret_cast<bf16*>(stage + row * ROW_BYTES);
-                bf16* vs_row = reinterpret_cast<bf16*>(stage + PAGE * ROW_BYTES + row * ROW_BYTES);
+                uint8_t* ks_tile = stage;
+                uint8_t* vs_tile = stage + PAGE_TILE_BYTES;
                 const bool page_ok = page >= 0 && page < p.n_pages;
                 if (!page_ok && lane == 0) atomicExch(p.status, 2);
                 const int64_t gbase = page_ok ? ((int64_t(page) * p.n_kv + kvh) * PAGE + row) * HD : 0;
-                for (int j = lane; j < HD / 2; j += 32) {
-                    const float x1 = __bfloat162float(kb[j]), x2 = __bfloat162float(kb[j + HD / 2]);
-                    const bf16 r1 = __float2bfloat16_rn(x1 * cs[j] - x2 * sn[j]);
-                    const bf16 r2 = __float2bfloat16_rn(x2 * cs[j] + x1 * sn[j]);
-                    const bf16 v1 = vb[j], v2 = vb[j + HD / 2];
-                    ks_row[j] = r1; ks_row[j + HD / 2] = r2;
-                    vs_row[j] = v1; vs_row[j + HD / 2] = v2;
-                    if (page_ok) {
-                        p.k_cache_w[gbase + j] = r1; p.k_cache_w[gbase + j + HD / 2] = r2;
-                        p.v_cache_w[gbase + j] = v1; p.v_cache_w[gbase + j + HD / 2] = v2;
+#pragma unroll
+                for (int u = 0; u < NP; u++) {
+                    const int j = lane + u * 32;
+                    if (j < HD / 2) {
+                        const bf16 r1 = __float2bfloat16_rn(nk1[u] * ncs[u] - nk2[u] * nsn[u]);
+                        const bf16 r2 = __float2bfloat16_rn(nk2[u] * ncs[u] + nk1[u] * nsn[u]);
+                        const uint32_t e1 = page_chunk(row, j >> 3) + (j & 7) * 2, e2 = page_chunk(row, (j + HD / 2) >> 3) + (j & 7) * 2;
+                        *reinterpret_cast<bf16*>(ks_tile + e1) = r1; *reinterpret_cast<bf16*>(ks_tile + e2) = r2;
+                        *reinterpret_cast<bf16*>(vs_tile + e1) = nv1[u]; *reinterpret_cast<bf16*>(vs_tile + e2) = nv2[u];
+                        if (page_ok) {
+                            p.k_cache_w[gbase + j] = r1; p.k_cache_w[gbase + j + HD / 2] = r2;
+                            p.v_cache_w[gbase + j] = nv1[u]; p.v_cache_w[gbase + j + HD / 2] = nv2[u];
+                        }
                     }
                 }
                 __syncwarp();
@@ -350,68 +572,67 @@ attn_decode_kernel(const AttnParams p) {
         }
         return key0;
     };
-    // Two pages (32 keys) can share one softmax round (DEC_PAIRS): the running maximum, the sum and the rescaling of
-    // the output cost the same for 32 keys as for 16. It needs a fourth stage to keep copies ahead of the arithmetic,
-    // and with 139 KB of shared memory the kernel no longer fits beside its neighbours' CTAs, which costs more (their
-    // weight streams start later) than the shorter loop gains: 16.7 against 9.2 us in a captured step. Off.
-    constexpr bool DEC_PAIRS = DEC_STAGES >= 4;
-    int i = 0;
-    while (i < my_pages) {
-        const bool two = DEC_PAIRS && i + 1 < my_pages;
-        if (two) cp_wait<(DEC_STAGES >= 3 ? DEC_STAGES - 3 : 0)>(); else cp_wait<DEC_STAGES - 2>();
-        __syncwarp();
-        if (i < 8) IB_DT(4 + 2 * i);
-        uint8_t* stage_a = my_ptr + (i % DEC_STAGES) * DEC_STAGE_BYTES;
-        uint8_t* stage_b = my_ptr + ((i + 1) % DEC_STAGES) * DEC_STAGE_BYTES;
-        const int key_a = prepare(i, stage_a);
-        const uint32_t ka = smem_u32(stage_a), va = ka + PAGE * ROW_BYTES;
-        if (two) {
-            const int key_b = prepare(i + 1, stage_b);
-            const uint32_t kb = smem_u32(stage_b), vb = kb + PAGE * ROW_BYTES;
-            float s[4][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}, {0, 0, 0, 0}, {0, 0, 0, 0}};
-            qk_tile<2>(s, qf, ka);
-            qk_tile<2>(s + 2, qf, kb);
-            softmax_update<4, HD / 8>(s, m, l, o, p.scale_log2, [&](int, int key) {
-                const int k = key < PAGE ? key_a + key : key_b + key - PAGE;
-                return (k >= lo) & (k <= pos);
-            });
-            pv_tile<2>(o, s, va);
-            pv_tile<2>(o, s + 2, vb);
+    bool pages_ok = true;
+    for (int i = 0; i < my_pages; i++) {
+        // (a wait that runs out raises the status word; the pages already requested are still waited for, so that no
+        // copy is in flight when the ring is reused below)
+        if constexpr (TMA_PAGES) {
+            if (!mbar_wait(smem_u32(&page_bar[warp][i % DEC_STAGES]), uint32_t(i / DEC_STAGES) & 1u)) {
+                if (pages_ok && lane == 0) atomicExch(p.status, STATUS_PAGE_TIMEOUT);
+                pages_ok = false;
+            }
         } else {
-            float s[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
-            qk_tile<2>(s, qf, ka);
-            softmax_update<2, HD / 8>(s, m, l, o, p.scale_log2, [&](int, int key) { return (key_a + key >= lo) & (key_a + key <= pos); });
-            pv_tile<2>(o, s, va);
+            cp_wait<DEC_STAGES - 1>();
         }
         __syncwarp();
-        issue(i + DEC_STAGES - 1);
-        if (two) issue(i + DEC_STAGES);
+        if (i < 8) IB_DT(4 + 2 * i);
+        if (pages_ok) {
+            uint8_t* stage = my_ptr + (i % DEC_STAGES) * DEC_STAGE_BYTES;
+            const int key0 = prepare(i, stage);
+            const uint32_t ka = smem_u32(stage), va = ka + PAGE_TILE_BYTES;
+            float s[NH][4];
+#pragma unroll
+            for (int nh = 0; nh < NH; nh++) s[nh][0] = s[nh][1] = s[nh][2] = s[nh][3] = 0.0f;
+            qk_page<NH>(s, qf, ka);
+            softmax_page<NH>(s, m, l, o, p.scale_log2, (key0 + g >= lo) & (key0 + g <= pos), (key0 + g + 8 >= lo) & (key0 + g + 8 <= pos));
+            pv_page<NH>(o, s, va);
+            __syncwarp();
+        }
+        if (pages_ok || !TMA_PAGES) issue(i + DEC_STAGES);       // into the stage that was just read
         if (i < 8) IB_DT(5 + 2 * i);
-        i += two ? 2 : 1;
     }
-    cp_wait<0>();
+    if constexpr (!TMA_PAGES) cp_wait<0>();
     IB_DT(20);
     ib::pdl_launch_dependents();
 #pragma unroll
-    for (int h = 0; h < 2; h++) {
-        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
-        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
-    }
-    __syncthreads();                                     // every warp is done with its stages: reuse them for the merge
-    float* mo = reinterpret_cast<float*>(smem);          // [warp][16][HD], after the CTA merge: [0][16][HD] holds the CTA's sum
-    float* mml = mo + DEC_WARPS * 16 * MO_PITCH;         // [warp][16][2]
+    for (int nh = 0; nh < NH; nh++)
 #pragma unroll
-    for (int n = 0; n < HD / 8; n++) {
-        float* b = mo + (warp * 16) * MO_PITCH + n * 8 + t4 * 2;
-        *reinterpret_cast<float2*>(b + g * MO_PITCH) = make_float2(o[n][0], o[n][1]);
-        *reinterpret_cast<float2*>(b + (g + 8) * MO_PITCH) = make_float2(o[n][2], o[n][3]);
-    }
-    if (t4 == 0) {
-        mml[(warp * 16 + g) * 2] = m[0]; mml[(warp * 16 + g) * 2 + 1] = l[0];
-        mml[(warp * 16 + g + 8) * 2] = m[1]; mml[(warp * 16 + g + 8) * 2 + 1] = l[1];
-    }
+        for (int c = 0; c < 2; c++) {                    // the lanes that share t4 hold shares of the same heads' sums
+            l[nh][c] += __shfl_xor_sync(0xffffffffu, l[nh][c], 4);
+            l[nh][c] += __shfl_xor_sync(0xffffffffu, l[nh][c], 8);
+            l[nh][c] += __shfl_xor_sync(0xffffffffu, l[nh][c], 16);
+        }
+    __syncthreads();                                     // every warp is done with its stages: reuse them for the merge
+    float* mo = reinterpret_cast<float*>(smem);          // [warp][head][MO_PITCH]: every warp's partial output
+    float* mml = mo + DEC_WARPS * 16 * MO_PITCH;         // [warp][head][2]
+#pragma unroll
+    for (int nh = 0; nh < NH; nh++)
+#pragma unroll
+        for (int c = 0; c < 2; c++) {
+            const int head = nh * 8 + t4 * 2 + c;
+            float* b = mo + (warp * 16 + head) * MO_PITCH + g;
+#pragma unroll
+            for (int mt = 0; mt < HD / 16; mt++) {
+                b[mt * 16] = o[nh][mt][c];
+                b[mt * 16 + 8] = o[nh][mt][2 + c];
+            }
+            if (g == 0) {
+                mml[(warp * 16 + head) * 2] = m[nh][c];
+                mml[(warp * 16 + head) * 2 + 1] = l[nh][c];
+            }
+        }
     __syncthreads();
-    // Merge of the CTA's four warps, kept in registers until every thread has read what it needs.
+    // Merge of the CTA's warps, kept in registers until every thread has read what it needs.
     float cta_val[(16 * HD + DEC_WARPS * 32 - 1) / (DEC_WARPS * 32)];
     float cta_m = -INFINITY, cta_l = 0.0f;
     {
@@ -691,11 +912,24 @@ int check_common(int n_segments, int n_heads, int n_kv, int head_dim, int page_s
     return IB_OK;
 }
 
+// Tensor maps of the K and V pages of one cache entry, seen as matrices [pages * kv heads * 16, HD] (boxes of one page's
+// 16 rows x 64 elements). Only the head sizes whose pages arrive by tensor copy need them.
+int page_maps(const void* k_cache, const void* v_cache, int64_t n_pages, int n_kv, CUtensorMap* mk, CUtensorMap* mv) {
+    if (!TMA_PAGES) return IB_OK;
+    if ((uintptr_t(k_cache) & 15) || (uintptr_t(v_cache) & 15)) return ib::fail(IB_ERR_ARG, "attention_fast: the cache must be 16-byte aligned");
+    if (n_pages * n_kv * PAGE >= (1LL << 31)) return ib::fail(IB_ERR_ARG, "attention_fast: the cache has too many rows for a tensor map");
+    int rc = ib::get_map(k_cache, n_pages * n_kv * PAGE, HD, PAGE, mk);
+    if (rc) return rc;
+    return ib::get_map(v_cache, n_pages * n_kv * PAGE, HD, PAGE, mv);
+}
+
 int configure() {
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM);
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<false, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_decode_kernel<false, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_decode_kernel<true, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_decode_kernel<true, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM);
         if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM);
         if (e != cudaSuccess) return ib::fail(IB_ERR_CUDA, "attention_fast: cannot set shared memory size: %s", cudaGetErrorString(e));
         configured = true;
@@ -726,9 +960,12 @@ IB_EXPORT int ib_attention_fast(const void* q, const void* k_cache, const void* 
     p.n_super = n_super; p.workspace = workspace; p.counters = counters;
     if ((rc = configure())) return rc;
     if (has_decode) {
+        CUtensorMap mk = {}, mv = {};
+        if ((rc = page_maps(k_cache, v_cache, n_pages, n_kv, &mk, &mv))) return rc;
         const dim3 grid{unsigned(n_splits * n_super), unsigned(n_kv), unsigned(n_segments)};
-        rc = ib::launch("attention_fast (decode)", attn_decode_kernel<false>, grid, dim3(DEC_WARPS * 32), size_t(DEC_SMEM), stream,
-                        unsigned(n_splits), p);
+        // the heads of a group are the columns of one MMA tile (up to 8) or of two (up to 16)
+        rc = ib::launch("attention_fast (decode)", p.group <= 8 ? attn_decode_kernel<false, 1> : attn_decode_kernel<false, 2>, grid,
+                        dim3(DEC_WARPS * 32), size_t(DEC_SMEM), stream, unsigned(n_splits), mk, mv, p);
         if (rc) return rc;
     }
     if (max_q_len > 1) {
@@ -764,7 +1001,9 @@ IB_EXPORT int ib_attention_decode_fused(const void* qkv, const float* cos_t, con
     p.scale_log2 = scale * LOG2E; p.n_pages = n_pages; p.n_splits = n_splits; p.status = status;
     p.n_super = n_super; p.workspace = workspace; p.counters = counters;
     if ((rc = configure())) return rc;
+    CUtensorMap mk = {}, mv = {};
+    if ((rc = page_maps(k_cache, v_cache, n_pages, n_kv, &mk, &mv))) return rc;
     const dim3 grid{unsigned(n_splits * n_super), unsigned(n_kv), unsigned(n_segments)};
-    return ib::launch("attention_decode_fused", attn_decode_kernel<true>, grid, dim3(DEC_WARPS * 32), size_t(DEC_SMEM), stream,
-                      unsigned(n_splits), p);
+    return ib::launch("attention_decode_fused", p.group <= 8 ? attn_decode_kernel<true, 1> : attn_decode_kernel<true, 2>, grid,
+                      dim3(DEC_WARPS * 32), size_t(DEC_SMEM), stream, unsigned(n_splits), mk, mv, p);
 }

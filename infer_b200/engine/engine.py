@@ -98,12 +98,16 @@ GRAPH_WIDTH_PAGES = 32        # decode-only block tables are padded to a multipl
 GRAPH_WARMUP_STEPS = 2        # eager steps of a shape before its graph is captured
 MAX_GRAPHS = 48
 GRAPH_COPIES = 2              # executable copies per decode shape, launched in turn
-# Steps that hold prompt portions are captured too once their exact shape (segment lengths, wanted rows, table widths)
-# has come a few times, as it does when prompts are cut into portions of the token budget: up to this many shapes, one
-# executable each, and only steps of at most this many tokens (a graph keeps its activations allocated).
-PORTION_GRAPH_AFTER = 2
-MAX_PORTION_GRAPHS = 6
+# Steps that hold prompt portions are captured too when their exact shape (segment lengths, wanted rows, table widths)
+# comes a second time, as it does when prompts are cut into portions of the token budget or a short prompt joins a full
+# batch of decoding requests: the first step of a shape runs eagerly (about 10 microseconds of host time per launch, two
+# hundred launches), the second is captured, later ones are replayed. One executable each; a graph keeps its
+# activations allocated, so only steps of at most PORTION_GRAPH_MAX_TOKENS tokens are captured and the captured shapes
+# together hold at most PORTION_GRAPH_TOKEN_POOL tokens (the oldest goes first).
+PORTION_GRAPH_AFTER = 1
+MAX_PORTION_GRAPHS = 32
 PORTION_GRAPH_MAX_TOKENS = 8192
+PORTION_GRAPH_TOKEN_POOL = 16384
 
 
 class _GraphEntry:
@@ -302,15 +306,15 @@ class Engine:
                 portion = key[0] == "portions"
                 if portion:
                     old = [k for k in self._graphs if k[0] == "portions"]
-                    if len(old) >= MAX_PORTION_GRAPHS:
-                        self._graphs.pop(old[0])
+                    while old and (len(old) >= MAX_PORTION_GRAPHS or sum(sum(k[1]) for k in old) + T > PORTION_GRAPH_TOKEN_POOL):
+                        self._graphs.pop(old.pop(0))
                 elif len(self._graphs) >= MAX_GRAPHS:
                     self._graphs.pop(next(k for k in self._graphs if k[0] != "portions"))
                 entry = self._graphs[key] = _GraphEntry(torch.empty(buf.size, dtype=torch.int32, device=self.rt.device))
                 entry.pinned = [torch.empty(buf.size, dtype=torch.int32).pin_memory() for _ in range(2)]
                 entry.copied = [torch.cuda.Event() for _ in range(2)]
                 if portion:
-                    entry.copies, entry.warm = 1, GRAPH_WARMUP_STEPS - 1      # the shape has run eagerly before
+                    entry.copies, entry.warm = 1, GRAPH_WARMUP_STEPS          # the shape has run eagerly before
             # Two pinned staging buffers alternate. The copy out of a buffer is asynchronous: before the buffer is
             # written again, the copy that read it last (two steps ago) must have run, or a caller that issues steps
             # without ever waiting for the device would overwrite integers that an earlier step has not yet taken.

@@ -48,7 +48,7 @@ def _run(heads, kv, hd, window, segs, n_splits=None, seed=0, n_clusters=1):
     return got
 
 
-LAYOUTS = [(12, 2, 128), (14, 2, 64), (4, 4, 16), (8, 1, 32), (5, 5, 48), (3, 1, 96)]
+LAYOUTS = [(12, 2, 128), (14, 2, 64), (4, 4, 16), (8, 1, 32), (5, 5, 48), (3, 1, 96), (16, 1, 64), (24, 2, 32)]
 
 
 @pytest.mark.parametrize("heads,kv,hd", LAYOUTS)
