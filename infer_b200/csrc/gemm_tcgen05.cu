@@ -783,178 +783,6 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
     }
 }
 
-
-// ------------------------------------------------------------------------------------------------ 2-CTA kernel
-// A pair of CTAs (a cluster of two, on neighbouring SMs) computes 256 x 256 tiles with tcgen05.mma.cta_group::2: each
-// member holds 128 rows of the A tile and 128 rows of the B tile in its shared memory, the leader's MMA thread issues
-// one M=256 x N=256 x K=16 instruction for both, and each member's tensor memory receives its 128 rows of the
-// accumulator. A member loads (128 + 128) rows of operands per 128 x 256 outputs, a third less than the one-CTA tiles,
-// which were bound by the rate at which operand tiles arrive from L2. Persistent, two accumulators, as above.
-//   both members   warp 0 loads its halves (TMA with the .cta_group::2 form, bytes counted on the LEADER's full barrier);
-//                  warps 2-5 drain their 128 accumulator rows and arrive on the leader's acc_empty barrier;
-//   leader only    warp 1 issues the MMAs; its commits are multicast to both members' empty / acc_full barriers.
-constexpr int QSTAGES = 6;
-constexpr int Q_STAGE_BYTES = 2 * 128 * BK * 2;                  // 128 rows of A + 128 rows of B
-constexpr int Q_SMEM_BYTES = QSTAGES * Q_STAGE_BYTES + 1024 + 256;
-
-__device__ __forceinline__ uint32_t cluster_rank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
-__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar_cluster, int x, int y) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(dst), "l"(map), "r"(bar_cluster), "r"(x), "r"(y) : "memory");
-}
-__device__ __forceinline__ void umma2_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-}
-// Arrives, once every MMA issued so far has finished, on the barrier at this offset in BOTH members of the pair.
-__device__ __forceinline__ void umma2_commit_both(uint32_t bar) {
-    const uint16_t mask = 3;
-    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar), "h"(mask) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster) : "memory");
-}
-
-template <typename TOut>
-__global__ void __launch_bounds__(NUM_THREADS)
-gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const GemmParams p) {
-    extern __shared__ uint8_t smem_raw[];
-    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
-    constexpr int S = QSTAGES;
-    const uint32_t bars = base + S * Q_STAGE_BYTES;               // full[S], empty[S], acc_full[2], acc_empty[2]
-    volatile uint32_t* slots = reinterpret_cast<volatile uint32_t*>(base_ptr + S * Q_STAGE_BYTES + (2 * S + 4) * 8);
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t rank = cluster_rank();
-    const bool leader = rank == 0;
-    const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
-    const int tiles_m = int((p.rows_a + 255) / 256), tiles_n = int((p.rows_b + 255) / 256);
-    const int n_tiles = tiles_m * tiles_n;
-    const int n_kb = p.kb_total;
-    auto full_bar = [&](int s) { return bars + 8u * s; };
-    auto empty_bar = [&](int s) { return bars + 8u * (S + s); };
-    auto acc_full_bar = [&](int b) { return bars + 8u * (2 * S + b); };
-    auto acc_empty_bar = [&](int b) { return bars + 8u * (2 * S + 2 + b); };
-
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < S; s++) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-        for (int b = 0; b < 2; b++) { mbar_init(acc_full_bar(b), 1); mbar_init(acc_empty_bar(b), 8); }
-        slots[1] = 0;
-        fence_barrier_init();
-        prefetch_tensormap(&tm_a);
-        prefetch_tensormap(&tm_b);
-    }
-    if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(const_cast<uint32_t*>(&slots[0]))), "r"(512u) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
-    }
-    tc_fence_before();
-    __syncthreads();
-    cluster_sync();                                      // both members' barriers exist before either signals the other
-    tc_fence_after();
-    const uint32_t tmem_base = slots[0];
-
-    if (warp == 0) {
-        // ---------------------------------------------------------------- TMA producer (both members)
-        if (lane == 0) {
-            ib::pdl_wait();
-            int it = 0, issued = 0;
-            for (int tile = pair; tile < n_tiles && !slots[1]; tile += n_pairs) {
-                const int tm = tile % tiles_m, tn = tile / tiles_m;
-                for (int kb = 0; kb < n_kb; kb++, it++) {
-                    const int s = it % S;
-                    if (it >= S && !mbar_wait(empty_bar(s), ((it / S) - 1) & 1)) {
-                        atomicExch(p.status, STATUS_TIMEOUT_PRODUCER); slots[1] = 1; break;
-                    }
-                    if (slots[1]) break;
-                    const uint32_t a_dst = base + s * Q_STAGE_BYTES, b_dst = a_dst + 128 * BK * 2;
-                    const uint32_t leader_full = map_cluster(full_bar(s), 0);
-                    if (leader) mbar_expect_tx(full_bar(s), 2 * Q_STAGE_BYTES);          // both members' bytes
-                    tma_load_2d_pair(a_dst, &tm_a, leader_full, kb * BK, tm * 256 + int(rank) * 128);
-                    tma_load_2d_pair(b_dst, &tm_b, leader_full, kb * BK, tn * 256 + int(rank) * 128);
-                    issued = it + 1;
-                }
-            }
-            if (slots[1] && leader) {
-                // Drain: the leader's full barriers count both members' bytes; wait (bounded) for the stages that were
-                // armed, so that no copy lands after the pair has left (the member waits for the leader at the final
-                // cluster barrier).
-                for (int i = max(0, issued - S); i < issued; i++) mbar_wait(full_bar(i % S), (i / S) & 1);
-            }
-        }
-    } else if (warp == 1) {
-        // ---------------------------------------------------------------- MMA issuer (leader only)
-        if (lane == 0 && leader) {
-            // M = 256 over the pair, N = 256
-            constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(256 >> 3) << 17) | (uint32_t(256 >> 4) << 24);
-            int it = 0, lt = 0;
-            for (int tile = pair; tile < n_tiles && !slots[1]; tile += n_pairs, lt++) {
-                const int b = lt & 1;
-                if (lt >= 2 && !mbar_wait(acc_empty_bar(b), ((lt >> 1) - 1) & 1)) {      // both members have drained it
-                    atomicExch(p.status, STATUS_TIMEOUT_MMA); slots[1] = 1; break;
-                }
-                tc_fence_after();
-                const uint32_t d = tmem_base + uint32_t(b * 256);
-                for (int kb = 0; kb < n_kb; kb++, it++) {
-                    const int s = it % S;
-                    if (!mbar_wait(full_bar(s), (it / S) & 1)) {
-                        atomicExch(p.status, STATUS_TIMEOUT_MMA); slots[1] = 1; break;
-                    }
-                    tc_fence_after();
-                    const uint32_t a_addr = base + s * Q_STAGE_BYTES;
-                    const uint64_t ad = make_desc(a_addr), bd = make_desc(a_addr + 128 * BK * 2);
-#pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; k++)
-                        umma2_f16(d, ad + uint64_t(2 * k), bd + uint64_t(2 * k), idesc, (kb > 0 || k > 0) ? 1u : 0u);
-                    umma2_commit_both(empty_bar(s));
-                }
-                if (slots[1]) break;
-                umma2_commit_both(acc_full_bar(b));
-            }
-        }
-        ib::pdl_launch_dependents();
-    } else {
-        // ---------------------------------------------------------------- epilogue (warps 2..5, both members)
-        const int quad = warp & 3;
-        ib::pdl_wait();
-        int lt = 0;
-        for (int tile = pair; tile < n_tiles; tile += n_pairs, lt++) {
-            const int tm = tile % tiles_m, tn = tile / tiles_m;
-            const int b = lt & 1;
-            bool ok = !slots[1] && mbar_wait(acc_full_bar(b), (lt >> 1) & 1);
-            if (!ok && !slots[1]) { atomicExch(p.status, STATUS_TIMEOUT_EPILOGUE); slots[1] = 1; }
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            tc_fence_after();
-            const int64_t a_row = int64_t(tm) * 256 + int(rank) * 128 + quad * 32 + lane;
-#pragma unroll 1
-            for (int c = 0; c < 256; c += 16) {
-                uint32_t raw[16];
-                tmem_ld16(tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(b * 256 + c), raw);
-                tmem_ld_wait();
-                float v[16];
-#pragma unroll
-                for (int j = 0; j < 16; j++) v[j] = __uint_as_float(raw[j]);
-                epilogue_store<TOut>(p, v, a_row, int64_t(tn) * 256 + c);
-            }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(map_cluster(acc_empty_bar(b), 0));
-        }
-    }
-    tc_fence_before();
-    __syncthreads();
-    cluster_sync();                                      // neither member frees tensor memory or leaves while the other may signal it
-    if (warp == 1) {
-        tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
-    }
-}
-
 // ------------------------------------------------------------------------------------------------ host side
 
 using ib::get_map;
@@ -986,20 +814,6 @@ int launch_persistent(const CUtensorMap& ma, const CUtensorMap& mb, const GemmPa
     const int64_t tiles = WIDE ? ((p.rows_a + 127) / 128) * ((p.rows_b + PBN - 1) / PBN) : ((p.rows_a + PBM - 1) / PBM) * ((p.rows_b + PBN - 1) / PBN);
     const unsigned ctas = unsigned(tiles < sm_count ? tiles : sm_count);
     return ib::launch("gemm_tc", gemm_tc_persistent_kernel<PBN, WIDE, TOut>, dim3(ctas), dim3(NUM_THREADS), size_t(P_SMEM_BYTES), stream, 1u, ma, mb, p);
-}
-
-template <typename TOut>
-int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, int sm_count, cudaStream_t stream) {
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_pair_kernel<TOut>, cudaFuncAttributeMaxDynamicSharedMemorySize, Q_SMEM_BYTES);
-        if (e != cudaSuccess) return ib::fail(IB_ERR_CUDA, "gemm_tc: cannot set shared memory size: %s", cudaGetErrorString(e));
-        configured = true;
-    }
-    const int64_t tiles = ((p.rows_a + 255) / 256) * ((p.rows_b + 255) / 256);
-    int64_t pairs = sm_count / 2;
-    if (tiles < pairs) pairs = tiles;
-    return ib::launch("gemm_tc", gemm_tc_pair_kernel<TOut>, dim3(unsigned(pairs * 2)), dim3(NUM_THREADS), size_t(Q_SMEM_BYTES), stream, 2u, ma, mb, p);
 }
 
 // Stages of the ring: the default leaves room for a second CTA on the SM (prefill: one tile's epilogue overlaps the
@@ -1085,11 +899,6 @@ IB_EXPORT int ib_gemm_tc_plan(int64_t M, int64_t N, int64_t K, int sm_count, int
                 }
             }
         }
-        // pairs of CTAs on 256 x 256 tiles where those keep most pairs busy: correct, but measured no faster than the
-        // one-CTA 128 x 256 tiles (gate/up 97 against 93 us), so only with INFER_B200_GEMM_PAIR=1
-        static const bool pair_on = [] { const char* e = getenv("INFER_B200_GEMM_PAIR"); return e && e[0] == '1'; }();
-        const int64_t t256 = tm * ((N + 255) / 256), pairs = sm_count / 2;
-        if (pair_on && *bn >= 256 && pairs > 0 && double(t256) / double(((t256 + pairs - 1) / pairs) * pairs) >= 0.8) *bn = 1024;
     }
     *workspace_floats = (s > 1 && !*swap && !cluster) ? int64_t(s) * tiles * BM * (*bn) : 0;
     *n_counters = (s > 1 && !*swap && !cluster) ? tiles : 0;
@@ -1107,8 +916,8 @@ IB_EXPORT int ib_gemm_tc(const void* x, const void* w, const float* bias, const 
     if (M <= 0 || N <= 0) return IB_OK;
     if (K <= 0 || K % 8) return ib::fail(IB_ERR_ARG, "gemm_tc: K = %lld must be a positive multiple of 8", (long long)K);
     if ((uintptr_t(x) & 15) || (uintptr_t(w) & 15)) return ib::fail(IB_ERR_ARG, "gemm_tc: operand bases must be 16-byte aligned");
-    if (bn != 16 && bn != 32 && bn != 64 && bn != 128 && bn != 256 && bn != 352 && bn != 384 && bn != 512 && bn != 1024)
-        return ib::fail(IB_ERR_ARG, "gemm_tc: bn must be 16, 32, 64, 128, or 256 (the persistent kernel on 256 x 128 tiles), 352, 384, 512 (on 128 x 176, 128 x 192, 128 x 256 with one MMA per k-step) or 1024 (CTA pairs)");
+    if (bn != 16 && bn != 32 && bn != 64 && bn != 128 && bn != 256 && bn != 352 && bn != 384 && bn != 512)
+        return ib::fail(IB_ERR_ARG, "gemm_tc: bn must be 16, 32, 64, 128, or 256 (the persistent kernel on 256 x 128 tiles), 352, 384, 512 (on 128 x 176, 128 x 192, 128 x 256 with one MMA per k-step)");
     if (bn >= 256 && (swap || splits > 1)) return ib::fail(IB_ERR_ARG, "gemm_tc: the persistent kernel takes the plain mapping without K slices");
     if (!status) return ib::fail(IB_ERR_ARG, "gemm_tc: a status word is required");
     if (epi != 0 && epi != 2) return ib::fail(IB_ERR_ARG, "gemm_tc: unknown epilogue %d", epi);
@@ -1138,9 +947,9 @@ IB_EXPORT int ib_gemm_tc(const void* x, const void* w, const float* bias, const 
     CUtensorMap ma, mb;
     if (bn >= 256) {
         const bool wide = bn >= 352 && bn <= 512;
-        int rc = get_map(x, p.rows_a, K, (wide || bn == 1024) ? 128 : PBM, &ma);
+        int rc = get_map(x, p.rows_a, K, wide ? 128 : PBM, &ma);
         if (rc) return rc;
-        rc = get_map(w, p.rows_b, K, bn == 1024 ? 128 : (wide ? bn / 2 : 128), &mb);
+        rc = get_map(w, p.rows_b, K, wide ? bn / 2 : 128, &mb);
         if (rc) return rc;
         static int sms = 0;
         if (!sms) {
@@ -1149,7 +958,6 @@ IB_EXPORT int ib_gemm_tc(const void* x, const void* w, const float* bias, const 
                 return ib::fail(IB_ERR_CUDA, "gemm_tc: cannot read the number of SMs");
         }
         p.splits = 1; p.cluster_split = 0; p.stages = PSTAGES;
-        if (bn == 1024) return f32 ? launch_pair<float>(ma, mb, p, sms, stream) : launch_pair<bf16>(ma, mb, p, sms, stream);
         if (bn == 512) return f32 ? launch_persistent<256, true, float>(ma, mb, p, sms, stream) : launch_persistent<256, true, bf16>(ma, mb, p, sms, stream);
         if (bn == 384) return f32 ? launch_persistent<192, true, float>(ma, mb, p, sms, stream) : launch_persistent<192, true, bf16>(ma, mb, p, sms, stream);
         if (bn == 352) return f32 ? launch_persistent<176, true, float>(ma, mb, p, sms, stream) : launch_persistent<176, true, bf16>(ma, mb, p, sms, stream);

@@ -93,29 +93,6 @@ def test_gemm_tc_split_choices_agree():
         assert ((got - ref).abs() / cond).max().item() < 2e-6, splits
 
 
-@pytest.mark.parametrize("M,N,K", [(2048, 2048, 1536), (1100, 3000, 520), (300, 260, 72)])
-def test_gemm_tc_cta_pairs(M, N, K):
-    """The 2-CTA kernel (tcgen05.mma.cta_group::2 on 256 x 256 tiles; plan code 1024), which the planner does not pick
-    by default, against the plain kernel: exact tiles, ragged M / N / K, fewer tiles than CTA pairs; with bias and the
-    residual epilogue in place."""
-    from infer_b200 import fast_ops
-    g = torch.Generator(device=DEV).manual_seed(M + N + K)
-    x = torch.randn(M, K, device=DEV, generator=g).bfloat16()
-    w = (torch.randn(N, K, device=DEV, generator=g) * 0.05).bfloat16()
-    bias = torch.randn(N, device=DEV, generator=g)
-    res = torch.randn(M, N, device=DEV, generator=g)
-    cond = x.float().abs() @ w.float().abs().T + 1.0
-    st = fast_ops.device_state(DEV)
-    st.status.zero_()
-    plan = (0, 1024, 1, 0, 0)
-    got = fast_ops.gemm_tc(x, w, bias, None, torch.float32, plan=plan)
-    assert ((got - _ref(x, w, bias, None)).abs() / cond).max().item() < 2e-6
-    r2 = res.clone()
-    fast_ops.gemm_tc(x, w, None, r2, torch.float32, out=r2, plan=plan)
-    assert ((r2 - _ref(x, w, None, res)).abs() / cond).max().item() < 2e-6
-    assert st.status.item() == 0
-
-
 @pytest.mark.parametrize("code", [256, 352, 384, 512])
 @pytest.mark.parametrize("M,N,K", [(2048, 1536, 1536), (1100, 3000, 520), (300, 260, 72)])
 def test_gemm_tc_wide_tiles(M, N, K, code):
