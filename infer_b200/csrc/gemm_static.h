@@ -16,8 +16,10 @@
 // No call allocates or frees: no cudaMalloc, cudaFree, or allocating library routine.
 //
 // Limits and rules.
-//  - Shapes whose split-K plan needs more scratch than the array holds are refused with an error (nothing runs).
-//    Shapes that need no split (most large ones) always fit.
+//  - Only a plan that adds its K slices through global memory uses the array (ib_gemm_tc_plan states how many floats
+//    and counters that takes): products of more than 128 rows with very few output tiles. If such a plan needs more
+//    than the array holds, the call is refused with an error and nothing runs. Every other plan (no split, or slices
+//    that meet in a thread-block cluster's shared memory) is given no scratch at all and always fits.
 //  - Every call on a device shares the one array. Calls that are ordered (same stream, or otherwise serialised) are
 //    fine; calls that overlap on the GPU race on the scratch and give wrong sums. The array keeps the last call's
 //    partial tiles; the counters at its start are zeroed on the stream before each launch.
