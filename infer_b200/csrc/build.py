@@ -33,6 +33,7 @@ MODULES: Dict[str, str] = {
     "gemm": "gemm_tcgen05.cu",
     "attn": "attention_fast.cu",
     "attn_tc": "attention_tc.cu",
+    "capi": "capi.cpp",          # host code only: the C handle API over the engine (needs the interpreter's headers)
 }
 HEADERS = ["common.cuh", "gemm_static.h", "tma_map.cuh"]
 # modules that are compiled per model size: the variant that build_all() makes (others are built at first use)
@@ -41,6 +42,14 @@ DEFAULT_DEFINES = {"attn": {"IB_HEAD_DIM": 128}, "attn_tc": {"IB_HEAD_DIM": 128}
 
 class BuildError(RuntimeError):
     pass
+
+
+def _module_flags(module: str):
+    """Extra compiler flags of a module."""
+    if module == "capi":
+        import sysconfig
+        return ["-I", sysconfig.get_paths()["include"]]
+    return []
 
 
 def _find_nvcc() -> str:
@@ -119,7 +128,7 @@ def compile_module(module: str, defines: Optional[Mapping[str, object]] = None, 
             if os.path.isfile(out):
                 return out
             tmp = f"{out}.{os.getpid()}.tmp"
-            cmd = [nvcc] + NVCC_FLAGS + [f"-D{k}={v}" for k, v in sorted(defines.items())] + \
+            cmd = [nvcc] + NVCC_FLAGS + _module_flags(module) + [f"-D{k}={v}" for k, v in sorted(defines.items())] + \
                   ["-I", HERE, "-o", tmp, os.path.join(HERE, MODULES[module])]
             _say(f"compiling {MODULES[module]} for sm_100a (first use; this happens once) ...")
             t0 = time.time()
@@ -165,9 +174,10 @@ def load_module(module: str, defines: Optional[Mapping[str, object]] = None) -> 
             lib = ctypes.CDLL(path)
         except OSError as e:
             raise BuildError(f"cannot load {path}: {e}") from None
-        lib.ib_last_error.restype = ctypes.c_char_p
-        if os.environ.get("INFER_B200_PDL", "1") == "0":
-            lib.ib_set_pdl(0)           # launch every kernel fully serialised (for comparisons)
+        if hasattr(lib, "ib_last_error"):                            # (the kernel libraries; the C handle API has its own)
+            lib.ib_last_error.restype = ctypes.c_char_p
+            if os.environ.get("INFER_B200_PDL", "1") == "0":
+                lib.ib_set_pdl(0)       # launch every kernel fully serialised (for comparisons)
         _LOADED[path] = lib
     return lib
 
