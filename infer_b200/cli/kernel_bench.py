@@ -133,7 +133,7 @@ def main(argv=None) -> int:
                 return fast_ops.attention_decode_fused(qkv, cos, sin, ks[i], vs[i], table, seg_start, pos0, nh, nkv, hd, None,
                                                        1 / math.sqrt(hd), ctx + 1, True, args.splits or None)
             return fast_ops.attention_fast(q, ks[i], vs[i], table, seg_start, pos0, nh, nkv, hd, None, 1 / math.sqrt(hd),
-                                           q_len == 1, q_len, ctx + q_len, B, args.splits or None)
+                                           q_len == 1, q_len, ctx + q_len, B if q_len == 1 else 0, args.splits or None)
         med, mn = _time(run, n_layers, args.reps)
         nbytes = B * (ctx + q_len) * nkv * hd * 2 * 2
         flops = 4 * B * nh * hd * (q_len * ctx + q_len * (q_len + 1) / 2)

@@ -28,6 +28,8 @@
 // neither two threads per row nor a second MMA-issuing thread shortened it.
 // Every mbarrier wait is bounded; one that runs out raises the status word, and the CTA drains its copies,
 // frees its tensor memory and returns.
+#include <algorithm>
+
 #include "common.cuh"
 #include "tma_map.cuh"
 
@@ -132,6 +134,9 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
         ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
           "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
 }
+__device__ __forceinline__ void softmax_barrier() {         // the four softmax warps (threads 64..191) among themselves
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+}
 __device__ __forceinline__ float fast_exp2(float x) {        // ex2.approx: 2^-inf = 0, about 2 ulp
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -176,7 +181,18 @@ struct Params {
     float scale_log2;
     int64_t n_pages;
     int* status;
+    // A query tile's key tiles are shared among up to `split` CTAs (blockIdx.y = query tile x split + part), each with
+    // at least PART_MIN_TILES of them: a part leaves its rows of O (unnormalised), their reference maxima and sums in
+    // the workspace, and the part that arrives last at the tile's counter adds all parts in index order, divides and
+    // writes the output. Few long query tiles (a prompt on few heads, a portion behind a long context) fill the SMs
+    // that way, and the heaviest tile of a causal prompt no longer sets the kernel's time alone.
+    int split;
+    float* workspace;                        // [segments][heads][query tiles][split][PART_FLOATS]
+    unsigned int* counters;                  // [segments][heads][query tiles], zero between launches
 };
+constexpr int MAX_SPLIT = 4;
+constexpr int PART_MIN_TILES = 4;
+constexpr int PART_FLOATS = BM * HD + 2 * BM;   // O as [HD][BM] (a warp's rows side by side), then the maxima, then the sums
 
 __global__ void __launch_bounds__(NUM_THREADS)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -195,7 +211,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     // The last query tiles have the most keys: they start first, for every head.
-    const int h = blockIdx.x, qt = gridDim.y - 1 - blockIdx.y, seg = blockIdx.z;
+    const int n_qt = gridDim.y / p.split;
+    const int h = blockIdx.x, qt = n_qt - 1 - int(blockIdx.y) / p.split, part = int(blockIdx.y) % p.split, seg = blockIdx.z;
     const int t0 = p.seg_start[seg];
     const int q_len = p.seg_start[seg + 1] - t0;
     if (q_len <= 1 || qt * BM >= q_len) return;          // one-token segments belong to the decode kernel
@@ -205,8 +222,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     const int last_written = pos0 + q_len - 1;           // the last position whose k and v exist
     const int q_last = min(last_written, q_first + BM - 1);
     const int lo_key = p.window > 0 ? max(0, q_first - p.window + 1) : 0;
-    const int kt0 = lo_key / BN, kt1 = q_last / BN;
-    const int n_tiles = kt1 - kt0 + 1;
+    // this CTA's key tiles: all of the query tile's, or one of `n_parts` contiguous shares
+    const int all0 = lo_key / BN, all1 = q_last / BN;
+    const int n_all = all1 - all0 + 1;
+    const int n_parts = max(1, min(p.split, n_all / PART_MIN_TILES));
+    if (part >= n_parts) return;
+    const int kt0 = all0 + (n_all * part) / n_parts, kt1 = all0 + (n_all * (part + 1)) / n_parts - 1;
+    const int n_tiles = kt1 - kt0 + 1;                   // >= PART_MIN_TILES when the tile is shared, >= 1 otherwise
+    const int tile_id = (seg * p.n_heads + h) * n_qt + qt;
     const int* table = p.block_table + int64_t(seg) * p.max_blocks;
     // The page ids of this CTA's key range, checked, in shared memory (a read of the table in global memory costs the
     // producer a round trip to L2 per page otherwise); ranges longer than the array fall back to the table itself.
@@ -462,25 +485,88 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             ok = __all_sync(0xffffffffu, ok);
         }
         if (!ok && !slots[1]) { atomicExch(p.status, STATUS_TIMEOUT); slots[1] = 1; }
-        if (ok) {
-            tc_fence_after();
-            const int qi = qt * BM + r;
-            const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-            bf16* dst = p.out + (int64_t(t0 + qi) * p.n_heads + h) * HD;
-#pragma unroll 1
-            for (int c = 0; c < HD; c += 16) {
-                uint32_t o[16];
-                tmem_ld16(lane_addr + O_COL + c, o);
-                tmem_ld_wait();
-                if (qi < q_len) {
-                    uint32_t w[8];
+        const int qi = qt * BM + r;
+        bf16* dst = p.out + (int64_t(t0 + qi) * p.n_heads + h) * HD;
+        auto store16 = [&](int c, const float* v) {      // 16 outputs of this row from column c on
+            uint32_t w[8];
 #pragma unroll
-                    for (int e = 0; e < 8; e++) {
-                        __nv_bfloat162 two = __floats2bfloat162_rn(__uint_as_float(o[2 * e]) * inv, __uint_as_float(o[2 * e + 1]) * inv);
-                        w[e] = *reinterpret_cast<uint32_t*>(&two);
+            for (int e = 0; e < 8; e++) {
+                __nv_bfloat162 two = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
+                w[e] = *reinterpret_cast<uint32_t*>(&two);
+            }
+            *reinterpret_cast<uint4*>(dst + c) = make_uint4(w[0], w[1], w[2], w[3]);
+            *reinterpret_cast<uint4*>(dst + c + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+        };
+        if (n_parts == 1) {
+            if (ok) {
+                tc_fence_after();
+                const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+#pragma unroll 1
+                for (int c = 0; c < HD; c += 16) {
+                    uint32_t o[16];
+                    tmem_ld16(lane_addr + O_COL + c, o);
+                    tmem_ld_wait();
+                    float v[16];
+#pragma unroll
+                    for (int e = 0; e < 16; e++) v[e] = __uint_as_float(o[e]) * inv;
+                    if (qi < q_len) store16(c, v);
+                }
+            }
+        } else {
+            // Every softmax warp goes through both barriers whatever happened to it, so that a failed wait in one warp
+            // (the status word is raised then) cannot leave the others waiting; the counter is always brought back to 0.
+            float* parts = p.workspace + int64_t(tile_id) * p.split * PART_FLOATS;
+            float* mine = parts + part * PART_FLOATS;
+            if (ok) {
+                tc_fence_after();
+#pragma unroll 1
+                for (int c = 0; c < HD; c += 16) {
+                    uint32_t o[16];
+                    tmem_ld16(lane_addr + O_COL + c, o);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int e = 0; e < 16; e++) __stcg(mine + (c + e) * BM + r, __uint_as_float(o[e]));
+                }
+                __stcg(mine + HD * BM + r, m_ref);
+                __stcg(mine + HD * BM + BM + r, l);
+            }
+            __threadfence();
+            softmax_barrier();
+            if (threadIdx.x == 64) slots[2] = atomicAdd(p.counters + tile_id, 1u);
+            softmax_barrier();
+            if (slots[2] == uint32_t(n_parts - 1)) {     // all parts of this query tile are in the workspace
+                __threadfence();
+                if (threadIdx.x == 64) p.counters[tile_id] = 0u;
+                float m = -INFINITY;
+#pragma unroll
+                for (int i = 0; i < MAX_SPLIT; i++)
+                    if (i < n_parts) m = fmaxf(m, __ldcg(parts + i * PART_FLOATS + HD * BM + r));
+                float f[MAX_SPLIT], l_all = 0.0f;
+#pragma unroll
+                for (int i = 0; i < MAX_SPLIT; i++) {
+                    f[i] = 0.0f;
+                    if (i < n_parts) {
+                        const float mi = __ldcg(parts + i * PART_FLOATS + HD * BM + r);
+                        f[i] = mi == -INFINITY ? 0.0f : fast_exp2(mi - m);       // a part with no visible key adds nothing
+                        l_all += __ldcg(parts + i * PART_FLOATS + HD * BM + BM + r) * f[i];
                     }
-                    *reinterpret_cast<uint4*>(dst + c) = make_uint4(w[0], w[1], w[2], w[3]);
-                    *reinterpret_cast<uint4*>(dst + c + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+                }
+                const float inv = l_all > 0.0f ? 1.0f / l_all : 0.0f;
+#pragma unroll
+                for (int i = 0; i < MAX_SPLIT; i++) f[i] *= inv;
+#pragma unroll 1
+                for (int c = 0; c < HD; c += 16) {
+                    float v[16];
+#pragma unroll
+                    for (int e = 0; e < 16; e++) v[e] = 0.0f;
+#pragma unroll
+                    for (int i = 0; i < MAX_SPLIT; i++) {
+                        if (i < n_parts) {
+#pragma unroll
+                            for (int e = 0; e < 16; e++) v[e] = fmaf(__ldcg(parts + i * PART_FLOATS + (c + e) * BM + r), f[i], v[e]);
+                        }
+                    }
+                    if (qi < q_len) store16(c, v);
                 }
             }
         }
@@ -500,10 +586,13 @@ IB_EXPORT int ib_attention_tc_head_dim() { return HD; }
 // Attention of the segments with two or more tokens (one-token segments are skipped: the decode kernel serves them).
 // q, out: bfloat16 [tokens, heads * HD]; caches bfloat16 [pages, kv heads, 16, HD] holding this step's keys and values
 // already; block_table int32 [segments, max_blocks]; seg_start int32 [segments + 1]; seg_pos0 int32 [segments].
+// split: up to how many CTAs share the key tiles of one query tile (1: none); it is lowered to what the workspace
+// (floats) and the counters (one per segment, head and query tile, zero before and after) have room for.
 IB_EXPORT int ib_attention_prefill_tc(const void* q, const void* k_cache, const void* v_cache, void* out, const int* block_table,
                                       int max_blocks, const int* seg_start, const int* seg_pos0, int n_segments, int64_t n_tokens,
                                       int n_heads, int n_kv, int head_dim, int page_size, int window, float scale, int64_t n_pages,
-                                      int max_q_len, int* status, cudaStream_t stream) {
+                                      int max_q_len, int* status, cudaStream_t stream, int split, float* workspace,
+                                      int64_t workspace_floats, unsigned int* counters, int64_t n_counters) {
     if (n_segments <= 0 || max_q_len <= 1) return IB_OK;
     if (head_dim != HD) return ib::fail(IB_ERR_ARG, "attention_tc: built for head_dim %d, called with %d", HD, head_dim);
     if (page_size != PAGE) return ib::fail(IB_ERR_ARG, "attention_tc: pages must hold %d positions, got %d", PAGE, page_size);
@@ -529,7 +618,14 @@ IB_EXPORT int ib_attention_prefill_tc(const void* q, const void* k_cache, const 
     p.out = (bf16*)out; p.block_table = block_table; p.max_blocks = max_blocks; p.seg_start = seg_start; p.seg_pos0 = seg_pos0;
     p.n_heads = n_heads; p.n_kv = n_kv; p.group = n_heads / n_kv; p.window = window; p.scale_log2 = scale * LOG2E;
     p.n_pages = n_pages; p.status = status;
-    const dim3 grid{unsigned(n_heads), unsigned((max_q_len + BM - 1) / BM), unsigned(n_segments)};
+    // Sharing query tiles needs scratch for every (segment, head, query tile); with less than that, fewer parts.
+    const int64_t n_qt = (max_q_len + BM - 1) / BM, tiles = int64_t(n_segments) * n_heads * n_qt;
+    split = std::max(1, std::min(split, MAX_SPLIT));
+    if (!workspace || !counters || tiles > n_counters) split = 1;
+    while (split > 1 && tiles * split * PART_FLOATS > workspace_floats) split--;
+    if (n_qt * split > 65535) split = 1;
+    p.split = split; p.workspace = workspace; p.counters = counters;
+    const dim3 grid{unsigned(n_heads), unsigned(n_qt * split), unsigned(n_segments)};
     return ib::launch("attention_tc", attn_prefill_tc_kernel, grid, dim3(NUM_THREADS), size_t(SMEM_BYTES), stream, 1u, mq, mk, mv, p);
 }
 

@@ -226,7 +226,9 @@ __device__ __forceinline__ void epilogue_store(const GemmParams& p, const float*
             if (m < p.M && n0 < p.N) {
                 float act[8];
 #pragma unroll
-                for (int j = 0; j < 8; j++) act[j] = v[j] / (1.0f + __expf(-v[j])) * v[j + 8];
+                // the approximate division: an IEEE one made the epilogue of a 128 x 256 tile longer than the tile's MMAs
+                // (gate/up of a 2,048-token step: 94 us with it, 86 us without)
+                for (int j = 0; j < 8; j++) act[j] = __fdividef(v[j], 1.0f + __expf(-v[j])) * v[j + 8];
                 if constexpr (sizeof(TOut) == 2) {
                     if ((half & 7) == 0) {                      // 8 bfloat16 = one 16-byte store
                         __nv_bfloat162 h0 = __floats2bfloat162_rn(act[0], act[1]), h1 = __floats2bfloat162_rn(act[2], act[3]);

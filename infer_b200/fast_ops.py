@@ -224,12 +224,39 @@ def _decode_scratch(st, n_segments: int, n_kv: int, head_dim: int, clusters: int
 # leaves prefill to the mma.sync kernel.
 ATTENTION_TC = os.environ.get("INFER_B200_ATTN_TC", "1") == "1"
 ATTENTION_TC_HEAD_DIMS = (64, 128)
+# Sharing a query tile's keys among CTAs (INFER_B200_ATTN_TC_SPLIT=1 switches it off): the kernel's limits.
+ATTENTION_TC_MAX_SPLIT = int(os.environ.get("INFER_B200_ATTN_TC_SPLIT", "4"))
+ATTENTION_TC_PART_MIN_TILES = 4
+
+
+def prefill_split(sm_count: int, n_heads: int, n_prefill: int, max_q_len: int, max_ctx_len: int, window: Optional[int]) -> int:
+    """Into how many parts the tcgen05 prefill kernel may cut the keys of a query tile. One CTA serves 128 queries of a
+    head and walks over their keys in tiles of 128; it has an SM to itself, and starting and finishing a CTA costs
+    about as much as three key tiles. So keys are shared only while all CTAs still run at once (a portion behind a
+    long context on few heads: 48 CTAs of 36 key tiles become 144 of 12); with more CTAs than SMs the extra starts
+    cost more than the evening-out gains (measured at 2,048 tokens on 12 heads: 38.5 us whole, 42 us shared)."""
+    if n_prefill <= 0 or max_q_len <= 1:
+        return 1
+    ctx0 = max_ctx_len - max_q_len
+    key_tiles = []
+    for q_first in range(ctx0, max_ctx_len, 128):
+        q_last = min(max_ctx_len - 1, q_first + 127)
+        lo = max(0, q_first - window + 1) if window else 0
+        key_tiles.append(q_last // 128 - lo // 128 + 1)
+    if max(key_tiles) < 2 * ATTENTION_TC_PART_MIN_TILES:
+        return 1
+    for split in range(ATTENTION_TC_MAX_SPLIT, 1, -1):
+        ctas = n_heads * n_prefill * sum(max(1, min(split, n // ATTENTION_TC_PART_MIN_TILES)) for n in key_tiles)
+        if ctas <= sm_count:
+            return split
+    return 1
 
 
 def attention_fast(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
                    seg_start: torch.Tensor, seg_pos0: torch.Tensor, n_heads: int, n_kv: int, head_dim: int,
                    window: Optional[int], scale: float, has_decode: bool, max_q_len: int, max_ctx_len: int,
-                   n_decode: Optional[int] = None, n_splits: Optional[int] = None, n_clusters: int = 1) -> Optional[torch.Tensor]:
+                   n_decode: Optional[int] = None, n_splits: Optional[int] = None, n_clusters: int = 1,
+                   tc_split: Optional[int] = None) -> Optional[torch.Tensor]:
     """Tensor-core attention of a step's segments over the paged bfloat16 cache; None if the shape is refused.
     The library is compiled for this head size at first use."""
     n_pages, ckv, page_size, chd = k_cache.shape
@@ -257,10 +284,18 @@ def attention_fast(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor
     tc = ATTENTION_TC and max_q_len > 1 and head_dim in ATTENTION_TC_HEAD_DIMS and page_size == 16
     if tc:
         g = _fn("attn_tc", "ib_attention_prefill_tc", [c_void_p] * 5 + [c_int] + [c_void_p] * 2 + [c_int, c_int64] + [c_int] * 5 +
-                [c_float, c_int64, c_int] + [c_void_p] * 2, {"IB_HEAD_DIM": head_dim})
+                [c_float, c_int64, c_int] + [c_void_p] * 2 + [c_int, c_void_p, c_int64, c_void_p, c_int64], {"IB_HEAD_DIM": head_dim})
+        n_prefill = S - (n_decode or 0)
+        split = prefill_split(st.sm_count, n_heads, n_prefill, max_q_len, max_ctx_len, window) if tc_split is None else tc_split
+        tc_ws = tc_cnt = None
+        if split > 1:
+            tiles = S * n_heads * -(-max_q_len // 128)
+            tc_ws, tc_cnt = st.workspace(tiles * split * (128 * head_dim + 256)), st.counters(tiles)
+            ops.note("attention_prefill_tc:shared_query_tiles")
         _call(g, q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), block_table.data_ptr(),
               block_table.shape[1], seg_start.data_ptr(), seg_pos0.data_ptr(), S, T, n_heads, n_kv, head_dim, page_size,
-              int(window or 0), float(scale), n_pages, int(max_q_len), st.status.data_ptr(), _stream())
+              int(window or 0), float(scale), n_pages, int(max_q_len), st.status.data_ptr(), _stream(), int(split),
+              _ptr(tc_ws), 0 if tc_ws is None else tc_ws.numel(), _ptr(tc_cnt), 0 if tc_cnt is None else tc_cnt.numel())
         if max_q_len > 128:
             ops.note("attention_prefill_tc:several_query_tiles")
         if not has_decode:

@@ -12,7 +12,7 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
 
-def _run(heads, kv, hd, window, segs, n_splits=None, seed=0, n_clusters=1):
+def _run(heads, kv, hd, window, segs, n_splits=None, seed=0, n_clusters=1, tc_split=None):
     """segs: list of (context length before the step, tokens in the step)."""
     from infer_b200 import fast_ops
     lens = [c + n for c, n in segs]
@@ -38,7 +38,7 @@ def _run(heads, kv, hd, window, segs, n_splits=None, seed=0, n_clusters=1):
         q.reshape(T, -1).contiguous().to(DEV), kc.to(DEV), vc.to(DEV), table.to(DEV),
         torch.tensor(seg_start, dtype=torch.int32, device=DEV), torch.tensor([c for c, _ in segs], dtype=torch.int32, device=DEV),
         heads, kv, hd, window, scale, any(n == 1 for _, n in segs), max(n for _, n in segs), max(lens), n_splits=n_splits,
-        n_clusters=n_clusters)
+        n_clusters=n_clusters, tc_split=tc_split)
     assert out is not None
     assert st.status.item() == 0
     got = out.cpu().double().view_as(ref)
@@ -110,6 +110,37 @@ def test_prefill_long(heads, kv, hd, tc, monkeypatch):
     monkeypatch.setattr(fast_ops, "ATTENTION_TC", tc)
     _run(heads, kv, hd, None, [(0, 700), (1000, 300), (130, 129), (5, 2)])
     _run(heads, kv, hd, 300, [(0, 650), (900, 140)])
+
+
+@pytest.mark.parametrize("split", [2, 3, 4])
+@pytest.mark.parametrize("heads,kv,hd", [(12, 2, 128), (14, 2, 64)])
+def test_prefill_with_shared_query_tiles(heads, kv, hd, split):
+    """The keys of a query tile on several CTAs that meet in the workspace: query tiles with 1 to 17 key tiles (those
+    with fewer than eight stay whole, nine go two ways, twelve and more up to four ways), a portion behind a long
+    context, a two-token segment with twelve key tiles, one-token segments beside them, and a window that cuts the
+    first key tile of a part; twice, so that the counters must have come back to zero; the same bits whoever arrives
+    last."""
+    from infer_b200 import fast_ops
+    segs = [(0, 1100), (1900, 200), (1, 1), (1530, 2), (500, 1)]
+    first = _run(heads, kv, hd, None, segs, 2, seed=5, tc_split=split)
+    again = _run(heads, kv, hd, None, segs, 2, seed=5, tc_split=split)
+    assert torch.equal(first, again)
+    assert int(fast_ops.device_state(DEV)._counters.abs().sum()) == 0
+    whole = _run(heads, kv, hd, None, segs, 2, seed=5, tc_split=1)
+    assert (first - whole).abs().max() < 1e-2
+    _run(heads, kv, hd, 1200, [(700, 900), (2000, 130)], seed=6, tc_split=split)
+
+
+def test_prefill_split_follows_the_shape():
+    from infer_b200.fast_ops import prefill_split
+    assert prefill_split(148, 12, 1, 512, 4096, None) == 3         # a portion behind a long context: 48 long CTAs -> 144
+    assert prefill_split(148, 12, 1, 512, 8192, None) == 3
+    assert prefill_split(148, 12, 1, 1024, 1024, None) > 1         # 96 CTAs; the one query tile with 8 key tiles is shared
+    assert prefill_split(148, 12, 1, 2048, 2048, None) == 1        # 192 CTAs already: more starts cost more than they even out
+    assert prefill_split(148, 28, 1, 2048, 2048, None) == 1
+    assert prefill_split(148, 12, 4, 300, 600, None) == 1          # too few key tiles to share
+    assert prefill_split(148, 12, 1, 128, 4096, 256) == 1          # a window of three key tiles
+    assert prefill_split(148, 12, 0, 1, 4096, None) == 1           # decode only
 
 
 @pytest.mark.parametrize("heads,kv,hd", [(12, 2, 128), (4, 4, 16)])
