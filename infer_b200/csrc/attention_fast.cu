@@ -603,7 +603,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
     }
     if constexpr (!TMA_PAGES) cp_wait<0>();
     IB_DT(20);
-    ib::pdl_launch_dependents();
+    ib::pdl_launch_dependents();                         // (at the kernel's start instead: every batch size slower)
 #pragma unroll
     for (int nh = 0; nh < NH; nh++)
 #pragma unroll

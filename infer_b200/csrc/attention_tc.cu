@@ -270,6 +270,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = slots[0];
+    ib::pdl_launch_dependents();                         // the successor's CTAs set up as soon as an SM has room for them
     ib::pdl_wait();                                      // q and this step's cache rows come from the predecessor
 
     if (warp == 0) {

@@ -104,6 +104,27 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
 }
+// Weights are read once per step and never again before the whole model has streamed past: their tiles are marked
+// to leave L2 first, so that they do not push out what is read again soon (activations, the residual stream, cache
+// pages, and the kernels' own instructions: with the default policy a kernel that runs between other kernels spent
+// thousands of cycles in parts of its code it had not touched since its last launch).
+#ifndef IB_WEIGHTS_EVICT_FIRST
+#define IB_WEIGHTS_EVICT_FIRST 1
+#endif
+__device__ __forceinline__ uint64_t policy_evict_first() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ void tma_load_2d_once(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, uint64_t policy) {
+#if IB_WEIGHTS_EVICT_FIRST
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "l"(policy) : "memory");
+#else
+    tma_load_2d(dst, map, bar, x, y);
+#endif
+}
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
@@ -251,14 +272,19 @@ __device__ __forceinline__ void epilogue_store(const GemmParams& p, const float*
         const int64_t n = a_row;
         if (n >= p.N) return;
         const float b = p.bias ? p.bias[n] : 0.0f;
+        // The residual may be the output itself, so the compiler keeps every load behind the store before it: written
+        // as one loop, a row cost a trip to L2 per token. Each thread reads and writes the same addresses, so all of
+        // its residual values can be requested first.
+        float res[16];
 #pragma unroll
         for (int j = 0; j < 16; j++) {
             const int64_t m = b_row0 + j;
-            if (m < p.M && j < ncols) {
-                float x = v[j] + b;
-                if (p.residual) x += p.residual[m * p.N + n];
-                store_elem<TOut>(out + m * p.N + n, x);
-            }
+            res[j] = (p.residual && m < p.M && j < ncols) ? p.residual[m * p.N + n] : 0.0f;
+        }
+#pragma unroll
+        for (int j = 0; j < 16; j++) {
+            const int64_t m = b_row0 + j;
+            if (m < p.M && j < ncols) store_elem<TOut>(out + m * p.N + n, v[j] + b + res[j]);
         }
     } else {
         const int64_t m = a_row;
@@ -370,9 +396,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             int issued = 0;
             // With the weights on the A side (decode) their first stages set out before the wait: no kernel writes them.
             const int pre = p.swap ? min(S, n_kb) : 0;
+            const uint64_t once = policy_evict_first();
             for (int i = 0; i < pre; i++) {
                 mbar_expect_tx(full_bar(i), C::STAGE_BYTES);
-                tma_load_2d(base + i * C::STAGE_BYTES, &tm_a, full_bar(i), (kb0 + i) * BK, tile_a * BM);
+                tma_load_2d_once(base + i * C::STAGE_BYTES, &tm_a, full_bar(i), (kb0 + i) * BK, tile_a * BM, once);
             }
             IB_MT(2);
             ib::pdl_wait();
@@ -389,8 +416,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 if (slots[1]) break;
                 const uint32_t a_dst = base + s * C::STAGE_BYTES, b_dst = a_dst + C::A_BYTES;
                 mbar_expect_tx(full_bar(s), C::STAGE_BYTES);
-                tma_load_2d(a_dst, &tm_a, full_bar(s), (kb0 + i) * BK, tile_a * BM);
-                tma_load_2d(b_dst, &tm_b, full_bar(s), (kb0 + i) * BK, tile_b * BN);
+                if (p.swap) {
+                    tma_load_2d_once(a_dst, &tm_a, full_bar(s), (kb0 + i) * BK, tile_a * BM, once);
+                    tma_load_2d(b_dst, &tm_b, full_bar(s), (kb0 + i) * BK, tile_b * BN);
+                } else {
+                    tma_load_2d(a_dst, &tm_a, full_bar(s), (kb0 + i) * BK, tile_a * BM);
+                    tma_load_2d_once(b_dst, &tm_b, full_bar(s), (kb0 + i) * BK, tile_b * BN, once);
+                }
                 issued = i + 1;
             }
             IB_MT(4);
@@ -684,9 +716,11 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
 
     if (warp == 0) {
         // ---------------------------------------------------------------- TMA producer
+        if (lane != 0) ib::pdl_launch_dependents();      // the successor's CTAs set up as soon as an SM has room for them
         if (lane == 0) {
             ib::pdl_wait();
             int it = 0, issued = 0;
+            const uint64_t once = policy_evict_first();
             for (int tile = blockIdx.x; tile < n_tiles && !slots[1]; tile += gridDim.x) {
                 const int tm = tile % tiles_m, tn = tile / tiles_m;    // neighbouring CTAs share the weight tile
                 for (int kb = 0; kb < n_kb; kb++, it++) {
@@ -698,7 +732,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
                     const uint32_t a_dst = base + s * P_STAGE_BYTES, b_dst = a_dst + A_BYTES;
                     mbar_expect_tx(full_bar(s), A_BYTES + B_BYTES);
                     tma_load_2d(a_dst, &tm_a, full_bar(s), kb * BK, tm * TM);
-                    tma_load_2d(b_dst, &tm_b, full_bar(s), kb * BK, tn * TN);
+                    tma_load_2d_once(b_dst, &tm_b, full_bar(s), kb * BK, tn * TN, once);
                     issued = it + 1;
                 }
             }
@@ -743,7 +777,6 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
                 umma_commit(acc_full_bar(b));
             }
         }
-        ib::pdl_launch_dependents();
     } else {
         // ---------------------------------------------------------------- epilogue (warps 2..5)
         const int quad = warp & 3;

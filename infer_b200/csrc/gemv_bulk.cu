@@ -81,9 +81,24 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     }
     return false;
 }
-__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+// Weight rows are read once per step: they are marked to leave L2 first, so that streaming the model through it
+// does not push out what is read again soon (activations, cache pages, the kernels' own instructions).
+#ifndef IB_WEIGHTS_EVICT_FIRST
+#define IB_WEIGHTS_EVICT_FIRST 1
+#endif
+__device__ __forceinline__ uint64_t policy_evict_first() {
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar, uint64_t policy) {
+#if IB_WEIGHTS_EVICT_FIRST
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar), "l"(policy) : "memory");
+#else
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+#endif
 }
 __device__ __forceinline__ void mma_bf16(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
@@ -172,6 +187,7 @@ bulk_gemv_kernel(const GemvParams p) {
         int s = 0, st = 0;
         uint32_t round = 0;
         int64_t tile = group;
+        const uint64_t once = policy_evict_first();
         for (int64_t i = 0; i < n_iter; i++) {
             if (i == 1 && p.gate_ring) {
                 // With every SM's ring being filled at once, activations requested after the dependency wait would
@@ -194,7 +210,7 @@ bulk_gemv_kernel(const GemvParams p) {
             const uint32_t bytes = uint32_t(min(int64_t(KC), K - k0) * 2);
             if (lane == 0) mbar_expect_tx(full_bar(s), bytes * uint32_t(live_rows));
             __syncwarp();
-            if (lane < live_rows) bulk_load(stage0 + s * STAGE_BYTES + lane * PITCH, p.w + (n0 + lane) * K + k0, bytes, full_bar(s));
+            if (lane < live_rows) bulk_load(stage0 + s * STAGE_BYTES + lane * PITCH, p.w + (n0 + lane) * K + k0, bytes, full_bar(s), once);
             if (i == NS - 1 || i == n_iter - 1) ib::pdl_launch_dependents();     // the first ring is on its way
             if (++s == NS) { s = 0; round++; }
             if (++st == spt) { st = 0; tile += p.groups; }

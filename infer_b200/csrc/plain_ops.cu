@@ -60,6 +60,7 @@ __global__ void embedding_kernel(const T* __restrict__ table, const int* __restr
 template <typename TOut>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, float eps, int64_t hidden,
                                const int* __restrict__ rows, TOut* __restrict__ out) {
+    ib::pdl_launch_dependents();                          // the successor may set up (and request its weights) meanwhile
     ib::pdl_wait();
     __shared__ float red[32];
     const int64_t r_out = blockIdx.x;
@@ -85,6 +86,7 @@ template <typename TOut>
 __global__ void __launch_bounds__(NORM_THREADS)
 rmsnorm_vec_kernel(const float* __restrict__ x, const float* __restrict__ w, float eps, int64_t hidden,
                    const int* __restrict__ rows, TOut* __restrict__ out) {
+    ib::pdl_launch_dependents();                          // the successor may set up (and request its weights) meanwhile
     ib::pdl_wait();
     __shared__ float red[NORM_THREADS / 32];
     const int64_t r_out = blockIdx.x;
@@ -213,6 +215,7 @@ __global__ void rope_kv_write_kernel(const T* __restrict__ qkv, const float* __r
                                      int64_t max_blocks, T* __restrict__ q_out, T* __restrict__ k_cache,
                                      T* __restrict__ v_cache, int64_t n_tokens, int n_heads, int n_kv, int head_dim,
                                      int page_size, int write_cache, int64_t n_pages, int* status) {
+    ib::pdl_launch_dependents();                          // the successor may set up (and request its weights) meanwhile
     ib::pdl_wait();
     const int half = head_dim / 2;
     const int units = (n_heads + 2 * n_kv) * half;   // one unit = one (head, j) pair
@@ -259,6 +262,7 @@ rope_kv_write_vec_kernel(const bf16* __restrict__ qkv, const float* __restrict__
                          const int* __restrict__ block_table, int64_t max_blocks, bf16* __restrict__ q_out,
                          bf16* __restrict__ k_cache, bf16* __restrict__ v_cache, int64_t n_tokens, int n_heads, int n_kv,
                          int head_dim, int page_size, int write_cache, int64_t n_pages, int* status) {
+    ib::pdl_launch_dependents();                          // the successor may set up (and request its weights) meanwhile
     ib::pdl_wait();
     const int half = head_dim / 2, groups = half / 8;
     const int units = (n_heads + 2 * n_kv) * groups;
