@@ -388,6 +388,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     if (threadIdx.x == 0) IB_MT(1);
     // The set-up above overlapped the predecessor. Each role waits for it where it first touches what the predecessor
     // may have written: the producer before it loads activations, the epilogue before it reads or writes the output.
+    // K slices as a cluster, weights on the rows: the CTA that owns a few of the tile's token columns needs their
+    // residual values and its row's bias only after the cluster barrier, at the very end of the kernel; it asks for
+    // them as soon as the predecessor is done, so that no trip to L2 is left on the tail.
+    float own_res[16], own_bias = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 16; j++) own_res[j] = 0.0f;
+    const int own_per = (BN + p.splits - 1) / p.splits;
+    const bool own_early = p.cluster_split && p.swap && p.epi == 0 && own_per <= 16;
 
     if (warp == 0) {
         // ---------------------------------------------------------------- TMA producer
@@ -464,6 +472,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         const int r = quad * 32 + lane;                             // tile row
         const int64_t a_row = int64_t(tile_a) * BM + r;
         ib::pdl_wait();
+        if (own_early && a_row < p.N) {
+            const int c_begin = min(BN, split * own_per), n_own = min(BN, c_begin + own_per) - c_begin;
+            if (p.bias) own_bias = p.bias[a_row];
+            if (p.residual) {
+#pragma unroll
+                for (int j = 0; j < 16; j++) {
+                    const int64_t m = int64_t(tile_b) * BN + c_begin + j;
+                    if (j < n_own && m < p.M) own_res[j] = p.residual[m * p.N + a_row];
+                }
+            }
+        }
         bool ok = mbar_wait(tmem_full_bar, 0);
         if (!ok) { atomicExch(p.status, STATUS_TIMEOUT_EPILOGUE); slots[1] = 1; }
         ok = __all_sync(0xffffffffu, ok);
@@ -574,7 +593,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     for (int j = 0; j < 16; j++)
                         if (j < ncols) v[j] += recv[((z * per) + (c0 - c_begin) + j) * BM];
                 }
-                epilogue_store<TOut>(p, v, a_row, int64_t(tile_b) * BN + c0, ncols);
+                if (own_early) {
+                    if (a_row < p.N) {
+                        TOut* dst = reinterpret_cast<TOut*>(p.out) + (int64_t(tile_b) * BN + c0) * p.N + a_row;
+#pragma unroll
+                        for (int j = 0; j < 16; j++)
+                            if (j < ncols && int64_t(tile_b) * BN + c0 + j < p.M) store_elem<TOut>(dst + j * p.N, v[j] + own_bias + own_res[j]);
+                    }
+                } else {
+                    epilogue_store<TOut>(p, v, a_row, int64_t(tile_b) * BN + c0, ncols);
+                }
             }
         }
         if (threadIdx.x == 64) IB_MT(13);
