@@ -93,6 +93,9 @@ __device__ __forceinline__ uint32_t map_cluster(uint32_t local_smem, uint32_t ra
 __device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
     asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
 }
+__device__ __forceinline__ void st_cluster_v4(uint32_t addr, float a, float b, float c, float d) {
+    asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
 __device__ __forceinline__ float ld_cluster_f32(uint32_t addr) {
     float v;
     asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
@@ -498,7 +501,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 // received, in slice order, and nobody touches remote memory again.
                 const int per = (BN + p.splits - 1) / p.splits;               // columns per owner
                 const uint32_t recv = base + uint32_t(p.stages) * C::STAGE_BYTES + C::RECV_OFFSET;
-                const uint32_t mine = recv + uint32_t((split * per) * BM + r) * 4u;   // [slice][column of the owner][row]
+                // Where the owners' widths are multiples of four columns the owner's area is [slice][group of four
+                // columns][row][4]: a thread sends four columns in one 16-byte store and a warp's stores are contiguous;
+                // otherwise [slice][column][row] with single floats.
+                const bool vec = (per & 3) == 0;
+                const uint32_t mine = vec ? recv + uint32_t(split * (per >> 2) * BM + r) * 16u : recv + uint32_t((split * per) * BM + r) * 4u;
                 int owner = 0, lc = 0;                            // (carried along: no division per column)
                 uint32_t dst = map_cluster(mine, 0u);
 #pragma unroll 1
@@ -506,11 +513,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     uint32_t raw[16];
                     tmem_ld16(tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(c), raw);
                     tmem_ld_wait();
+                    if (vec) {
 #pragma unroll
-                    for (int j = 0; j < 16; j++) {
-                        st_cluster_f32(dst, __uint_as_float(raw[j]));
-                        dst += BM * 4u;
-                        if (++lc == per) { lc = 0; owner++; dst = map_cluster(mine, uint32_t(owner)); }
+                        for (int g = 0; g < 4; g++) {
+                            st_cluster_v4(dst, __uint_as_float(raw[4 * g]), __uint_as_float(raw[4 * g + 1]),
+                                          __uint_as_float(raw[4 * g + 2]), __uint_as_float(raw[4 * g + 3]));
+                            dst += BM * 16u;
+                            lc += 4;
+                            if (lc == per) { lc = 0; owner++; if (owner < p.splits) dst = map_cluster(mine, uint32_t(owner)); }
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; j++) {
+                            if (owner < p.splits) st_cluster_f32(dst, __uint_as_float(raw[j]));
+                            dst += BM * 4u;
+                            if (++lc == per) { lc = 0; owner++; if (owner < p.splits) dst = map_cluster(mine, uint32_t(owner)); }
+                        }
                     }
                 }
             } else if (p.splits == 1) {
@@ -582,16 +600,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             const int64_t a_row = int64_t(tile_a) * BM + r;
             const int per = (BN + p.splits - 1) / p.splits;
             const int c_begin = min(BN, split * per), c_end = min(BN, c_begin + per);
-            const float* recv = reinterpret_cast<const float*>(base_ptr + size_t(p.stages) * C::STAGE_BYTES + C::RECV_OFFSET) + r;
+            const float* recv = reinterpret_cast<const float*>(base_ptr + size_t(p.stages) * C::STAGE_BYTES + C::RECV_OFFSET);
+            const bool vec = (per & 3) == 0;
             for (int c0 = c_begin; c0 < c_end; c0 += 16) {
                 const int ncols = min(16, c_end - c0);
                 float v[16];
 #pragma unroll
                 for (int j = 0; j < 16; j++) v[j] = 0.0f;
                 for (int z = 0; z < p.splits; z++) {
+                    if (vec) {
+                        const float4* src = reinterpret_cast<const float4*>(recv) + (z * (per >> 2) + ((c0 - c_begin) >> 2)) * BM + r;
 #pragma unroll
-                    for (int j = 0; j < 16; j++)
-                        if (j < ncols) v[j] += recv[((z * per) + (c0 - c_begin) + j) * BM];
+                        for (int g = 0; g < 4; g++) {
+                            if (4 * g < ncols) {
+                                const float4 f = src[g * BM];
+                                v[4 * g] += f.x; v[4 * g + 1] += f.y; v[4 * g + 2] += f.z; v[4 * g + 3] += f.w;
+                            }
+                        }
+                    } else {
+                        const float* src = recv + ((z * per) + (c0 - c_begin)) * BM + r;
+#pragma unroll
+                        for (int j = 0; j < 16; j++)
+                            if (j < ncols) v[j] += src[j * BM];
+                    }
                 }
                 if (own_early) {
                     if (a_row < p.N) {
