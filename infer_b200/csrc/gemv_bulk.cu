@@ -126,8 +126,8 @@ struct GemvParams {
     int64_t N, K;
     int cluster;              // CTAs per tile
     int gate_ring;            // 1: the ring's second slot is requested only after the consumers have requested the activations
-    int nw_smem;              // 1: the fused norm's weight is staged in shared memory behind the ring (measured: q/k/v
-                              //    4.1 -> 3.2 us; with every SM's ring filling at once, gate/up, it costs 0.4 us instead)
+    int nw_smem;              // 1: the fused norm's weight is staged in shared memory behind the ring by asynchronous
+                              //    copies (up to 8 rows of activations; measured: q/k/v 4.1 -> 3.2 us)
     int kc;                   // elements of K per stage and row: a multiple of 64, at most KC_MAX
     int ns;                   // stages in the ring: 2 .. NS_MAX, ns * ROWS * (kc * 2 + 64) <= RING_BYTES
     int64_t tiles;
@@ -232,8 +232,11 @@ bulk_gemv_kernel(const GemvParams p) {
     constexpr bool NW_SMEM = NWS;              // (a template parameter: as a run-time flag it cost 1 us per kernel)
     if (p.norm_w) {
         if constexpr (NW_SMEM) {
+            // asynchronous copies, awaited only where the weight is used: a CTA that starts after its predecessor has
+            // finished (most of gate/up's) then has this trip to L2 and the activations' in flight together
             for (int64_t k = threadIdx.x * 4; k < K; k += WARPS * 32 * 4)
-                *reinterpret_cast<float4*>(nw_s + k) = __ldg(reinterpret_cast<const float4*>(p.norm_w + k));
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(nw_s + k)), "l"(p.norm_w + k) : "memory");
+            asm volatile("cp.async.commit_group;" ::: "memory");
         } else {
 #pragma unroll
             for (int u = 0; u < CPW_MAX; u++) {
@@ -303,6 +306,7 @@ bulk_gemv_kernel(const GemvParams p) {
                 ss[nt] += __shfl_xor_sync(0xffffffffu, ss[nt], 2);
                 if (t == 0) sumsq[warp][nt * 8 + g] = ss[nt];
             }
+            if constexpr (NW_SMEM) asm volatile("cp.async.wait_all;" ::: "memory");      // the norm's weight: visible after the barrier
             asm volatile("bar.sync 1, 256;" ::: "memory");
             IB_GT(61);
             float scale[NT];
@@ -536,7 +540,7 @@ IB_EXPORT int ib_linear_skinny_bulk(const void* x, const float* norm_w, float no
     p.M = int(M); p.N = N; p.K = K; p.cluster = cluster; p.status = status; p.tiles = tiles; p.kc = kc; p.ns = ns;
     // gate the ring's second slot where the whole GPU's rings fill at once (a CTA per half SM) and a tile is one stage
     p.gate_ring = (n_stages == 1 && cluster == 1 && tiles >= 2LL * sms) ? 1 : 0;
-    p.nw_smem = (norm_w && !p.gate_ring) ? 1 : 0;
+    p.nw_smem = norm_w ? 1 : 0;
     p.prefetch = prefetch; p.prefetch_bytes = prefetch_bytes & ~int64_t(15);
     // Two CTAs fit an SM; with more tiles than that, a CTA walks over several and its ring never drains between them.
     constexpr int64_t PER_SM = IB_GEMV_CTAS_PER_SM;
