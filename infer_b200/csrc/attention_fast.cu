@@ -123,9 +123,15 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
     }
     return false;
 }
+// A page of the cache for the decode kernel: a decode step reads every page of its requests once, so the tiles are
+// marked to leave L2 first; with the default policy a batch's cache (134 MB per layer at 64 x 2,048 tokens) pushed
+// out what the neighbouring kernels read again: their activations and their own instructions (batch 64: 2.21 -> 2.07 ms
+// per step; batch 8: 1.033 -> 1.021).
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-                 ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "l"(pol) : "memory");
 }
 // Byte offset of the 16-byte chunk c of row r inside a page tile of the decode ring: swizzled 128-byte lines in tiles
 // of 64 elements (what the tensor copy writes), or padded rows.
