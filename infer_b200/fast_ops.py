@@ -205,7 +205,8 @@ def _decode_splits(st, n_decode: int, n_kv: int, visible: int):
     units = max(1, n_decode * n_kv)
     pages = max(1, -(-visible // 16))
     n = 1
-    while n < 8 and units * n < st.sm_count and pages // (2 * n) >= 8:
+    # (with nearly a CTA per SM already, two slices do not pay for their merge: 25.1 against 26.2 us at batch 64)
+    while n < 8 and units * n < st.sm_count and pages // (2 * n) >= 8 and not (n == 1 and 6 * units >= 5 * st.sm_count):
         n *= 2
     clusters = 1
     if n == 8 and pages >= 8 * ATTENTION_CLUSTER_FROM:

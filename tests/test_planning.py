@@ -55,7 +55,8 @@ def test_decode_attention_slices_and_clusters():
     from infer_b200 import fast_ops
     st = types.SimpleNamespace(sm_count=SMS)
     assert fast_ops._decode_splits(st, 8, 2, 2048) == (8, 1)      # the serving shape: 128 CTAs, one cluster each
-    assert fast_ops._decode_splits(st, 64, 2, 2048) == (2, 1)     # enough requests: two slices
+    assert fast_ops._decode_splits(st, 64, 2, 2048) == (1, 1)     # 128 CTAs for 148 SMs: a second slice would not pay for its merge
+    assert fast_ops._decode_splits(st, 48, 2, 2048) == (2, 1)     # 96: two slices
     assert fast_ops._decode_splits(st, 1, 2, 100) == (1, 1)       # 7 pages: not worth cutting
     assert fast_ops._decode_splits(st, 8, 2, 8192) == (8, 1)      # the second level does not pay yet
     n, c = fast_ops._decode_splits(st, 1, 2, 30000)
