@@ -61,7 +61,7 @@ def main(argv=None) -> int:
     ap.add_argument("--kv-heads", type=int, default=2)
     ap.add_argument("--head-dim", type=int, default=128)
     ap.add_argument("--splits", type=int, default=0)
-    ap.add_argument("--bn", type=int, default=0, help="tc: the tile code instead of the planner's (many tokens, no K slices)")
+    ap.add_argument("--bn", type=int, default=0, help="tc: the tile code instead of the planner's (many tokens; 768 with --splits 2, 4 or 8: K slices as a cluster)")
     ap.add_argument("--cluster", type=int, default=0)
     ap.add_argument("--fused", action="store_true", help="attention: the decode kernel that also rotates and stores k/v")
     ap.add_argument("--norm", action="store_true", help="skinny kernel with the fused RMSNorm prologue")
@@ -93,7 +93,7 @@ def main(argv=None) -> int:
             plan = (plan[0], plan[1], args.splits, args.splits * tiles * 128 * plan[1], tiles)
 
         if plan is not None and args.bn:
-            plan = (0, args.bn, 1, 0, 0)
+            plan = (0, args.bn, (args.splits or 2) if args.bn == 768 else 1, 0, 0)
 
         def run(i):
             r = res

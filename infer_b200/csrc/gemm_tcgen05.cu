@@ -198,6 +198,9 @@ struct GemmParams {
     int stages;                          // stages of the operand ring in use (<= Cfg::MAX_STAGES)
     int cluster_split;                   // 1: the K slices of a tile are the CTAs of one cluster (grid.x) and are added
                                          //    through distributed shared memory; no workspace, no counters
+    int recv_in_ring;                    // 1: the slices' columns are received in the operand ring itself, once every slice
+                                         //    of the cluster is done with its ring (one more cluster barrier; for tiles whose
+                                         //    float columns would not fit behind the ring)
 };
 
 template <int BN> struct Cfg {
@@ -205,7 +208,7 @@ template <int BN> struct Cfg {
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int STAGES = BN >= 128 ? 3 : (BN >= 64 ? 4 : 5);       // <= ~100 KB: two CTAs per SM
-    static constexpr int MAX_STAGES = BN >= 128 ? 6 : 8;                    // a CTA alone on its SM (decode: all of the ring in flight)
+    static constexpr int MAX_STAGES = BN >= 256 ? 4 : (BN >= 128 ? 6 : 8);  // a CTA alone on its SM (decode: all of the ring in flight)
     static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
     static constexpr int SMEM_EXTRA = 1024 /*alignment slack*/ + 256 /*barriers*/;
     static constexpr int RECV_OFFSET = 256;                                 // behind the barriers
@@ -400,6 +403,47 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     const int own_per = (BN + p.splits - 1) / p.splits;
     const bool own_early = p.cluster_split && p.swap && p.epi == 0 && own_per <= 16;
 
+    // K slices as a cluster: every slice pushes the columns of its float tile to the CTA that owns them, through
+    // distributed shared memory; after a cluster barrier the owners add what they received, in slice order, and
+    // nobody touches remote memory again. The receive area lies behind the ring (a fast slice may push while the
+    // owner's ring is still in use) or, for wide tiles, is the ring itself, after a cluster barrier of its own.
+    // Called by the epilogue warps once their accumulator is complete.
+    auto push_partials = [&]() {
+        const int quad = warp & 3, r = quad * 32 + lane;
+        const int per = (BN + p.splits - 1) / p.splits;               // columns per owner
+        const uint32_t recv = p.recv_in_ring ? base : base + uint32_t(p.stages) * C::STAGE_BYTES + C::RECV_OFFSET;
+        // Where the owners' widths are multiples of four columns the owner's area is [slice][group of four
+        // columns][row][4]: a thread sends four columns in one 16-byte store and a warp's stores are contiguous;
+        // otherwise [slice][column][row] with single floats.
+        const bool vec = (per & 3) == 0;
+        const uint32_t mine = vec ? recv + uint32_t(split * (per >> 2) * BM + r) * 16u : recv + uint32_t((split * per) * BM + r) * 4u;
+        int owner = 0, lc = 0;                            // (carried along: no division per column)
+        uint32_t dst = map_cluster(mine, 0u);
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 16) {
+            uint32_t raw[16];
+            tmem_ld16(tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(c), raw);
+            tmem_ld_wait();
+            if (vec) {
+#pragma unroll
+                for (int g = 0; g < 4; g++) {
+                    st_cluster_v4(dst, __uint_as_float(raw[4 * g]), __uint_as_float(raw[4 * g + 1]),
+                                  __uint_as_float(raw[4 * g + 2]), __uint_as_float(raw[4 * g + 3]));
+                    dst += BM * 16u;
+                    lc += 4;
+                    if (lc == per) { lc = 0; owner++; if (owner < p.splits) dst = map_cluster(mine, uint32_t(owner)); }
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; j++) {
+                    if (owner < p.splits) st_cluster_f32(dst, __uint_as_float(raw[j]));
+                    dst += BM * 4u;
+                    if (++lc == per) { lc = 0; owner++; if (owner < p.splits) dst = map_cluster(mine, uint32_t(owner)); }
+                }
+            }
+        }
+    };
+
     if (warp == 0) {
         // ---------------------------------------------------------------- TMA producer
         if (lane != 0) ib::pdl_launch_dependents();
@@ -495,42 +539,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             const int n_tiles = gridDim.x * gridDim.y;
             const int tile = tile_b * gridDim.x + tile_a;
             if (p.cluster_split) {
-                // The K slices of a tile are the CTAs of one cluster. Every slice pushes the columns of its float tile to
-                // the CTA that owns them (a receive area behind the ring: a fast slice may push while the owner's ring is
-                // still in use), through distributed shared memory; after one cluster barrier the owners add what they
-                // received, in slice order, and nobody touches remote memory again.
-                const int per = (BN + p.splits - 1) / p.splits;               // columns per owner
-                const uint32_t recv = base + uint32_t(p.stages) * C::STAGE_BYTES + C::RECV_OFFSET;
-                // Where the owners' widths are multiples of four columns the owner's area is [slice][group of four
-                // columns][row][4]: a thread sends four columns in one 16-byte store and a warp's stores are contiguous;
-                // otherwise [slice][column][row] with single floats.
-                const bool vec = (per & 3) == 0;
-                const uint32_t mine = vec ? recv + uint32_t(split * (per >> 2) * BM + r) * 16u : recv + uint32_t((split * per) * BM + r) * 4u;
-                int owner = 0, lc = 0;                            // (carried along: no division per column)
-                uint32_t dst = map_cluster(mine, 0u);
-#pragma unroll 1
-                for (int c = 0; c < BN; c += 16) {
-                    uint32_t raw[16];
-                    tmem_ld16(tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(c), raw);
-                    tmem_ld_wait();
-                    if (vec) {
-#pragma unroll
-                        for (int g = 0; g < 4; g++) {
-                            st_cluster_v4(dst, __uint_as_float(raw[4 * g]), __uint_as_float(raw[4 * g + 1]),
-                                          __uint_as_float(raw[4 * g + 2]), __uint_as_float(raw[4 * g + 3]));
-                            dst += BM * 16u;
-                            lc += 4;
-                            if (lc == per) { lc = 0; owner++; if (owner < p.splits) dst = map_cluster(mine, uint32_t(owner)); }
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 16; j++) {
-                            if (owner < p.splits) st_cluster_f32(dst, __uint_as_float(raw[j]));
-                            dst += BM * 4u;
-                            if (++lc == per) { lc = 0; owner++; if (owner < p.splits) dst = map_cluster(mine, uint32_t(owner)); }
-                        }
-                    }
-                }
+                if (!p.recv_in_ring) push_partials();
             } else if (p.splits == 1) {
 #pragma unroll 1
                 for (int c = 0; c < BN; c += 16) {
@@ -591,6 +600,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         }
     }
     if (p.cluster_split) {
+        if (p.recv_in_ring) {
+            __syncwarp();
+            cluster_sync();                              // every slice's MMAs are complete: the rings are free
+            if (warp >= 2 && !slots[1]) { tc_fence_after(); push_partials(); }
+        }
         if (threadIdx.x == 64) IB_MT(11);
         __syncwarp();
         cluster_sync();                                  // every slice's pushes have arrived
@@ -600,7 +614,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             const int64_t a_row = int64_t(tile_a) * BM + r;
             const int per = (BN + p.splits - 1) / p.splits;
             const int c_begin = min(BN, split * per), c_end = min(BN, c_begin + per);
-            const float* recv = reinterpret_cast<const float*>(base_ptr + size_t(p.stages) * C::STAGE_BYTES + C::RECV_OFFSET);
+            const float* recv = reinterpret_cast<const float*>(p.recv_in_ring ? base_ptr : base_ptr + size_t(p.stages) * C::STAGE_BYTES + C::RECV_OFFSET);
             const bool vec = (per & 3) == 0;
             for (int c0 = c_begin; c0 < c_end; c0 += 16) {
                 const int ncols = min(16, c_end - c0);
@@ -891,7 +905,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, di
         configured = true;
     }
     if (p.stages < 1 || p.stages > C::MAX_STAGES) return ib::fail(IB_ERR_ARG, "gemm_tc: %d stages (at most %d)", p.stages, C::MAX_STAGES);
-    const size_t smem = size_t(p.stages) * C::STAGE_BYTES + C::SMEM_EXTRA + (p.cluster_split ? C::RECV_BYTES : 0);
+    const size_t smem = size_t(p.stages) * C::STAGE_BYTES + C::SMEM_EXTRA + (p.cluster_split && !p.recv_in_ring ? C::RECV_BYTES : 0);
     if (smem > size_t(C::SMEM_BYTES)) return ib::fail(IB_ERR_ARG, "gemm_tc: %d stages and the receive area do not fit", p.stages);
     return ib::launch("gemm_tc", gemm_tc_kernel<BN, TOut>, grid, dim3(NUM_THREADS), smem, stream,
                       p.cluster_split ? unsigned(p.splits) : 1u, ma, mb, p);
@@ -982,16 +996,36 @@ IB_EXPORT int ib_gemm_tc_plan(int64_t M, int64_t N, int64_t K, int sm_count, int
         const int64_t tm = (M + PBM - 1) / PBM, tm128 = (M + 127) / 128;
         const int64_t t128 = tm * ((N + 127) / 128);
         static const bool wide_on = [] { const char* e = getenv("INFER_B200_GEMM_WIDE"); return !(e && e[0] == '0'); }();
-        if (t128 * 2 >= sm_count) {
-            *bn = 256;
-            if (wide_on) {
-                int64_t best = -1;
-                for (int width : {256, 192, 176}) {
-                    const int64_t t = tm128 * ((N + width - 1) / width);
-                    const int64_t cost = ((t + sm_count - 1) / sm_count) * (width + 224);
-                    if (best < 0 || cost < best) { best = cost; *bn = 2 * width; }
-                }
+        int64_t best = -1, best_tiles = 0;
+        int best_code = 256;
+        for (int width : {256, 192, 176}) {
+            const int64_t t = tm128 * ((N + width - 1) / width);
+            const int64_t cost = ((t + sm_count - 1) / sm_count) * (width + 224);
+            if (best < 0 || cost < best) { best = cost; best_code = 2 * width; best_tiles = t; }
+        }
+        // Also where the tiles fill only 40 % of the SMs (a 512-token portion of a prompt at 3584 features: 84 tiles):
+        // the one-tile kernel without K slices then reads (128 + 128) operand rows per 128 x 128 outputs on every SM at
+        // once and loses to it (down at 7B sizes, 512 tokens: 127 us against 105; q/k/v 28 against 24).
+        if (t128 * 2 >= sm_count || (wide_on && best_tiles * 5 >= int64_t(sm_count) * 2)) *bn = wide_on ? best_code : 256;
+        // A long K on tiles that leave SMs idle (down at 3584 features, a 512-token portion: 84 tiles of 176 columns,
+        // 296 k-blocks each): tiles of 128 x 256 whose K slices form a cluster of 2, 4 or 8 (bn = 768 stands for them),
+        // the slices' columns meeting in the owners' operand rings. Estimated in MMA cycles per CTA; the slices pay
+        // for their exchange with about eight k-blocks.
+        static const bool sliced_on = [] { const char* e = getenv("INFER_B200_GEMM_SLICED"); return !(e && e[0] == '0'); }();
+        const int64_t t256 = tm128 * ((N + 255) / 256);
+        int slices = 0;
+        for (int c : {2, 4, 8})
+            if (t256 * c <= sm_count && kb_total / c >= 16) slices = c;
+        if (sliced_on && slices) {
+            const int64_t sliced = (int64_t(kb_total + slices - 1) / slices + 8) * 256;
+            int64_t other;
+            if (*bn >= 256) {
+                const int64_t width = *bn == 256 ? 256 : *bn / 2, t = *bn == 256 ? t128 : tm128 * ((N + width - 1) / width);
+                other = ((t + sm_count - 1) / sm_count) * kb_total * width;
+            } else {
+                other = ((tiles + sm_count - 1) / sm_count) * kb_total * 256;      // 128 x 128 tiles run at about half the rate
             }
+            if (sliced * 23 < other * 20) { *bn = 768; s = slices; *splits = s; cluster = true; }
         }
     }
     *workspace_floats = (s > 1 && !*swap && !cluster) ? int64_t(s) * tiles * BM * (*bn) : 0;
@@ -1010,9 +1044,13 @@ IB_EXPORT int ib_gemm_tc(const void* x, const void* w, const float* bias, const 
     if (M <= 0 || N <= 0) return IB_OK;
     if (K <= 0 || K % 8) return ib::fail(IB_ERR_ARG, "gemm_tc: K = %lld must be a positive multiple of 8", (long long)K);
     if ((uintptr_t(x) & 15) || (uintptr_t(w) & 15)) return ib::fail(IB_ERR_ARG, "gemm_tc: operand bases must be 16-byte aligned");
-    if (bn != 16 && bn != 32 && bn != 64 && bn != 128 && bn != 256 && bn != 352 && bn != 384 && bn != 512)
-        return ib::fail(IB_ERR_ARG, "gemm_tc: bn must be 16, 32, 64, 128, or 256 (the persistent kernel on 256 x 128 tiles), 352, 384, 512 (on 128 x 176, 128 x 192, 128 x 256 with one MMA per k-step)");
-    if (bn >= 256 && (swap || splits > 1)) return ib::fail(IB_ERR_ARG, "gemm_tc: the persistent kernel takes the plain mapping without K slices");
+    if (bn != 16 && bn != 32 && bn != 64 && bn != 128 && bn != 256 && bn != 352 && bn != 384 && bn != 512 && bn != 768)
+        return ib::fail(IB_ERR_ARG, "gemm_tc: bn must be 16, 32, 64, 128, or 256 (the persistent kernel on 256 x 128 tiles), 352, 384, 512 (on 128 x 176, 128 x 192, 128 x 256 with one MMA per k-step) or 768 (one 128 x 256 tile per CTA, K slices as a cluster)");
+    const bool sliced_wide = bn == 768;
+    if (sliced_wide) {
+        if (swap || workspace || (splits != 2 && splits != 4 && splits != 8)) return ib::fail(IB_ERR_ARG, "gemm_tc: 128 x 256 tiles with K slices take the plain mapping, 2, 4 or 8 slices and no workspace");
+        bn = 256;
+    } else if (bn >= 256 && (swap || splits > 1)) return ib::fail(IB_ERR_ARG, "gemm_tc: the persistent kernel takes the plain mapping without K slices");
     if (!status) return ib::fail(IB_ERR_ARG, "gemm_tc: a status word is required");
     if (epi != 0 && epi != 2) return ib::fail(IB_ERR_ARG, "gemm_tc: unknown epilogue %d", epi);
     if (epi == 2 && (N % 16 || bias || residual)) return ib::fail(IB_ERR_ARG, "gemm_tc: the SwiGLU epilogue needs N %% 16 == 0 and no bias or residual");
@@ -1028,6 +1066,8 @@ IB_EXPORT int ib_gemm_tc(const void* x, const void* w, const float* bias, const 
     p.kb_per_split = (p.kb_total + splits - 1) / splits;
     p.splits = (p.kb_total + p.kb_per_split - 1) / p.kb_per_split;
     p.cluster_split = (p.splits > 1 && !workspace) ? 1 : 0;
+    p.recv_in_ring = sliced_wide ? 1 : 0;
+    if (sliced_wide && !p.cluster_split) return ib::fail(IB_ERR_ARG, "gemm_tc: K = %lld is too short for %d slices of 128 x 256 tiles", (long long)K, splits);
     if (p.cluster_split && (p.splits > 8 || (!swap && (BM % p.splits || (BM / p.splits) % 16))))
         return ib::fail(IB_ERR_ARG, "gemm_tc: split-K without a workspace takes at most 8 slices, in the plain mapping 2, 4 or 8 (whole 16-column chunks per owner)");
     if (p.splits > 1 && !p.cluster_split && !counters) return ib::fail(IB_ERR_ARG, "gemm_tc: split-K through the workspace needs counters");
@@ -1039,7 +1079,7 @@ IB_EXPORT int ib_gemm_tc(const void* x, const void* w, const float* bias, const 
     const bool f32 = out_dtype == IB_F32;
     if (!f32 && out_dtype != IB_BF16) return ib::fail(IB_ERR_ARG, "gemm_tc: unknown output dtype %d", out_dtype);
     CUtensorMap ma, mb;
-    if (bn >= 256) {
+    if (bn >= 256 && !sliced_wide) {
         const bool wide = bn >= 352 && bn <= 512;
         int rc = get_map(x, p.rows_a, K, wide ? 128 : PBM, &ma);
         if (rc) return rc;
@@ -1061,6 +1101,10 @@ IB_EXPORT int ib_gemm_tc(const void* x, const void* w, const float* bias, const 
     if (rc) return rc;
     rc = get_map(swap ? x : w, p.rows_b, K, bn, &mb);
     if (rc) return rc;
+    if (sliced_wide) {
+        p.stages = p.kb_per_split >= 4 ? 4 : 3;          // the ring also receives the slices' columns: 128 KB
+        return f32 ? launch<256, float>(ma, mb, p, grid, stream) : launch<256, bf16>(ma, mb, p, grid, stream);
+    }
     p.stages = bn == 16 ? pick_stages<16>(p) : bn == 32 ? pick_stages<32>(p) : bn == 64 ? pick_stages<64>(p) : pick_stages<128>(p);
     switch (bn) {
         case 16: return f32 ? launch<16, float>(ma, mb, p, grid, stream) : launch<16, bf16>(ma, mb, p, grid, stream);

@@ -108,7 +108,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = Non
     f = _fn("gemm", "ib_gemm_tc", [c_void_p] * 5 + [c_int64] * 3 + [c_int] * 5 + [c_void_p] * 4)
     _call(f, x.data_ptr(), w.data_ptr(), _ptr(bias), _ptr(residual), out.data_ptr(), M, N, K, dtype_code(out_dtype),
           2 if swiglu else 0, swap, bn, splits, _ptr(ws), _ptr(cnt), st.status.data_ptr(), _stream())
-    ops.note("gemm_tc:persistent" if bn >= 256 else ("gemm_tc:swapped" if swap else "gemm_tc:one_tile"))
+    ops.note("gemm_tc:sliced_wide" if bn == 768 else "gemm_tc:persistent" if bn >= 256 else ("gemm_tc:swapped" if swap else "gemm_tc:one_tile"))
     return out
 
 

@@ -120,6 +120,33 @@ def test_gemm_tc_wide_tiles(M, N, K, code):
     assert st.status.item() == 0
 
 
+@pytest.mark.parametrize("M,N,K,slices", [(512, 3584, 4736, 2), (540, 1000, 2056, 4), (130, 520, 8192, 8), (300, 256, 1024, 2)])
+def test_gemm_tc_wide_tiles_with_k_slices(M, N, K, slices):
+    """128 x 256 tiles whose K slices are the CTAs of a cluster and exchange their columns through the operand rings
+    (plan code 768): ragged M and N, a K tail, 2, 4 and 8 slices; bias, residual in place, SwiGLU; against float64."""
+    from infer_b200 import fast_ops
+    g = torch.Generator(device=DEV).manual_seed(M + N + K)
+    x = torch.randn(M, K, device=DEV, generator=g).bfloat16()
+    w = (torch.randn(N, K, device=DEV, generator=g) * 0.05).bfloat16()
+    bias = torch.randn(N, device=DEV, generator=g)
+    res = torch.randn(M, N, device=DEV, generator=g)
+    ref = x.double() @ w.double().T
+    cond = x.float().abs() @ w.float().abs().T + 1.0
+    st = fast_ops.device_state(DEV)
+    st.status.zero_()
+    plan = (0, 768, slices, 0, 0)
+    got = fast_ops.gemm_tc(x, w, bias, None, torch.float32, plan=plan)
+    assert ((got.double() - (ref + bias.double())).abs() / cond).max().item() < 2e-6
+    r2 = res.clone()
+    fast_ops.gemm_tc(x, w, None, r2, torch.float32, out=r2, plan=plan)
+    assert ((r2.double() - (ref + res.double())).abs() / cond).max().item() < 2e-6
+    if N % 16 == 0:
+        act = fast_ops.gemm_tc(x, w, out_dtype=torch.bfloat16, plan=plan, swiglu=True)
+        same = fast_ops.gemm_tc(x, w, out_dtype=torch.bfloat16, plan=(0, 128, 1, 0, 0), swiglu=True)
+        assert (act.float() - same.float()).abs().max().item() <= 2.0 ** -6 * same.float().abs().max().item()
+    assert st.status.item() == 0
+
+
 def test_gemm_tc_refuses_what_it_cannot_do():
     from infer_b200 import fast_ops
     x = torch.randn(4, 100, device=DEV).bfloat16()            # K = 100 is not a multiple of 8

@@ -44,6 +44,10 @@ def test_many_tokens_take_the_persistent_kernel_with_the_width_that_fills_the_sm
     assert _plan(2048, 1536, 8960) == (0, 352, 1, 0, 0)           # 16 x 9 tiles of 176 columns = 144 CTAs
     assert _plan(2048, 1536, 1536) == (0, 352, 1, 0, 0)
     assert _plan(3000, 3584, 3584)[1] in (352, 384, 512)
+    # a long K on few tiles: 128 x 256 tiles with K slices as a cluster (5 x 14 tiles x 2 slices = 140 CTAs)
+    assert _plan(540, 3584, 18944) == (0, 768, 2, 0, 0)
+    assert _plan(512, 3584, 18944) == (0, 768, 2, 0, 0)
+    assert _plan(512, 4608, 3584)[1] == 352                        # 56 k-blocks: the slices' exchange would not pay
 
 
 def test_refused_shapes():
