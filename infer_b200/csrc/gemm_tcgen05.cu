@@ -1007,23 +1007,34 @@ IB_EXPORT int ib_gemm_tc_plan(int64_t M, int64_t N, int64_t K, int sm_count, int
         // the one-tile kernel without K slices then reads (128 + 128) operand rows per 128 x 128 outputs on every SM at
         // once and loses to it (down at 7B sizes, 512 tokens: 127 us against 105; q/k/v 28 against 24).
         if (t128 * 2 >= sm_count || (wide_on && best_tiles * 5 >= int64_t(sm_count) * 2)) *bn = wide_on ? best_code : 256;
-        // A long K on tiles that leave SMs idle (down at 3584 features, a 512-token portion: 84 tiles of 176 columns,
-        // 296 k-blocks each): tiles of 128 x 256 whose K slices form a cluster of 2, 4 or 8 (bn = 768 stands for them),
-        // the slices' columns meeting in the owners' operand rings. Estimated in MMA cycles per CTA; the slices pay
-        // for their exchange with about eight k-blocks.
-        static const bool sliced_on = [] { const char* e = getenv("INFER_B200_GEMM_SLICED"); return !(e && e[0] == '0'); }();
-        const int64_t t256 = tm128 * ((N + 255) / 256);
+    }
+    // A long K on tiles that leave SMs idle (down at 3584 features, a 512-token portion: 84 tiles of 176 columns, 296
+    // k-blocks each; or at 1536 features: 48 tiles of 128 columns in two slices): tiles of 128 x 256 whose K slices form
+    // a cluster of 2, 4 or 8 (bn = 768 stands for them), the slices' columns meeting in the owners' operand rings.
+    // The ways are compared by a model fitted to measurements (unit: the time of one k-block of a sliced tile, 0.38 us):
+    // a CTA of 128 x 128 or of 128 x 256 takes one unit per k-block, the persistent kernel 0.4 + width / 330; beside
+    // that a one-tile kernel costs 20 units, a sliced wide one 34 (40 with eight slices: the exchange), the persistent
+    // one 10. A grid of clusters runs at once only if it leaves the SMs free that clusters cannot use.
+    static const bool sliced_on = [] { const char* e = getenv("INFER_B200_GEMM_SLICED"); return !(e && e[0] == '0'); }();
+    if (!*swap && sliced_on && sm_count > 0) {
+        auto room = [&](int c) -> int64_t { return c == 1 ? 2 * int64_t(sm_count) : (c == 2 ? sm_count - 4 : sm_count - sm_count / 7); };
+        const int64_t tm128 = (M + 127) / 128, t256 = tm128 * ((N + 255) / 256);
         int slices = 0;
-        for (int c : {2, 4, 8})
-            if (t256 * c <= sm_count && kb_total / c >= 16) slices = c;
-        if (sliced_on && slices) {
-            const int64_t sliced = (int64_t(kb_total + slices - 1) / slices + 8) * 256;
+        int64_t sliced = 0;                                       // in hundredths of a unit
+        for (int c : {2, 4, 8}) {
+            if (t256 * c > room(c) || kb_total / c < 16) continue;
+            const int64_t est = 100 * (int64_t(kb_total + c - 1) / c) + (c == 8 ? 4000 : 3400);
+            if (!slices || est < sliced) { slices = c; sliced = est; }
+        }
+        if (slices) {
             int64_t other;
-            if (*bn >= 256) {
-                const int64_t width = *bn == 256 ? 256 : *bn / 2, t = *bn == 256 ? t128 : tm128 * ((N + width - 1) / width);
-                other = ((t + sm_count - 1) / sm_count) * kb_total * width;
-            } else {
-                other = ((tiles + sm_count - 1) / sm_count) * kb_total * 256;      // 128 x 128 tiles run at about half the rate
+            if (*bn >= 256) {                                     // the persistent kernel
+                const int64_t width = *bn == 256 ? 256 : *bn / 2, rows = *bn == 256 ? 256 : 128;
+                const int64_t t = ((M + rows - 1) / rows) * ((N + (*bn == 256 ? 128 : width) - 1) / (*bn == 256 ? 128 : width));
+                other = ((t + sm_count - 1) / sm_count) * kb_total * (40 + width * 100 / 330) + 1000;
+            } else {                                              // one 128 x 128 tile per CTA, s slices
+                const int64_t ctas = tiles * s, cap = cluster ? room(s) : 2 * int64_t(sm_count);
+                other = ((ctas + cap - 1) / cap) * 100 * (int64_t(kb_total + s - 1) / s) + 2000;
             }
             if (sliced * 23 < other * 20) { *bn = 768; s = slices; *splits = s; cluster = true; }
         }

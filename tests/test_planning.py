@@ -32,7 +32,8 @@ def test_middling_token_counts_take_the_plain_mapping():
     assert _plan(129, 1536, 8960)[:2] == (0, 128)
     # 24 tiles: 4 slices of K as a cluster (8 would leave a third of the CTAs to a second round), no scratch
     assert _plan(256, 1536, 8960) == (0, 128, 4, 0, 0)
-    assert _plan(512, 1536, 8960) == (0, 128, 2, 0, 0)
+    assert _plan(768, 1536, 8960) == (0, 128, 2, 0, 0)             # 72 tiles in two slices: 144 CTAs run at once
+    assert _plan(512, 1536, 8960) == (0, 768, 4, 0, 0)             # 24 wide tiles in four slices instead of 48 in two
     # very few tiles: up to 16 slices through the workspace, with one counter per tile
     swap, bn, splits, ws, counters = _plan(200, 300, 4096)
     assert (swap, bn, splits, counters) == (0, 128, 16, 6) and ws == 16 * 6 * 128 * 128
