@@ -186,6 +186,7 @@ struct Params {
     // the workspace, and the part that arrives last at the tile's counter adds all parts in index order, divides and
     // writes the output. Few long query tiles (a prompt on few heads, a portion behind a long context) fill the SMs
     // that way, and the heaviest tile of a causal prompt no longer sets the kernel's time alone.
+    int early_release;                       // 1: the successor is released at the kernel's start (few CTAs: a short kernel)
     int split;
     float* workspace;                        // [segments][heads][query tiles][split][PART_FLOATS]
     unsigned int* counters;                  // [segments][heads][query tiles], zero between launches
@@ -270,7 +271,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = slots[0];
-    ib::pdl_launch_dependents();                         // the successor's CTAs set up as soon as an SM has room for them
+    if (p.early_release) ib::pdl_launch_dependents();    // (pays for short kernels only: see the GEMM's note)
     ib::pdl_wait();                                      // q and this step's cache rows come from the predecessor
 
     if (warp == 0) {
@@ -626,6 +627,7 @@ IB_EXPORT int ib_attention_prefill_tc(const void* q, const void* k_cache, const 
     while (split > 1 && tiles * split * PART_FLOATS > workspace_floats) split--;
     if (n_qt * split > 65535) split = 1;
     p.split = split; p.workspace = workspace; p.counters = counters;
+    p.early_release = int64_t(n_segments) * n_heads * n_qt * split <= 296 ? 1 : 0;
     const dim3 grid{unsigned(n_heads), unsigned(n_qt * split), unsigned(n_segments)};
     return ib::launch("attention_tc", attn_prefill_tc_kernel, grid, dim3(NUM_THREADS), size_t(SMEM_BYTES), stream, 1u, mq, mk, mv, p);
 }

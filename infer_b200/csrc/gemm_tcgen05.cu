@@ -198,6 +198,13 @@ struct GemmParams {
     int stages;                          // stages of the operand ring in use (<= Cfg::MAX_STAGES)
     int cluster_split;                   // 1: the K slices of a tile are the CTAs of one cluster (grid.x) and are added
                                          //    through distributed shared memory; no workspace, no counters
+    int early_release;                   // persistent kernel: 1 = the successor is released at the kernel's start (its CTAs
+                                         //    set up wherever an SM has room), 0 = after the MMA loop. Early costs where
+                                         //    kernels are long (a 2,048-token step at 5120 features: 60 against 57 ms; the
+                                         //    waiting CTAs are not free on a power-bound GPU) and is kept for short ones
+    int weights_once;                    // persistent kernel: 1 = the weight tiles carry the L2 evict-first policy (a matrix
+                                         //    that fits L2 beside the activations; a larger one is evicted between the row
+                                         //    tiles' reads: 2 % slower at 3584 and 5120 features)
     int recv_in_ring;                    // 1: the slices' columns are received in the operand ring itself, once every slice
                                          //    of the cluster is done with its ring (one more cluster barrier; for tiles whose
                                          //    float columns would not fit behind the ring)
@@ -789,7 +796,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
 
     if (warp == 0) {
         // ---------------------------------------------------------------- TMA producer
-        if (lane != 0) ib::pdl_launch_dependents();      // the successor's CTAs set up as soon as an SM has room for them
+        if (p.early_release && lane != 0) ib::pdl_launch_dependents();
         if (lane == 0) {
             ib::pdl_wait();
             int it = 0, issued = 0;
@@ -805,7 +812,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
                     const uint32_t a_dst = base + s * P_STAGE_BYTES, b_dst = a_dst + A_BYTES;
                     mbar_expect_tx(full_bar(s), A_BYTES + B_BYTES);
                     tma_load_2d(a_dst, &tm_a, full_bar(s), kb * BK, tm * TM);
-                    tma_load_2d_once(b_dst, &tm_b, full_bar(s), kb * BK, tn * TN, once);
+                    if (p.weights_once) tma_load_2d_once(b_dst, &tm_b, full_bar(s), kb * BK, tn * TN, once);
+                    else tma_load_2d(b_dst, &tm_b, full_bar(s), kb * BK, tn * TN);
                     issued = it + 1;
                 }
             }
@@ -850,6 +858,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid
                 umma_commit(acc_full_bar(b));
             }
         }
+        ib::pdl_launch_dependents();                     // (unless that happened at the start)
     } else {
         // ---------------------------------------------------------------- epilogue (warps 2..5)
         const int quad = warp & 3;
@@ -1078,6 +1087,7 @@ IB_EXPORT int ib_gemm_tc(const void* x, const void* w, const float* bias, const 
     p.splits = (p.kb_total + p.kb_per_split - 1) / p.kb_per_split;
     p.cluster_split = (p.splits > 1 && !workspace) ? 1 : 0;
     p.recv_in_ring = sliced_wide ? 1 : 0;
+    p.weights_once = 1; p.early_release = 1;
     if (sliced_wide && !p.cluster_split) return ib::fail(IB_ERR_ARG, "gemm_tc: K = %lld is too short for %d slices of 128 x 256 tiles", (long long)K, splits);
     if (p.cluster_split && (p.splits > 8 || (!swap && (BM % p.splits || (BM / p.splits) % 16))))
         return ib::fail(IB_ERR_ARG, "gemm_tc: split-K without a workspace takes at most 8 slices, in the plain mapping 2, 4 or 8 (whole 16-column chunks per owner)");
@@ -1103,6 +1113,13 @@ IB_EXPORT int ib_gemm_tc(const void* x, const void* w, const float* bias, const 
                 return ib::fail(IB_ERR_CUDA, "gemm_tc: cannot read the number of SMs");
         }
         p.splits = 1; p.cluster_split = 0; p.stages = PSTAGES;
+        p.weights_once = N * K * 2 <= (64LL << 20) ? 1 : 0;
+        {
+            // k-blocks a CTA goes through: up to about 300 (120 us) the successor is released at once
+            const int64_t tm_rows = wide ? 128 : PBM, tn_cols = wide ? bn / 2 : 128;
+            const int64_t n_tiles = ((M + tm_rows - 1) / tm_rows) * ((N + tn_cols - 1) / tn_cols);
+            p.early_release = ((n_tiles + sms - 1) / sms) * p.kb_total * (wide ? 1 : 2) <= 300 ? 1 : 0;
+        }
         if (bn == 512) return f32 ? launch_persistent<256, true, float>(ma, mb, p, sms, stream) : launch_persistent<256, true, bf16>(ma, mb, p, sms, stream);
         if (bn == 384) return f32 ? launch_persistent<192, true, float>(ma, mb, p, sms, stream) : launch_persistent<192, true, bf16>(ma, mb, p, sms, stream);
         if (bn == 352) return f32 ? launch_persistent<176, true, float>(ma, mb, p, sms, stream) : launch_persistent<176, true, bf16>(ma, mb, p, sms, stream);
