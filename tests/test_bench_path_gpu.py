@@ -109,6 +109,23 @@ def test_portions_of_changing_size_above_and_below_128_tokens(dtype):
     _assert_bench_kernels_ran(before, dtype)
 
 
+def test_portions_behind_a_long_context_share_their_query_tiles():
+    """A 1,400-token prompt in portions of 300: from 1,024 tokens on a portion's query tiles have eight and more key
+    tiles and few CTAs, so the tcgen05 attention shares their keys among CTAs that meet in the workspace (asserted
+    from the launcher's counter); its logits against the plain implementation like every other cutting."""
+    reqs = {"long": H.random_ids(CFG, 1400, 5)}
+    ids = reqs["long"]
+    steps = []
+    for i in range(0, len(ids), 300):
+        n = min(300, len(ids) - i)
+        steps.append({"entries": [("long", ids[i:i + n], list(range(max(0, n - 40), n)))], "end": []})
+    steps[-1]["end"] = ["long"]
+    before = _counts()
+    got = H.run_trace(_engine(torch.bfloat16, max_tokens=1472), steps)
+    _check(torch.bfloat16, got, reqs)
+    assert _ran(before, "attention_prefill_tc:shared_query_tiles") > 0, "no portion's query tiles were shared among CTAs"
+
+
 def _mixed(reqs, max_tokens, seed=3, max_live=4):
     """Up to four live requests; a step takes a prompt portion of 2..260 tokens from those still in their prompt and
     one token from those decoding. A request starts only when the rounded-up final lengths of the live ones leave
