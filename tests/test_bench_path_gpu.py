@@ -68,6 +68,9 @@ def test_whole_prompts_of_300_and_600_tokens(dtype):
     got = H.run_trace(eng, H.trace_whole(reqs))
     _check(dtype, got, reqs)
     _assert_bench_kernels_ran(before, dtype)
+    if dtype == torch.bfloat16:
+        # the down product of 300 and 600 tokens: 128 x 256 tiles whose K slices meet in the operand rings
+        assert _ran(before, "gemm_tc:sliced_wide") > 0, "no product ran on wide tiles with K slices"
     assert eng.cache.pages_in_use() == [0]
 
 
