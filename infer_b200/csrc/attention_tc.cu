@@ -188,8 +188,8 @@ struct Params {
     // that way, and the heaviest tile of a causal prompt no longer sets the kernel's time alone.
     int early_release;                       // 1: the successor is released at the kernel's start (few CTAs: a short kernel)
     int split;
-    float* workspace;                        // [segments][heads][query tiles][split][PART_FLOATS]
-    unsigned int* counters;                  // [segments][heads][query tiles], zero between launches
+    float* workspace;                        // [segments of two or more tokens][heads][query tiles][split][PART_FLOATS]
+    unsigned int* counters;                  // [segments of two or more tokens][heads][query tiles], zero between launches
 };
 constexpr int MAX_SPLIT = 4;
 constexpr int PART_MIN_TILES = 4;
@@ -230,7 +230,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     if (part >= n_parts) return;
     const int kt0 = all0 + (n_all * part) / n_parts, kt1 = all0 + (n_all * (part + 1)) / n_parts - 1;
     const int n_tiles = kt1 - kt0 + 1;                   // >= PART_MIN_TILES when the tile is shared, >= 1 otherwise
-    const int tile_id = (seg * p.n_heads + h) * n_qt + qt;
+    // Scratch is laid out over the segments that have two or more tokens only (a step may carry dozens of one-token
+    // segments beside one portion): this segment's rank among those, counted from the segment table.
+    int tile_id = 0;
+    if (n_parts > 1) {
+        int before = 0;
+        for (int s2 = 0; s2 < seg; s2++) before += (p.seg_start[s2 + 1] - p.seg_start[s2] > 1) ? 1 : 0;
+        tile_id = (before * p.n_heads + h) * n_qt + qt;
+    }
     const int* table = p.block_table + int64_t(seg) * p.max_blocks;
     // The page ids of this CTA's key range, checked, in shared memory (a read of the table in global memory costs the
     // producer a round trip to L2 per page otherwise); ranges longer than the array fall back to the table itself.
@@ -589,12 +596,13 @@ IB_EXPORT int ib_attention_tc_head_dim() { return HD; }
 // q, out: bfloat16 [tokens, heads * HD]; caches bfloat16 [pages, kv heads, 16, HD] holding this step's keys and values
 // already; block_table int32 [segments, max_blocks]; seg_start int32 [segments + 1]; seg_pos0 int32 [segments].
 // split: up to how many CTAs share the key tiles of one query tile (1: none); it is lowered to what the workspace
-// (floats) and the counters (one per segment, head and query tile, zero before and after) have room for.
+// (floats) and the counters (zero before and after) have room for: one slot per segment of two or more tokens
+// (n_long_segments of them; 0: assume all), head and query tile.
 IB_EXPORT int ib_attention_prefill_tc(const void* q, const void* k_cache, const void* v_cache, void* out, const int* block_table,
                                       int max_blocks, const int* seg_start, const int* seg_pos0, int n_segments, int64_t n_tokens,
                                       int n_heads, int n_kv, int head_dim, int page_size, int window, float scale, int64_t n_pages,
                                       int max_q_len, int* status, cudaStream_t stream, int split, float* workspace,
-                                      int64_t workspace_floats, unsigned int* counters, int64_t n_counters) {
+                                      int64_t workspace_floats, unsigned int* counters, int64_t n_counters, int n_long_segments) {
     if (n_segments <= 0 || max_q_len <= 1) return IB_OK;
     if (head_dim != HD) return ib::fail(IB_ERR_ARG, "attention_tc: built for head_dim %d, called with %d", HD, head_dim);
     if (page_size != PAGE) return ib::fail(IB_ERR_ARG, "attention_tc: pages must hold %d positions, got %d", PAGE, page_size);
@@ -621,7 +629,8 @@ IB_EXPORT int ib_attention_prefill_tc(const void* q, const void* k_cache, const 
     p.n_heads = n_heads; p.n_kv = n_kv; p.group = n_heads / n_kv; p.window = window; p.scale_log2 = scale * LOG2E;
     p.n_pages = n_pages; p.status = status;
     // Sharing query tiles needs scratch for every (segment, head, query tile); with less than that, fewer parts.
-    const int64_t n_qt = (max_q_len + BM - 1) / BM, tiles = int64_t(n_segments) * n_heads * n_qt;
+    if (n_long_segments <= 0 || n_long_segments > n_segments) n_long_segments = n_segments;
+    const int64_t n_qt = (max_q_len + BM - 1) / BM, tiles = int64_t(n_long_segments) * n_heads * n_qt;
     split = std::max(1, std::min(split, MAX_SPLIT));
     if (!workspace || !counters || tiles > n_counters) split = 1;
     while (split > 1 && tiles * split * PART_FLOATS > workspace_floats) split--;

@@ -285,18 +285,19 @@ def attention_fast(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor
     tc = ATTENTION_TC and max_q_len > 1 and head_dim in ATTENTION_TC_HEAD_DIMS and page_size == 16
     if tc:
         g = _fn("attn_tc", "ib_attention_prefill_tc", [c_void_p] * 5 + [c_int] + [c_void_p] * 2 + [c_int, c_int64] + [c_int] * 5 +
-                [c_float, c_int64, c_int] + [c_void_p] * 2 + [c_int, c_void_p, c_int64, c_void_p, c_int64], {"IB_HEAD_DIM": head_dim})
+                [c_float, c_int64, c_int] + [c_void_p] * 2 + [c_int, c_void_p, c_int64, c_void_p, c_int64, c_int], {"IB_HEAD_DIM": head_dim})
         n_prefill = S - (n_decode or 0)
         split = prefill_split(st.sm_count, n_heads, n_prefill, max_q_len, max_ctx_len, window) if tc_split is None else tc_split
         tc_ws = tc_cnt = None
         if split > 1:
-            tiles = S * n_heads * -(-max_q_len // 128)
+            tiles = max(1, n_prefill) * n_heads * -(-max_q_len // 128)
             tc_ws, tc_cnt = st.workspace(tiles * split * (128 * head_dim + 256)), st.counters(tiles)
             ops.note("attention_prefill_tc:shared_query_tiles")
         _call(g, q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), block_table.data_ptr(),
               block_table.shape[1], seg_start.data_ptr(), seg_pos0.data_ptr(), S, T, n_heads, n_kv, head_dim, page_size,
               int(window or 0), float(scale), n_pages, int(max_q_len), st.status.data_ptr(), _stream(), int(split),
-              _ptr(tc_ws), 0 if tc_ws is None else tc_ws.numel(), _ptr(tc_cnt), 0 if tc_cnt is None else tc_cnt.numel())
+              _ptr(tc_ws), 0 if tc_ws is None else tc_ws.numel(), _ptr(tc_cnt), 0 if tc_cnt is None else tc_cnt.numel(),
+              int(n_prefill) if n_decode is not None else 0)
         if max_q_len > 128:
             ops.note("attention_prefill_tc:several_query_tiles")
         if not has_decode:

@@ -12,7 +12,7 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
 
-def _run(heads, kv, hd, window, segs, n_splits=None, seed=0, n_clusters=1, tc_split=None):
+def _run(heads, kv, hd, window, segs, n_splits=None, seed=0, n_clusters=1, tc_split=None, count_decode=False):
     """segs: list of (context length before the step, tokens in the step)."""
     from infer_b200 import fast_ops
     lens = [c + n for c, n in segs]
@@ -38,7 +38,7 @@ def _run(heads, kv, hd, window, segs, n_splits=None, seed=0, n_clusters=1, tc_sp
         q.reshape(T, -1).contiguous().to(DEV), kc.to(DEV), vc.to(DEV), table.to(DEV),
         torch.tensor(seg_start, dtype=torch.int32, device=DEV), torch.tensor([c for c, _ in segs], dtype=torch.int32, device=DEV),
         heads, kv, hd, window, scale, any(n == 1 for _, n in segs), max(n for _, n in segs), max(lens), n_splits=n_splits,
-        n_clusters=n_clusters, tc_split=tc_split)
+        n_decode=sum(1 for _, n in segs if n == 1) if count_decode else None, n_clusters=n_clusters, tc_split=tc_split)
     assert out is not None
     assert st.status.item() == 0
     got = out.cpu().double().view_as(ref)
@@ -128,6 +128,9 @@ def test_prefill_with_shared_query_tiles(heads, kv, hd, split):
     assert int(fast_ops.device_state(DEV)._counters.abs().sum()) == 0
     whole = _run(heads, kv, hd, None, segs, 2, seed=5, tc_split=1)
     assert (first - whole).abs().max() < 1e-2
+    # as the engine calls it: the scratch is laid out over the segments of two or more tokens only
+    packed = _run(heads, kv, hd, None, segs, 2, seed=5, tc_split=split, count_decode=True)
+    assert torch.equal(first, packed)
     _run(heads, kv, hd, 1200, [(700, 900), (2000, 130)], seed=6, tc_split=split)
 
 
