@@ -2,7 +2,7 @@
 //   out[M, N] = x[M, K] . w[N, K]^T (+ bias[N]) (+ residual[M, N])
 // both operands row-major with K contiguous ("K-major"), float accumulation in tensor memory (TMEM).
 //
-// Structure of one CTA (192 threads, one 128 x BN output tile, BN in {16, 32, 64, 128}):
+// Structure of one CTA (192 threads, one 128 x BN output tile, BN in {16, 32, 64, 128}; 256 with K slices):
 //   warp 0      one lane issues TMA loads (cp.async.bulk.tensor.2d, 128-byte swizzle) of 128 x 64 and BN x 64
 //               operand tiles into a ring of shared-memory stages, each guarded by a full/empty mbarrier pair;
 //   warp 1      allocates BN TMEM columns; one lane issues tcgen05.mma (M=128, N=BN, K=16, kind::f16) four times
@@ -20,7 +20,12 @@
 // adds the slices in ascending order and runs the epilogue. Otherwise (grid.z, up to 16 slices of very few tiles)
 // each CTA writes its float tile to a workspace and the CTA that arrives last at the tile's counter adds the slices
 // in ascending order. Either way the sum does not depend on arrival order.
+// A long K on few tiles (a 512-token portion of a prompt against a down matrix) takes 128 x 256 tiles with 2, 4 or 8
+// K slices as a cluster: 128 KB of float tile do not fit behind the ring, so the slices' columns are received in the
+// operand ring itself, once a cluster barrier has told every slice that the others' MMAs are done.
 // For many tokens a persistent kernel (further down) walks over tiles with two accumulators in tensor memory.
+// ib_gemm_tc_plan chooses among these ways with a time model fitted to measurements.
+// What is read once per step (the weights' tiles) is loaded with the L2 evict-first policy.
 // In the swapped mapping the ring takes up to eight stages (the CTA has the SM to itself and all of its weights
 // should be in flight) and the weights' first stages are requested before the kernel waits for its predecessor.
 //
