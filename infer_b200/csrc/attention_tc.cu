@@ -22,6 +22,11 @@
 // sums. V rows of positions that this step has not written (beyond the segment's last token, or in pages the table
 // does not hold) are zeroed in shared memory before P V, so stale cache contents cannot reach a sum.
 //
+// Where few long query tiles would leave SMs idle (a portion of a prompt behind a long context), the key tiles of a
+// query tile are shared among up to four CTAs: each leaves its unnormalised rows of O, their reference maxima and sums
+// in a workspace, and the one that arrives last at the tile's counter adds the parts in index order and writes the
+// output (the host shares only while all CTAs still run at once: a CTA's start and end cost about three key tiles).
+//
 // One CTA per SM (193 KB of shared memory, all 512 tensor-memory columns). Query tiles start heaviest first. Measured
 // at 2,048 tokens, 12/2 heads of 128: 38 us against 88 us for the mma.sync kernel. A key tile takes about 3,700 cycles,
 // the softmax thread's own sequence (wait for S, read it, maximum, 128 exponentials, wait for the previous P V, store P):
